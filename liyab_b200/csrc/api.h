@@ -1,0 +1,64 @@
+/* The C interface of the kernel library (libliyab_b200.so).
+ *
+ * Plain C types only, one status return per call in the reference's numbering
+ * (0 = ok; include/liyab/liyab_c_api.h:41-53), the message of the last failure on
+ * the calling thread from lb_last_error().  Pointers are device pointers unless a
+ * name says otherwise; `stream` is a cudaStream_t passed as void*.  Element types
+ * are LB_F32 = 0 and LB_BF16 = 1.  Nothing here allocates device memory unless its
+ * comment says so.
+ */
+#pragma once
+
+#include <stdint.h>
+
+#define LB_ABI_VERSION 3
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+const char* lb_last_error(void);
+int lb_abi_version(void);
+
+/* x[t,:] = table[tokens[t],:] * scale + pos_table[positions[t],:] in 32-bit;
+ * pos_table may be null.  Tables are `dtype`; x is float. */
+int lb_embed_positions(int dtype, const int32_t* tokens, const int32_t* positions, const void* table,
+                       const void* pos_table, float* x, int n_tokens, int width, float scale, void* stream);
+
+/* y[r,:] = LayerNorm(x[rows ? rows[r] : r, :]) with 32-bit statistics; weight and
+ * bias are float and may be null; y is `out_dtype`. */
+int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight, const float* bias, void* y,
+                 int n_rows, int width, float eps, void* stream);
+
+/* Copies each token's key and value rows (row_stride elements apart) into the
+ * layer's cache [page][K|V][kv_head][slot][head_dim] at slot_mapping[t] =
+ * page * page_size + slot; a negative entry skips the token. */
+int lb_kv_append(int dtype, const void* k, const void* v, int64_t row_stride, const int32_t* slot_mapping, void* cache,
+                 int n_tokens, int n_kv_head, int head_dim, int page_size, void* stream);
+
+/* out[M,N] = act(A[M,K] . W[N,K]^T + bias) + residual on the 32-bit units; bias
+ * and residual (float, row stride ldr) may be null; out may alias residual. */
+int lb_gemm_ffma(int in_dtype, int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                 const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                 void* stream);
+
+/* Causal attention of every token of the step over its request's pages.
+ * q: [n_tokens, n_head*head_dim] with row stride q_stride; tok_seq[t] is the row
+ * of block_table (stride table_stride) of the token's request; positions[t] its
+ * absolute position; window 0 = all earlier keys. */
+int lb_paged_attention_generic(int dtype, const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq,
+                               const int32_t* positions, const int32_t* block_table, int table_stride, void* out,
+                               int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
+                               int page_size, float scale, int window, void* stream);
+
+/* One token id per row of logits.  temperature[r] <= 0: the first maximum.
+ * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw
+ * uniform[r] in [0,1).  out_probs (optional, [n_rows, vocab]) receives the
+ * distribution drawn from. */
+int lb_sample(const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
+              const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids, float* out_probs,
+              void* stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -1,0 +1,152 @@
+// Causal attention over the paged cache for any mix of prompt portions and
+// single decoded tokens, any head size up to 256 and any number of heads and
+// key/value groups, with all arithmetic in 32-bit.
+//
+// This is the 32-bit engine's attention and the fallback of the bfloat16 engine
+// for shapes its tensor-core kernels refuse.  One warp serves one (token, head):
+// it walks the token's visible keys 32 at a time from the first visible key, so
+// the order of every sum depends on the token's position only, never on the
+// batch or on where its pages lie (the reference cuts a token's keys by its
+// position alone for the same reason: src/core/transformer.cpp:2130-2144,
+// 2225-2227).  Scores s_j = (q . k_j) * scale, running maximum, p = exp(s - m),
+// o = sum p_j v_j, out = o / sum p (src/core/transformer.cpp:2303-2313, 2327-2341,
+// 2344-2358, 2367-2385).
+#include "api.h"
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kTile = 32;       // keys per step, one per lane
+constexpr int kMaxHeadDim = 256;
+
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ cache,
+                               const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
+                               const int32_t* __restrict__ block_table, int table_stride, T* __restrict__ out,
+                               int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
+                               int page_size, float scale, int window) {
+    extern __shared__ float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int pair = blockIdx.x * kWarps + warp;
+    if (pair >= n_tokens * n_head) return;     // whole warps leave; no block-wide barrier below
+    const int t = pair / n_head, h = pair - t * n_head;
+    const int kvh = h / (n_head / n_kv_head);
+    const int pos = positions[t];
+    const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
+
+    const int tile_stride = head_dim + 1;
+    float* q_s = smem + (size_t)warp * (head_dim + kTile * tile_stride + kTile);
+    float* tile = q_s + head_dim;
+    float* p_s = tile + kTile * tile_stride;
+
+    const T* q_row = q + (size_t)t * q_stride + (size_t)h * head_dim;
+    for (int d = lane; d < head_dim; d += 32) q_s[d] = lb_to_float(q_row[d]);
+
+    const size_t plane = (size_t)n_kv_head * page_size * head_dim;
+    float m = -CUDART_INF_F, l = 0.0f;
+    float acc[kMaxHeadDim / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
+
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    for (int j0 = first; j0 <= pos; j0 += kTile) {
+        const int n_keys = min(kTile, pos + 1 - j0);
+        // Each lane resolves its own key's row once; the others fetch it by shuffle.
+        long long base = -1;
+        if (lane < n_keys) {
+            const int j = j0 + lane;
+            const int page = table[j / page_size];
+            base = (long long)page * 2 * (long long)plane + ((long long)kvh * page_size + (j % page_size)) * head_dim;
+        }
+        __syncwarp();
+        for (int idx = lane; idx < kTile * head_dim; idx += 32) {
+            const int key = idx / head_dim, d = idx - key * head_dim;
+            const long long b = __shfl_sync(0xffffffffu, base, key);
+            tile[key * tile_stride + d] = b >= 0 ? lb_to_float(cache[b + d]) : 0.0f;
+        }
+        __syncwarp();
+        float s = -CUDART_INF_F;
+        if (lane < n_keys) {
+            float dot = 0.0f;
+            const float* krow = tile + lane * tile_stride;
+            for (int d = 0; d < head_dim; ++d) dot = fmaf(q_s[d], krow[d], dot);
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, lb_warp_max(s));
+        const float p = lane < n_keys ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first tile
+        l = l * corr + lb_warp_sum(p);
+        m = m_new;
+        p_s[lane] = p;
+        __syncwarp();
+        for (int idx = lane; idx < kTile * head_dim; idx += 32) {
+            const int key = idx / head_dim, d = idx - key * head_dim;
+            const long long b = __shfl_sync(0xffffffffu, base, key);
+            tile[key * tile_stride + d] = b >= 0 ? lb_to_float(cache[b + (long long)plane + d]) : 0.0f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) {
+                float o = acc[i] * corr;
+                for (int j = 0; j < n_keys; ++j) o = fmaf(p_s[j], tile[j * tile_stride + d], o);
+                acc[i] = o;
+            }
+        }
+        __syncwarp();
+    }
+    const float inv = 1.0f / l;
+    T* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < head_dim) o_row[d] = lb_from_float<T>(acc[i] * inv);
+    }
+}
+
+template <typename T>
+int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
+           const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
+           int n_kv_head, int head_dim, int page_size, float scale, int window, cudaStream_t s) {
+    const size_t smem = (size_t)kWarps * (head_dim + kTile * (head_dim + 1) + kTile) * sizeof(float);
+    static size_t configured = 0;   // largest dynamic shared memory asked for so far
+    if (smem > configured) {
+        LB_CHECK_CUDA(cudaFuncSetAttribute(paged_attention_generic_kernel<T>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
+    }
+    const long long pairs = (long long)n_tokens * n_head;
+    const unsigned blocks = (unsigned)((pairs + kWarps - 1) / kWarps);
+    paged_attention_generic_kernel<T><<<blocks, kWarps * 32, smem, s>>>(
+        (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
+        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+}  // namespace
+
+extern "C" int lb_paged_attention_generic(int dtype, const void* q, int64_t q_stride, const void* cache,
+                                          const int32_t* tok_seq, const int32_t* positions,
+                                          const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                          int n_tokens, int n_head, int n_kv_head, int head_dim, int page_size,
+                                          float scale, int window, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_head > 0 && n_kv_head > 0 && page_size > 0, "attention: bad sizes");
+    LB_CHECK_ARG(n_head % n_kv_head == 0, "attention: n_head %d is not a multiple of n_kv_head %d", n_head, n_kv_head);
+    LB_CHECK_ARG(head_dim > 0 && head_dim <= kMaxHeadDim, "attention: head_dim %d is outside (0, %d]", head_dim,
+                 kMaxHeadDim);
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dtype == LB_F32)
+        return launch<float>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out, out_stride,
+                             n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, s);
+    if (dtype == LB_BF16)
+        return launch<__nv_bfloat16>(q, q_stride, cache, tok_seq, positions, block_table, table_stride, out,
+                                     out_stride, n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window, s);
+    return lb_fail(LB_ERR_INVALID_ARGUMENT, "attention: unknown dtype %d", dtype);
+}

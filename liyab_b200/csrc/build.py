@@ -1,0 +1,174 @@
+"""Builds and loads the kernel library.
+
+Every .cu file of this folder is compiled for sm_100a with nvcc into an object,
+and the objects are linked into libliyab_b200.so under `_build/` beside the
+sources (or, where that folder cannot be written, under the system's temporary
+folder).  Nothing is built when the library on disk was made from the same
+sources and flags.  The first call in a fresh checkout therefore compiles what
+the engine needs, printing a line per file; later calls only load.
+
+There is no fallback: without the library (no nvcc, a compile error) the engine
+raises, it never computes on the CPU or through another library instead.
+"""
+from __future__ import annotations
+
+import ctypes
+import fcntl
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+from concurrent.futures import ThreadPoolExecutor
+from typing import List, Optional
+
+from ..status import backend_error
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_NAME = "libliyab_b200.so"
+NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
+              "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-warn-spills"]
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+
+
+def _say(msg: str) -> None:
+    print(f"[liyab_b200] {msg}", file=sys.stderr, flush=True)
+
+
+def sources() -> List[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+
+
+def _headers() -> List[str]:
+    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+
+
+def _digest(files: List[str], extra: str = "") -> str:
+    h = hashlib.sha256(extra.encode())
+    for name in files:
+        with open(os.path.join(HERE, name), "rb") as f:
+            h.update(name.encode() + b"\0" + f.read())
+    return h.hexdigest()[:24]
+
+
+def find_nvcc() -> str:
+    for cand in (os.environ.get("LIYAB_NVCC"), shutil.which("nvcc"),
+                 os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "bin", "nvcc"), "/usr/local/cuda/bin/nvcc"):
+        if cand and os.path.isfile(cand) and os.access(cand, os.X_OK):
+            return cand
+    raise backend_error("nvcc was not found (looked at $LIYAB_NVCC, PATH, $CUDA_HOME/bin and /usr/local/cuda/bin); "
+                        "the engine's kernels cannot be built and there is no other path")
+
+
+def build_dir() -> str:
+    env = os.environ.get("LIYAB_B200_BUILD_DIR")
+    if env:
+        os.makedirs(env, exist_ok=True)
+        return env
+    local = os.path.join(HERE, "_build")
+    try:
+        os.makedirs(local, exist_ok=True)
+        probe = os.path.join(local, f".write_probe_{os.getpid()}")
+        with open(probe, "w"):
+            pass
+        os.unlink(probe)
+        return local
+    except OSError:
+        alt = os.path.join(tempfile.gettempdir(), f"liyab_b200_build_{os.getuid()}")
+        os.makedirs(alt, exist_ok=True)
+        return alt
+
+
+def _compile_one(nvcc: str, src: str, obj: str, log: str) -> None:
+    cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+    proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    with open(log, "w") as f:
+        f.write(" ".join(cmd) + "\n" + proc.stdout)
+    if proc.returncode != 0:
+        raise backend_error(f"nvcc failed on {src}:\n{proc.stdout[-4000:]}")
+
+
+def ensure_built(verbose: bool = True) -> str:
+    """Compiles what is out of date and returns the path of the library."""
+    out = build_dir()
+    srcs, hdrs = sources(), _headers()
+    flags = " ".join(NVCC_FLAGS)
+    whole = _digest(srcs + hdrs, flags)
+    lib = os.path.join(out, LIB_NAME)
+    stamp = os.path.join(out, "stamp")
+
+    def fresh() -> bool:
+        try:
+            with open(stamp) as f:
+                return f.read().strip() == whole and os.path.isfile(lib)
+        except OSError:
+            return False
+
+    if fresh():
+        return lib
+    with open(os.path.join(out, ".lock"), "w") as lockf:
+        fcntl.flock(lockf, fcntl.LOCK_EX)
+        try:
+            if fresh():
+                return lib
+            nvcc = find_nvcc()
+            hdr_digest = _digest(hdrs, flags)
+            todo, objs = [], []
+            for src in srcs:
+                tag = _digest([src], hdr_digest)
+                obj = os.path.join(out, f"{os.path.splitext(src)[0]}.{tag}.o")
+                objs.append(obj)
+                if not os.path.isfile(obj):
+                    todo.append((src, obj))
+            if todo and verbose:
+                _say(f"compiling {len(todo)} CUDA source file(s) for sm_100a into {out} (first call only)")
+            t0 = time.time()
+            done = [0]
+
+            def work(item):
+                src, obj = item
+                tmp = obj + f".tmp{os.getpid()}"
+                _compile_one(nvcc, src, tmp, os.path.join(out, src + ".log"))
+                os.replace(tmp, obj)
+                done[0] += 1
+                if verbose:
+                    _say(f"  compiled {src} ({done[0]}/{len(todo)}, {time.time() - t0:.0f} s)")
+
+            with ThreadPoolExecutor(max_workers=min(8, max(1, os.cpu_count() or 1))) as pool:
+                list(pool.map(work, todo))
+            tmp_lib = lib + f".tmp{os.getpid()}"
+            link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+            proc = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+            if proc.returncode != 0:
+                raise backend_error(f"linking {LIB_NAME} failed:\n{proc.stdout[-4000:]}")
+            os.replace(tmp_lib, lib)
+            with open(stamp, "w") as f:
+                f.write(whole)
+            keep = set(objs)
+            for name in os.listdir(out):       # objects of older sources
+                path = os.path.join(out, name)
+                if name.endswith(".o") and path not in keep:
+                    os.unlink(path)
+            if verbose and todo:
+                _say(f"built {LIB_NAME} in {time.time() - t0:.0f} s")
+            return lib
+        finally:
+            fcntl.flock(lockf, fcntl.LOCK_UN)
+
+
+def load_library() -> ctypes.CDLL:
+    """The loaded kernel library; built first if it has to be."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            path = ensure_built()
+            try:
+                _lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise backend_error(f"cannot load {path}: {e}") from e
+        return _lib

@@ -1,0 +1,160 @@
+// Embedding + position add, LayerNorm, and the copy of new keys and values into
+// their cache pages.  All three are bound by memory traffic; each row is read
+// once and written once.
+#include "api.h"
+#include "common.cuh"
+
+#include <cstring>
+
+// ---------------------------------------------------------------- errors
+
+static thread_local char g_last_error[512] = "";
+
+int lb_fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_last_error, sizeof g_last_error, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+extern "C" const char* lb_last_error(void) { return g_last_error; }
+
+extern "C" int lb_abi_version(void) { return LB_ABI_VERSION; }
+
+// ---------------------------------------------------------------- embedding
+
+// x[t, :] = table[token[t], :] * scale + positions[pos[t], :]  (32-bit sum).
+// Reference: embed (src/core/transformer.cpp:5495-5512), add_positions (:2791-2808).
+template <typename T>
+__global__ void embed_positions_kernel(const int32_t* __restrict__ tokens, const int32_t* __restrict__ pos,
+                                       const T* __restrict__ table, const T* __restrict__ pos_table,
+                                       float* __restrict__ x, int width, float scale) {
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)tokens[t] * width;
+    const T* prow = pos_table != nullptr ? pos_table + (size_t)pos[t] * width : nullptr;
+    float* out = x + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = lb_to_float(row[i]) * scale;
+        if (prow != nullptr) v += lb_to_float(prow[i]);
+        out[i] = v;
+    }
+}
+
+extern "C" int lb_embed_positions(int dtype, const int32_t* tokens, const int32_t* positions, const void* table,
+                                  const void* pos_table, float* x, int n_tokens, int width, float scale,
+                                  void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && width > 0, "embed: bad sizes n_tokens=%d width=%d", n_tokens, width);
+    if (n_tokens == 0) return LB_OK;
+    const int threads = width >= 1024 ? 256 : 128;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (dtype == LB_F32) {
+        embed_positions_kernel<float><<<n_tokens, threads, 0, s>>>(tokens, positions, (const float*)table,
+                                                                  (const float*)pos_table, x, width, scale);
+    } else if (dtype == LB_BF16) {
+        embed_positions_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>(
+            tokens, positions, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pos_table, x, width, scale);
+    } else {
+        return lb_fail(LB_ERR_INVALID_ARGUMENT, "embed: unknown dtype %d", dtype);
+    }
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+// ---------------------------------------------------------------- LayerNorm
+
+// y = (x - mean) / sqrt(var + eps) * w + b with the population variance of the
+// centred values, both statistics in 32-bit (two passes over the row, so no
+// cancellation).  Reference: layernorm (src/core/transformer.cpp:77-106), which
+// accumulates in double; the difference is below one 32-bit rounding of y.
+// `rows` (optional) gathers: output row r is made from input row rows[r].
+template <typename T>
+__global__ void layernorm_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows,
+                                 const float* __restrict__ w, const float* __restrict__ b, T* __restrict__ y,
+                                 int width, float eps) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const float* in = x + (size_t)(rows != nullptr ? rows[r] : r) * width;
+    T* out = y + (size_t)r * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) sum += in[i];
+    const float mean = lb_block_sum(sum, scratch) / (float)width;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float d = in[i] - mean;
+        ss = fmaf(d, d, ss);
+    }
+    const float var = lb_block_sum(ss, scratch) / (float)width;
+    const float inv = 1.0f / sqrtf(var + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = (in[i] - mean) * inv;
+        if (w != nullptr) v *= w[i];
+        if (b != nullptr) v += b[i];
+        out[i] = lb_from_float<T>(v);
+    }
+}
+
+extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight,
+                            const float* bias, void* y, int n_rows, int width, float eps, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && width > 0, "layernorm: bad sizes n_rows=%d width=%d", n_rows, width);
+    if (n_rows == 0) return LB_OK;
+    const int threads = width >= 2048 ? 256 : 128;   // fixed by the width alone: a row's sums never depend on the batch
+    auto s = static_cast<cudaStream_t>(stream);
+    if (out_dtype == LB_F32) {
+        layernorm_kernel<float><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (float*)y, width, eps);
+    } else if (out_dtype == LB_BF16) {
+        layernorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (__nv_bfloat16*)y, width, eps);
+    } else {
+        return lb_fail(LB_ERR_INVALID_ARGUMENT, "layernorm: unknown dtype %d", out_dtype);
+    }
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+// ---------------------------------------------------------------- cache append
+
+// Copies each new token's key and value rows into its page.  A layer's cache is
+// [page][K|V][kv_head][slot][head_dim]; slot_mapping[t] = page * page_size + slot
+// (negative: the token's keys are not kept, e.g. a layer that reads another's cache).
+// Reference: store_kv (src/core/transformer.cpp:2875-2890, src/core/kv_cache.cpp:322-332).
+template <typename T>
+__global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, int64_t row_stride,
+                                 const int32_t* __restrict__ slot_mapping, T* __restrict__ cache, int n_kv_head,
+                                 int head_dim, int page_size) {
+    const int t = blockIdx.x;
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const int page = slot / page_size, off = slot - page * page_size;
+    const int row = n_kv_head * head_dim;
+    const size_t plane = (size_t)n_kv_head * page_size * head_dim;
+    T* kdst = cache + (size_t)page * 2 * plane;
+    T* vdst = kdst + plane;
+    const T* ksrc = k + (size_t)t * row_stride;
+    const T* vsrc = v + (size_t)t * row_stride;
+    for (int i = threadIdx.x; i < row; i += blockDim.x) {
+        const int h = i / head_dim, d = i - h * head_dim;
+        const size_t at = ((size_t)h * page_size + off) * head_dim + d;
+        kdst[at] = ksrc[i];
+        vdst[at] = vsrc[i];
+    }
+}
+
+extern "C" int lb_kv_append(int dtype, const void* k, const void* v, int64_t row_stride, const int32_t* slot_mapping,
+                            void* cache, int n_tokens, int n_kv_head, int head_dim, int page_size, void* stream) {
+    LB_CHECK_ARG(n_tokens >= 0 && n_kv_head > 0 && head_dim > 0 && page_size > 0, "kv_append: bad sizes");
+    if (n_tokens == 0) return LB_OK;
+    auto s = static_cast<cudaStream_t>(stream);
+    const int threads = 128;
+    if (dtype == LB_F32) {
+        kv_append_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)k, (const float*)v, row_stride, slot_mapping,
+                                                            (float*)cache, n_kv_head, head_dim, page_size);
+    } else if (dtype == LB_BF16) {
+        kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+                                                                    row_stride, slot_mapping, (__nv_bfloat16*)cache,
+                                                                    n_kv_head, head_dim, page_size);
+    } else {
+        return lb_fail(LB_ERR_INVALID_ARGUMENT, "kv_append: unknown dtype %d", dtype);
+    }
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}

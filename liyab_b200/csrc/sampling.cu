@@ -1,0 +1,338 @@
+// Next-token choice on the device: greedy, or temperature -> top-k -> top-p ->
+// draw, one thread block per row of logits, each row with its own options.
+//
+// The distribution is the reference sampler's (src/core/sampling.cpp:16-61):
+// keep the top_k largest logits, p_i = exp((l_i - l_max) / T) in float, total in
+// double, keep the shortest prefix of the candidates sorted by logit whose
+// cumulative p_i / total reaches top_p, renormalise by the kept mass; then walk
+// the ids in index order subtracting p_i from r = u * total until r < 0
+// (sampling.cpp:66-79).  Greedy takes the first maximum (sampling.cpp:12-14).
+// Where the reference's order among equal logits is left to std::nth_element and
+// std::sort, ties here go to the lower index.  Nothing is sorted: the k-th
+// largest logit and the top-p cut are found by radix selection over the logits'
+// bit patterns (four passes of eight bits), by count for top-k and by probability
+// mass for top-p.
+#include "api.h"
+#include "common.cuh"
+
+#include <math_constants.h>
+
+namespace {
+
+constexpr int kThreads = 1024;
+
+// Monotone map from float to uint32: a larger float gives a larger key.
+__device__ __forceinline__ uint32_t order_key(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+struct ArgMax {
+    float v;
+    int i;
+};
+
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* 33 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b{__shfl_xor_sync(0xffffffffu, a.v, o), __shfl_xor_sync(0xffffffffu, a.i, o)};
+        a = better(a, b);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = a;
+    __syncthreads();
+    if (warp == 0) {
+        ArgMax t = lane < (int)(blockDim.x >> 5) ? scratch[lane] : ArgMax{-CUDART_INF_F, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax b{__shfl_xor_sync(0xffffffffu, t.v, o), __shfl_xor_sync(0xffffffffu, t.i, o)};
+            t = better(t, b);
+        }
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Exclusive prefix sum of one value per thread, in thread order; returns the
+// block total through *total.  T is int or double.
+template <typename T>
+__device__ T block_exclusive_scan(T v, T* scratch /* 33 */, T* total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    T inc = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const T up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+    }
+    __syncthreads();
+    if (lane == 31) scratch[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+        T w = lane < n_warps ? scratch[lane] : T(0);
+        T winc = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const T up = __shfl_up_sync(0xffffffffu, winc, o);
+            if (lane >= o) winc += up;
+        }
+        scratch[lane] = winc - w;           // exclusive offset of each warp
+        if (lane == 31) scratch[32] = winc;  // block total
+    }
+    __syncthreads();
+    *total = scratch[32];
+    return scratch[warp] + inc - v;
+}
+
+__global__ void __launch_bounds__(kThreads)
+sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, const float* __restrict__ temperature,
+              const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const double* __restrict__ uniform,
+              int32_t* __restrict__ out_ids, float* __restrict__ out_probs) {
+    __shared__ ArgMax am_scratch[33];
+    __shared__ int i_scratch[33];
+    __shared__ double d_scratch[33];
+    __shared__ int hist_count[256];
+    __shared__ double hist_mass[256];
+    __shared__ uint32_t sh_prefix;
+    __shared__ int sh_int;
+    __shared__ double sh_double;
+    __shared__ int sh_choice;
+
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const float* x = logits + (size_t)row * row_stride;
+    float* probs = out_probs != nullptr ? out_probs + (size_t)row * vocab : nullptr;
+    const float temp = temperature[row];
+
+    // Contiguous range of this thread: sums and ranks in index order need one scan.
+    const int per = (vocab + kThreads - 1) / kThreads;
+    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+
+    ArgMax best{-CUDART_INF_F, 0x7fffffff};
+    for (int i = tid; i < vocab; i += kThreads) best = better(best, ArgMax{x[i], i});
+    best = block_argmax(best, am_scratch);
+    if (temp <= 0.0f) {
+        if (probs != nullptr)
+            for (int i = tid; i < vocab; i += kThreads) probs[i] = i == best.i ? 1.0f : 0.0f;
+        if (tid == 0) out_ids[row] = best.i;
+        return;
+    }
+    const float max_logit = best.v;
+    const float inv_t = 1.0f / temp;
+
+    // ---- top-k by count: key of the k-th largest, and how many ties at it are kept.
+    int k = top_k[row];
+    uint32_t kth_key = 0;          // every key >= 0 is a member when top-k is off
+    int kth_need = 0x7fffffff;     // ties at kth_key that are members (by index order)
+    if (k > 0 && k < vocab) {
+        uint32_t prefix = 0;
+        int remaining = k;         // rank still to find inside the current bucket
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += kThreads) hist_count[b] = 0;
+            __syncthreads();
+            const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            for (int i = tid; i < vocab; i += kThreads) {
+                const uint32_t key = order_key(x[i]);
+                if ((key & mask) == prefix) atomicAdd(&hist_count[(key >> shift) & 255u], 1);
+            }
+            __syncthreads();
+            if (tid == 0) {
+                int rem = remaining, digit = 255;
+                for (; digit > 0; --digit) {
+                    if (hist_count[digit] >= rem) break;
+                    rem -= hist_count[digit];
+                }
+                sh_int = rem;
+                sh_prefix = prefix | ((uint32_t)digit << shift);
+            }
+            __syncthreads();
+            remaining = sh_int;
+            prefix = sh_prefix;
+            __syncthreads();
+        }
+        kth_key = prefix;
+        kth_need = remaining;      // >= 1
+    }
+
+    // ---- rank of each tie at kth_key in index order (only if some ties are cut).
+    int tie_rank_base = 0;
+    {
+        int mine = 0;
+        for (int i = lo; i < hi; ++i) mine += order_key(x[i]) == kth_key ? 1 : 0;
+        int total;
+        tie_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
+    }
+    // member(i): key > kth_key, or key == kth_key and its rank among such ties < kth_need.
+
+    // ---- total mass of the members.
+    double total_mass;
+    {
+        double mine = 0.0;
+        int rank = tie_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            if (member) mine += (double)expf((x[i] - max_logit) * inv_t);
+        }
+        block_exclusive_scan<double>(mine, d_scratch, &total_mass);
+    }
+
+    // ---- top-p by mass over the members: cut key, mass above it, ties kept at it.
+    const float p_cut = top_p[row];
+    uint32_t cut_key = 0;
+    int cut_need = 0x7fffffff;
+    double kept_mass = total_mass;
+    if (p_cut < 1.0f) {
+        uint32_t prefix = 0;
+        double above = 0.0;        // mass of members with a key above the current bucket
+        for (int shift = 24; shift >= 0; shift -= 8) {
+            for (int b = tid; b < 256; b += kThreads) hist_mass[b] = 0.0;
+            __syncthreads();
+            const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+            int rank = tie_rank_base;
+            for (int i = lo; i < hi; ++i) {
+                const uint32_t key = order_key(x[i]);
+                bool member = key > kth_key;
+                if (key == kth_key) member = rank++ < kth_need;
+                if (member && (key & mask) == prefix)
+                    atomicAdd(&hist_mass[(key >> shift) & 255u], (double)expf((x[i] - max_logit) * inv_t));
+            }
+            __syncthreads();
+            if (tid == 0) {
+                double acc = above;
+                int digit = 255;
+                for (; digit > 0; --digit) {
+                    if ((acc + hist_mass[digit]) / total_mass >= (double)p_cut) break;
+                    acc += hist_mass[digit];
+                }
+                sh_double = acc;
+                sh_prefix = prefix | ((uint32_t)digit << shift);
+            }
+            __syncthreads();
+            above = sh_double;
+            prefix = sh_prefix;
+            __syncthreads();
+        }
+        cut_key = prefix;
+        // Members at cut_key all have the same p; keep as many (in index order) as the prefix needs.
+        if (tid == 0) {
+            const uint32_t b = (cut_key & 0x80000000u) ? (cut_key & 0x7fffffffu) : ~cut_key;
+            const float pv = expf((__uint_as_float(b) - max_logit) * inv_t);
+            // At least one tie is kept (the bucket was chosen because it reaches p_cut or is the last).
+            const double unit = (double)pv / total_mass, start = above / total_mass;
+            long long need = unit > 0.0 ? (long long)ceil(((double)p_cut - start) / unit) : 1;
+            if (need < 1) need = 1;
+            if (need > vocab) need = vocab;
+            while (need > 1 && start + (double)(need - 1) * unit >= (double)p_cut) --need;
+            while (need < vocab && start + (double)need * unit < (double)p_cut) ++need;
+            sh_int = (int)need;
+        }
+        __syncthreads();
+        cut_need = sh_int;
+        __syncthreads();
+    }
+
+    // ---- final pass in index order: kept mass, probabilities, and the draw.
+    // kept(i): member(i) and (key > cut_key, or key == cut_key with rank among member ties at cut_key < cut_need).
+    int cut_rank_base = 0;
+    {
+        int mine = 0, rank = tie_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            mine += (member && key == cut_key) ? 1 : 0;
+        }
+        int total;
+        cut_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
+    }
+    {
+        double mine = 0.0;
+        int rank = tie_rank_base, crank = cut_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            bool kept = member && key > cut_key;
+            if (member && key == cut_key) kept = crank++ < cut_need;
+            if (kept) mine += (double)expf((x[i] - max_logit) * inv_t);
+        }
+        block_exclusive_scan<double>(mine, d_scratch, &kept_mass);
+    }
+    // Normalised float probabilities, their double sum in index order, and the walk.
+    double my_sum = 0.0;
+    {
+        int rank = tie_rank_base, crank = cut_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            bool kept = member && key > cut_key;
+            if (member && key == cut_key) kept = crank++ < cut_need;
+            const float p = kept ? (float)((double)expf((x[i] - max_logit) * inv_t) / kept_mass) : 0.0f;
+            if (probs != nullptr) probs[i] = p;
+            my_sum += (double)p;
+        }
+    }
+    double total;
+    const double before = block_exclusive_scan<double>(my_sum, d_scratch, &total);
+    if (tid == 0) sh_choice = 0x7fffffff;
+    __syncthreads();
+    const double r = uniform[row] * total;
+    if (before <= r && r < before + my_sum) {
+        // The draw falls inside this thread's range: walk it as the reference walks the whole vocabulary.
+        double left = r - before;
+        int rank = tie_rank_base, crank = cut_rank_base, choice = -1;
+        for (int i = lo; i < hi && choice < 0; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            bool kept = member && key > cut_key;
+            if (member && key == cut_key) kept = crank++ < cut_need;
+            if (!kept) continue;
+            left -= (double)(float)((double)expf((x[i] - max_logit) * inv_t) / kept_mass);
+            if (left < 0.0) choice = i;
+        }
+        if (choice >= 0) atomicMin(&sh_choice, choice);
+    }
+    __syncthreads();
+    if (sh_choice == 0x7fffffff) {
+        // Rounding left r at or past the last kept id: take the last id with mass.
+        int last = -1, rank = tie_rank_base, crank = cut_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            bool kept = member && key > cut_key;
+            if (member && key == cut_key) kept = crank++ < cut_need;
+            if (kept && expf((x[i] - max_logit) * inv_t) > 0.0f) last = i;
+        }
+        __shared__ int sh_last;
+        if (tid == 0) sh_last = -1;
+        __syncthreads();
+        if (last >= 0) atomicMax(&sh_last, last);
+        __syncthreads();
+        if (tid == 0) out_ids[row] = sh_last >= 0 ? sh_last : best.i;
+    } else if (tid == 0) {
+        out_ids[row] = sh_choice;
+    }
+}
+
+}  // namespace
+
+extern "C" int lb_sample(const float* logits, int64_t row_stride, int n_rows, int vocab, const float* temperature,
+                         const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids,
+                         float* out_probs, void* stream) {
+    LB_CHECK_ARG(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
+    if (n_rows == 0) return LB_OK;
+    sample_kernel<<<n_rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}

@@ -1,0 +1,191 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks what the kernel cannot check for itself (device, types,
+contiguity, sizes it refuses), passes raw device pointers and the current CUDA
+stream to the library's C interface, and turns a non-zero status into a
+`LiyabError`.  Nothing here computes: there is no CPU path and no library
+fallback; a tensor that is not on a CUDA device is an error.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .csrc.build import load_library
+from .status import ErrorCode, LiyabError, invalid_argument
+
+F32, BF16 = 0, 1
+ACTIVATIONS = {"none": 0, "gelu_tanh": 1, "gelu_erf": 2}
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_c = ctypes
+_p, _i, _l, _f = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float
+
+_SIGNATURES = {
+    "lb_embed_positions": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
+    "lb_layernorm": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
+    "lb_kv_append": [_i, _p, _p, _l, _p, _p, _i, _i, _i, _i, _p],
+    "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
+    "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
+    "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
+}
+
+_lib = None
+
+
+def lib():
+    """The kernel library with argument types declared (built at first use)."""
+    global _lib
+    if _lib is None:
+        l = load_library()
+        l.lb_last_error.restype = _c.c_char_p
+        for name, args in _SIGNATURES.items():
+            fn = getattr(l, name)
+            fn.argtypes = args
+            fn.restype = _i
+        _lib = l
+    return _lib
+
+
+def declare(name: str, argtypes) -> None:
+    """Registers the signature of a further exported function."""
+    _SIGNATURES[name] = argtypes
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = argtypes
+        fn.restype = _i
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        msg = lib().lb_last_error().decode("utf-8", "replace")
+        try:
+            code = ErrorCode(status)
+        except ValueError:
+            code = ErrorCode.INTERNAL
+        raise LiyabError(code, f"{what}: {msg}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _dev(t: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> int:
+    if not t.is_cuda:
+        raise invalid_argument(f"{name} is on {t.device}; the engine's kernels run on a CUDA device only")
+    if dtype is not None and t.dtype != dtype:
+        raise invalid_argument(f"{name} has dtype {t.dtype}, expected {dtype}")
+    return t.data_ptr()
+
+
+def _opt(t: Optional[torch.Tensor], name: str, dtype: Optional[torch.dtype] = None) -> Optional[int]:
+    return None if t is None else _dev(t, name, dtype)
+
+
+def _code(dtype: torch.dtype, name: str) -> int:
+    if dtype not in _DT:
+        raise invalid_argument(f"{name} has dtype {dtype}; the kernels take float32 and bfloat16")
+    return _DT[dtype]
+
+
+# ------------------------------------------------------------------ elementwise
+
+def embed_positions(tokens: torch.Tensor, positions: torch.Tensor, table: torch.Tensor,
+                    pos_table: Optional[torch.Tensor], out: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = table[tokens[t]] * scale + pos_table[positions[t]], 32-bit."""
+    n, width = tokens.numel(), table.shape[1]
+    if pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != width):
+        raise invalid_argument("embed: the position table does not match the embedding table")
+    if out.shape[0] < n or out.shape[1] != width or not out.is_contiguous():
+        raise invalid_argument("embed: output buffer has the wrong shape")
+    check(lib().lb_embed_positions(_code(table.dtype, "table"), _dev(tokens, "tokens", torch.int32),
+                                   _dev(positions, "positions", torch.int32), _dev(table, "table"),
+                                   _opt(pos_table, "pos_table"), _dev(out, "out", torch.float32), n, width,
+                                   float(scale), stream_ptr()), "embed_positions")
+    return out
+
+
+def layernorm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,
+              out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = LayerNorm(x[rows[r]] or x[r]); statistics in 32-bit."""
+    width = x.shape[1]
+    if not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != width or out.shape[0] < n_rows:
+        raise invalid_argument("layernorm: buffers must be contiguous [rows, width]")
+    check(lib().lb_layernorm(_code(out.dtype, "out"), _dev(x, "x", torch.float32), _opt(rows, "rows", torch.int32),
+                             _opt(weight, "weight", torch.float32), _opt(bias, "bias", torch.float32), _dev(out, "out"),
+                             n_rows, width, float(eps), stream_ptr()), "layernorm")
+    return out
+
+
+def kv_append(k: torch.Tensor, v: torch.Tensor, slot_mapping: torch.Tensor, cache: torch.Tensor, n_tokens: int,
+              n_kv_head: int, head_dim: int, page_size: int) -> None:
+    """Copies the step's key and value rows (views with a common row stride) into the layer's pages."""
+    if k.stride(0) != v.stride(0) or k.stride(1) != 1 or v.stride(1) != 1 or k.dtype != cache.dtype:
+        raise invalid_argument("kv_append: k and v must share a row stride, be dense in a row and match the cache type")
+    check(lib().lb_kv_append(_code(cache.dtype, "cache"), _dev(k, "k"), _dev(v, "v"), k.stride(0),
+                             _dev(slot_mapping, "slot_mapping", torch.int32), _dev(cache, "cache"), n_tokens,
+                             n_kv_head, head_dim, page_size, stream_ptr()), "kv_append")
+
+
+# ------------------------------------------------------------------ matrix products
+
+def gemm_ffma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
+              activation: str = "none", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual, on the 32-bit units."""
+    n, k = w.shape
+    if a.shape[1] != k or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != n:
+        raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if a.dtype != w.dtype:
+        raise invalid_argument(f"gemm: a is {a.dtype} but w is {w.dtype}")
+    if residual is not None and (residual.shape[1] != n or residual.stride(1) != 1):
+        raise invalid_argument("gemm: residual has the wrong shape")
+    check(lib().lb_gemm_ffma(_code(a.dtype, "a"), _code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"),
+                             w.stride(0), _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
+                             residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n,
+                             k, ACTIVATIONS[activation], stream_ptr()), "gemm_ffma")
+    return out
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
+           activation: str = "none", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual: the kernel is chosen by type and size."""
+    return gemm_ffma(a, w, bias, out, m, activation, residual)
+
+
+# ------------------------------------------------------------------ attention
+
+def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, tok_seq: torch.Tensor, positions: torch.Tensor,
+                            block_table: torch.Tensor, out: torch.Tensor, n_tokens: int, n_head: int, n_kv_head: int,
+                            head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Causal attention of the step's tokens over their requests' pages, 32-bit arithmetic."""
+    if q.dtype != cache.dtype or out.dtype != cache.dtype:
+        raise invalid_argument("attention: q, cache and out must have one element type")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise invalid_argument("attention: q and out must be dense within a row")
+    check(lib().lb_paged_attention_generic(
+        _code(cache.dtype, "cache"), _dev(q, "q"), q.stride(0), _dev(cache, "cache"),
+        _dev(tok_seq, "tok_seq", torch.int32), _dev(positions, "positions", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
+        n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), stream_ptr()),
+        "paged_attention_generic")
+    return out
+
+
+# ------------------------------------------------------------------ sampling
+
+def sample(logits: torch.Tensor, n_rows: int, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           uniform: torch.Tensor, out_ids: torch.Tensor, out_probs: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token id per row; see csrc/sampling.cu for the distribution."""
+    vocab = logits.shape[1]
+    if logits.stride(1) != 1:
+        raise invalid_argument("sample: logits must be dense within a row")
+    if out_probs is not None and (not out_probs.is_contiguous() or out_probs.shape[1] != vocab):
+        raise invalid_argument("sample: out_probs must be contiguous [rows, vocab]")
+    check(lib().lb_sample(_dev(logits, "logits", torch.float32), logits.stride(0), n_rows, vocab,
+                          _dev(temperature, "temperature", torch.float32), _dev(top_k, "top_k", torch.int32),
+                          _dev(top_p, "top_p", torch.float32), _dev(uniform, "uniform", torch.float64),
+                          _dev(out_ids, "out_ids", torch.int32), _opt(out_probs, "out_probs", torch.float32),
+                          stream_ptr()), "sample")
+    return out_ids

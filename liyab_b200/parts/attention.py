@@ -1,0 +1,70 @@
+"""Causal self-attention over the paged cache, with one fused projection of
+queries, keys and values.
+
+Sizes and constants are the spec's: heads, key/value heads, head size, the
+factor on the scores and the window.  The step's keys and values are written to
+the unit's pages first; attention then reads every key, old and new, from the
+pages, so a token's result does not depend on how its sequence was cut into
+steps.  Reference: attention_mixer (src/core/transformer.cpp:3035-3142): fused
+projection and split [q | k | v] (:2657-2673), biases (:3089-3101), store_kv
+(:2875-2890), attention (:2130-2453), output projection (:3139-3140).
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from .. import ops
+from ..cache.pages import KvNeed, StateNeed
+from ..config.spec import AttentionSpec
+from ..status import invalid_model
+from .base import CacheUnit, Runtime, StepContext
+from .linear import Linear
+from .registry import MIXERS
+
+
+@MIXERS.register("attention")
+class CausalSelfAttention:
+    def __init__(self, spec: AttentionSpec, params: Dict[str, torch.Tensor], runtime: Runtime):
+        if spec.n_head % spec.n_kv_head != 0:
+            raise invalid_model(f"attention: n_head {spec.n_head} is not a multiple of n_kv_head {spec.n_kv_head}")
+        self.spec = spec
+        self.runtime = runtime
+        self.q_dim = spec.n_head * spec.head_dim
+        self.kv_dim = spec.n_kv_head * spec.head_dim
+        self.qkv = Linear(params["qkv.weight"], params.get("qkv.bias"), "attention.qkv")
+        self.out = Linear(params["out.weight"], params.get("out.bias"), "attention.out")
+
+    @classmethod
+    def parameters(cls, spec: AttentionSpec) -> Dict[str, Tuple[tuple, str]]:
+        q, kv = spec.n_head * spec.head_dim, spec.n_kv_head * spec.head_dim
+        p = {}
+        for k, v in Linear.parameters(q + 2 * kv, spec.hidden, spec.bias).items():
+            p["qkv." + k] = v
+        for k, v in Linear.parameters(spec.hidden, q, spec.bias).items():
+            p["out." + k] = v
+        return p
+
+    def kv_need(self) -> Optional[KvNeed]:
+        return KvNeed(n_kv_head=self.spec.n_kv_head, head_dim=self.spec.head_dim, window=self.spec.window)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor, unit: CacheUnit) -> None:
+        s, T, dt = self.spec, ctx.n_tokens, self.runtime.dtype
+        ws = ctx.workspace
+        qkv = ws.get("attn.qkv", T, self.q_dim + 2 * self.kv_dim, dt)
+        self.qkv.forward(h, qkv, T)
+        q = qkv[:, :self.q_dim]
+        cache, view = ctx.kv(unit.read)
+        page_size = view.group.page_size
+        if unit.write:
+            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
+            v = qkv[:, self.q_dim + self.kv_dim:]
+            ops.kv_append(k, v, view.slot_mapping, cache, T, s.n_kv_head, s.head_dim, page_size)
+        att = ws.get("attn.out", T, self.q_dim, dt)
+        ops.paged_attention_generic(q, cache, ctx.tok_seq, ctx.positions, view.block_table, att, T, s.n_head,
+                                    s.n_kv_head, s.head_dim, page_size, s.scale, s.window)
+        self.out.forward(att, x, T, residual=x)

@@ -1,0 +1,234 @@
+"""Each kernel alone against a plain float32/float64 PyTorch restatement, at
+sizes other than the engine's."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    assert torch.cuda.is_available(), "these tests need a CUDA device"
+    return torch.device("cuda:0")
+
+
+def _rand(shape, seed, dev, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).to(dev)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width", [48, 200, 1600])
+def test_embed_positions(dev, dtype, width):
+    from liyab_b200 import ops
+    V, P, T = 301, 77, 19
+    table, pos_table = _rand((V, width), 1, dev, dtype), _rand((P, width), 2, dev, dtype)
+    tokens = torch.randint(0, V, (T,), dtype=torch.int32, device=dev)
+    positions = torch.randint(0, P, (T,), dtype=torch.int32, device=dev)
+    out = torch.empty((T, width), dtype=torch.float32, device=dev)
+    ops.embed_positions(tokens, positions, table, pos_table, out, scale=1.0)
+    ref = table.float()[tokens.long()] + pos_table.float()[positions.long()]
+    assert torch.equal(out, ref)
+    ops.embed_positions(tokens, positions, table, None, out, scale=0.5)
+    assert torch.equal(out, table.float()[tokens.long()] * 0.5)
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("width,eps", [(48, 1e-5), (250, 1e-6), (1600, 1e-3), (4100, 1e-5)])
+def test_layernorm(dev, out_dtype, width, eps):
+    from liyab_b200 import ops
+    R = 37
+    x = _rand((R, width), 3, dev) * 3.0 + 5.0          # a mean far from zero shows a one-pass variance
+    w, b = _rand((width,), 4, dev) + 1.0, _rand((width,), 5, dev)
+    out = torch.empty((R, width), dtype=out_dtype, device=dev)
+    ops.layernorm(x, w, b, eps, out, R)
+    ref = torch.from_numpy(plain.layernorm(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy(), eps))
+    tol = 2e-5 if out_dtype == torch.float32 else 2e-2
+    assert (out.double().cpu() - ref).abs().max().item() < tol * ref.abs().max().item()
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32, device=dev)
+    out2 = torch.empty((4, width), dtype=out_dtype, device=dev)
+    ops.layernorm(x, w, b, eps, out2, 4, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtypes", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                    (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M,N,K", [(1, 50, 24), (7, 333, 100), (64, 96, 96), (130, 257, 72), (300, 1000, 513)])
+@pytest.mark.parametrize("act", ["none", "gelu_tanh", "gelu_erf"])
+def test_gemm_ffma(dev, dtypes, M, N, K, act):
+    from liyab_b200 import ops
+    tin, tout = dtypes
+    a, w = _rand((M, K), 6, dev, tin), _rand((N, K), 7, dev, tin, 0.2)
+    bias, res = _rand((N,), 8, dev), _rand((M, N), 9, dev)
+    ref = a.double() @ w.double().t() + bias.double()
+    ref = {"none": lambda v: v, "gelu_tanh": lambda v: torch.from_numpy(plain.gelu_tanh(v.cpu().numpy())).to(dev),
+           "gelu_erf": lambda v: torch.from_numpy(plain.gelu_erf(v.cpu().numpy())).to(dev)}[act](ref)
+    out = torch.empty((M, N), dtype=tout, device=dev)
+    ops.gemm_ffma(a, w, bias, out, M, act)
+    tol = 1e-5 if tout == torch.float32 else 1e-2
+    assert (out.double() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    if tout == torch.float32:
+        out2 = res.clone()
+        ops.gemm_ffma(a, w, bias, out2, M, act, residual=out2)
+        assert (out2.double() - (ref + res.double())).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+        # A row's bits do not depend on how many rows share the launch.
+        one = torch.empty((1, N), dtype=tout, device=dev)
+        ops.gemm_ffma(a[M - 1:M], w, bias, one, 1, act)
+        assert torch.equal(one[0], out[M - 1])
+
+
+def _paged_case(dev, dtype, n_head, n_kv_head, head_dim, page_size, lens, q_lens, seed, boost=None):
+    """Random q/k/v for requests with `lens` tokens, of which the last `q_lens` are this step's.
+    Returns kernel inputs and the float64 reference output."""
+    rng = np.random.default_rng(seed)
+    S = len(lens)
+    n_pages = sum(-(-l // page_size) for l in lens) + 3
+    perm = rng.permutation(n_pages)
+    cache = torch.zeros((n_pages, 2, n_kv_head, page_size, head_dim), dtype=dtype)
+    width = max(-(-l // page_size) for l in lens)
+    table = np.full((S, width), -1, dtype=np.int32)
+    qs, refs, tok_seq, positions = [], [], [], []
+    at = 0
+    for s, (L, Q) in enumerate(zip(lens, q_lens)):
+        k = torch.from_numpy(rng.standard_normal((L, n_kv_head, head_dim))).to(dtype)
+        v = torch.from_numpy(rng.standard_normal((L, n_kv_head, head_dim))).to(dtype)
+        q = torch.from_numpy(rng.standard_normal((Q, n_head, head_dim))).to(dtype)
+        if boost is not None:          # one far key that the query must find among many
+            key_pos, factor = boost
+            if key_pos < L:
+                k[key_pos] = q[-1, ::n_head // n_kv_head] * factor
+        for p in range(-(-L // page_size)):
+            table[s, p] = perm[at]
+            lo, hi = p * page_size, min(L, (p + 1) * page_size)
+            cache[perm[at], 0, :, :hi - lo] = k[lo:hi].permute(1, 0, 2)
+            cache[perm[at], 1, :, :hi - lo] = v[lo:hi].permute(1, 0, 2)
+            at += 1
+        qs.append(q)
+        tok_seq += [s] * Q
+        positions += list(range(L - Q, L))
+        refs.append((q.double(), k.double(), v.double(), L - Q))
+    q_all = torch.cat(qs).reshape(-1, n_head * head_dim)
+    return (q_all.to(dev), cache.to(dev), torch.tensor(tok_seq, dtype=torch.int32, device=dev),
+            torch.tensor(positions, dtype=torch.int32, device=dev), torch.from_numpy(table).to(dev), refs)
+
+
+def _attention_reference(refs, n_head, n_kv_head, scale, window):
+    outs = []
+    group = n_head // n_kv_head
+    for q, k, v, first in refs:
+        Q, L = q.shape[0], k.shape[0]
+        o = torch.zeros(Q, n_head, q.shape[2], dtype=torch.float64)
+        for h in range(n_head):
+            s = (q[:, h] @ k[:, h // group].t()) * scale
+            pos = torch.arange(first, first + Q)[:, None]
+            j = torch.arange(L)[None, :]
+            mask = j <= pos
+            if window > 0:
+                mask &= j > pos - window
+            s = s.masked_fill(~mask, float("-inf"))
+            o[:, h] = torch.softmax(s, dim=-1) @ v[:, h // group]
+        outs.append(o.reshape(Q, -1))
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [
+    (4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0), (5, 1, 64, 64, 0), (2, 2, 128, 16, 0),
+    (7, 7, 80, 16, 0), (4, 2, 256, 16, 0), (4, 4, 32, 16, 40), (2, 1, 64, 32, 7)])
+def test_paged_attention_generic(dev, dtype, n_head, n_kv_head, head_dim, page_size, window):
+    from liyab_b200 import ops
+    lens, q_lens = [1, 37, 130, 64, 300], [1, 37, 2, 1, 45]
+    scale = 0.37 / math.sqrt(head_dim)
+    q, cache, tok_seq, positions, table, refs = _paged_case(dev, dtype, n_head, n_kv_head, head_dim, page_size, lens,
+                                                            q_lens, seed=head_dim + n_head)
+    out = torch.empty_like(q)
+    ops.paged_attention_generic(q, cache, tok_seq, positions, table, out, q.shape[0], n_head, n_kv_head, head_dim,
+                                page_size, scale, window)
+    ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    assert (out.double().cpu() - ref).abs().max().item() < tol
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_a_far_key(dev, dtype):
+    """One key far back, scaled so that its score stands out among hundreds: a kernel that drops a page,
+    a tile or the first key shows it."""
+    from liyab_b200 import ops
+    n_head, n_kv_head, head_dim, page_size = 4, 2, 64, 16
+    for key_pos in (0, 15, 16, 271, 511):
+        q, cache, tok_seq, positions, table, refs = _paged_case(
+            dev, dtype, n_head, n_kv_head, head_dim, page_size, [512], [1], seed=key_pos, boost=(key_pos, 4.0))
+        out = torch.empty_like(q)
+        ops.paged_attention_generic(q, cache, tok_seq, positions, table, out, 1, n_head, n_kv_head, head_dim,
+                                    page_size, 1.0 / math.sqrt(head_dim), 0)
+        ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
+        tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+        assert (out.double().cpu() - ref).abs().max().item() < tol, f"far key at {key_pos}"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_kv_append(dev, dtype):
+    from liyab_b200 import ops
+    n_kv_head, head_dim, page_size, n_pages, T = 3, 48, 16, 9, 40
+    qkv = _rand((T, 5 * n_kv_head * head_dim), 11, dev, dtype)
+    k = qkv[:, n_kv_head * head_dim: 2 * n_kv_head * head_dim]
+    v = qkv[:, 3 * n_kv_head * head_dim: 4 * n_kv_head * head_dim]
+    slots = torch.randperm(n_pages * page_size)[:T].to(torch.int32)
+    slots[5] = -1
+    cache = torch.zeros((n_pages, 2, n_kv_head, page_size, head_dim), dtype=dtype, device=dev)
+    ops.kv_append(k, v, slots.to(dev), cache, T, n_kv_head, head_dim, page_size)
+    ref = torch.zeros_like(cache)
+    for t in range(T):
+        s = int(slots[t])
+        if s < 0:
+            continue
+        ref[s // page_size, 0, :, s % page_size] = k[t].reshape(n_kv_head, head_dim)
+        ref[s // page_size, 1, :, s % page_size] = v[t].reshape(n_kv_head, head_dim)
+    assert torch.equal(cache, ref)
+
+
+@pytest.mark.parametrize("vocab", [50, 1000, 50257])
+def test_sampling_matches_plain(dev, vocab):
+    from liyab_b200 import ops
+    rng = np.random.default_rng(vocab)
+    cases = [(0.0, 0, 1.0), (0.8, 40, 0.95), (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.5), (1.0, 1000000, 0.9),
+             (0.5, 3, 0.2), (2.0, 17, 0.999)]
+    R = len(cases)
+    logits = rng.standard_normal((R, vocab)).astype(np.float32) * 2.0
+    logits[1, 7] = logits[1].max() + 0.5
+    logits[3, :] = np.round(logits[3, :])          # many exact ties, also at the top-k edge
+    u = rng.random(R)
+    out_ids = torch.empty(R, dtype=torch.int32, device=dev)
+    probs = torch.empty((R, vocab), dtype=torch.float32, device=dev)
+    ops.sample(torch.from_numpy(logits).to(dev), R, torch.tensor([c[0] for c in cases], dtype=torch.float32, device=dev),
+               torch.tensor([c[1] for c in cases], dtype=torch.int32, device=dev),
+               torch.tensor([c[2] for c in cases], dtype=torch.float32, device=dev),
+               torch.from_numpy(u).to(dev), out_ids, probs)
+    got_ids, got_probs = out_ids.cpu().numpy(), probs.cpu().numpy()
+    for r, (t, k, p) in enumerate(cases):
+        ref = plain.sampler_probabilities(logits[r], t, k, p)
+        assert (ref > 0).sum() == (got_probs[r] > 0).sum(), f"case {r}: kept sets differ in size"
+        assert np.array_equal(ref > 0, got_probs[r] > 0), f"case {r}: kept sets differ"
+        assert np.abs(ref - got_probs[r]).max() < 2e-6, f"case {r}"
+        if t <= 0:
+            assert got_ids[r] == int(np.argmax(logits[r]))
+        else:
+            assert got_ids[r] == plain.sampler_draw(got_probs[r], float(u[r])), f"case {r}"
+
+
+def test_greedy_takes_the_first_maximum(dev):
+    from liyab_b200 import ops
+    logits = torch.zeros((2, 3000), dtype=torch.float32, device=dev)
+    logits[0, [2999, 1234, 77]] = 5.0
+    logits[1, :] = -1.0
+    out = torch.empty(2, dtype=torch.int32, device=dev)
+    z = torch.zeros(2, device=dev)
+    ops.sample(logits, 2, z, torch.zeros(2, dtype=torch.int32, device=dev), z + 1, z.double(), out)
+    assert out.tolist() == [77, 0]

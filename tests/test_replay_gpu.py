@@ -1,0 +1,135 @@
+"""The engine against the plain implementation under every way of cutting the
+work, in 32-bit and in bfloat16, on the two tiny configurations."""
+from __future__ import annotations
+
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_gpt2 as plain
+import trace_tools as tt
+from tiny_models import CONFIGS, random_tokens, write_model
+
+pytestmark = pytest.mark.gpu
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Largest |engine - plain| allowed on a logit, as a fraction of the largest |logit| of the sequence.
+# 32-bit: sums of a few hundred products in float32.  bfloat16: activations rounded to 8 bits of mantissa
+# between the parts, weights identical in both (the model file stores bfloat16).
+REL_TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+def request_set(name: str):
+    raw, seed = CONFIGS[name]
+    P, V = raw["n_positions"], raw["vocab_size"]
+    lengths = [P, 70, 33, 13, 7, 2, 1, 45]
+    return {f"r{i}": random_tokens(100 * seed + i, n, V) for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = str(tmp_path_factory.mktemp("models"))
+    return {(n, d): write_model(base, n, d) for n in ("A", "B") for d in ("float32", "bfloat16")}
+
+
+@pytest.fixture(scope="module")
+def oracle(folders):
+    out = {}
+    for (name, dtype), path in folders.items():
+        m = plain.load_plain_model(path)
+        out[(name, dtype)] = {r: plain.forward_logits(m, toks) for r, toks in request_set(name).items()}
+    return out
+
+
+def make_engine(path, dtype, max_tokens, page_size=16):
+    from liyab_b200.engine.replay import build_replayer
+    _, cache, stepper = build_replayer(path, dtype, max_tokens, page_size=page_size)
+    return cache, stepper
+
+
+def check_against_oracle(got, want, dtype):
+    worst = 0.0
+    for (r, pos), row in got.items():
+        ref = want[r][pos]
+        scale = np.abs(want[r]).max()
+        err = np.abs(row.astype(np.float64) - ref).max() / scale
+        worst = max(worst, err)
+        assert err <= REL_TOL[dtype], f"request {r} position {pos}: relative error {err:.3e} > {REL_TOL[dtype]:.1e}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_every_cutting_matches_plain(name, dtype, folders, oracle):
+    reqs = request_set(name)
+    want = oracle[(name, dtype)]
+    n_rows = sum(len(t) for t in reqs.values())
+    cache, stepper = make_engine(folders[(name, dtype)], dtype, max_tokens=4 * 256)
+    traces = {"whole": tt.whole(reqs), "tail": tt.tail_one_by_one(reqs, 32), "portions": tt.changing_portions(reqs)}
+    results = {}
+    for kind, steps in traces.items():
+        results[kind] = tt.collect(stepper, cache, steps)
+        assert len(results[kind]) == n_rows
+        check_against_oracle(results[kind], want, dtype)
+    # Mixed, with so few pages that they are used again: a pool for the trace's own peak only.
+    steps = tt.mixed(reqs, max_live=4, seed=3)
+    assert max(len(e) for e, _ in steps) >= 3, "the mixed trace must batch several requests"
+    peak = tt.peak_tokens(steps, 64)
+    cache2, stepper2 = make_engine(folders[(name, dtype)], dtype, max_tokens=peak)
+    results["mixed"] = tt.collect(stepper2, cache2, steps)
+    assert len(results["mixed"]) == n_rows
+    check_against_oracle(results["mixed"], want, dtype)
+    total_pages = sum(-(-len(t) // 16) for t in reqs.values())
+    assert cache2.groups[0].pool.num_pages < total_pages, "pages must have been used again"
+    if dtype == "float32":
+        # The engine's own invariant: a position's logits are the same bits however the tokens were cut.
+        for kind in ("tail", "portions", "mixed"):
+            for key, row in results["whole"].items():
+                assert np.array_equal(row, results[kind][key]), f"{kind}: {key} differs from the whole run"
+
+
+@pytest.mark.parametrize("page_size", [16, 64])
+def test_page_size_does_not_matter(page_size, folders, oracle):
+    reqs = request_set("B")
+    cache, stepper = make_engine(folders[("B", "float32")], "float32", max_tokens=1024, page_size=page_size)
+    got = tt.collect(stepper, cache, tt.changing_portions(reqs, sizes=(63, 2, 1, 64, 17)))
+    check_against_oracle(got, oracle[("B", "float32")], "float32")
+
+
+def test_first_tokens_and_long_decoding(folders, oracle):
+    """The first tokens of a sequence one by one, then decoding to the model's last position."""
+    reqs = {"r0": request_set("A")["r0"]}
+    cache, stepper = make_engine(folders[("A", "float32")], "float32", max_tokens=128)
+    got = tt.collect(stepper, cache, tt.tail_one_by_one(reqs, tail=128))
+    assert len(got) == 128
+    check_against_oracle(got, oracle[("A", "float32")], "float32")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_trace_run_program(dtype, folders, oracle, tmp_path):
+    """bin/trace_run as a user calls it: JSON lines in, <step>.f32 out, `done <step>` after each."""
+    reqs = {k: v for k, v in request_set("B").items() if k in ("r1", "r2", "r3", "r6")}
+    steps = tt.mixed(reqs, max_live=4, seed=5)
+    out_dir = str(tmp_path / "out")
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[("B", dtype)],
+                           "--dtype", dtype, "--out", out_dir, "--max-tokens", str(tt.peak_tokens(steps))],
+                          input=tt.to_jsonl(steps), capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {i}" for i in range(len(steps))]
+    V = CONFIGS["B"][0]["vocab_size"]
+    held = {}
+    for i, (entries, end) in enumerate(steps):
+        data = np.fromfile(os.path.join(out_dir, f"{i}.f32"), dtype="<f4").reshape(-1, V)
+        row = 0
+        for r, toks, want in entries:
+            base = held.get(r, 0)
+            for w in want:
+                ref = oracle[("B", dtype)][r][base + w]
+                assert np.abs(data[row] - ref).max() <= REL_TOL[dtype] * np.abs(oracle[("B", dtype)][r]).max()
+                row += 1
+            held[r] = base + len(toks)
+        assert row == data.shape[0]
