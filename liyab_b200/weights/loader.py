@@ -66,7 +66,9 @@ def load_parameters(model_dir: str, config: ArchitectureConfig, dtype: str, devi
                 wrong.append(f"tensor '{full}' has shape {list(entry.shape)}, expected {list(spec.shape)}")
             elif not entry.dtype.is_floating_point and spec.kind != "index":
                 wrong.append(f"tensor '{full}' has dtype {entry.dtype}, expected a floating type")
-        ignored = [re.compile("^" + re.escape(prefix) + p + "$") for p in config.ignored_tensors()]
+        # A tensor that carries no weights may sit under the file's prefix or outside it
+        # (a stored copy of a tied head usually does not carry the body's prefix).
+        ignored = [re.compile("^(?:" + re.escape(prefix) + ")?" + p + "$") for p in config.ignored_tensors()]
         unexpected = sorted(n for n in names - used if not any(p.match(n) for p in ignored))
         if missing or wrong or unexpected:
             parts = []
