@@ -1,6 +1,20 @@
 """liyab_b200: a single-GPU inference engine for NVIDIA B200 in the manner of
-andrei-borcea/liyab, built around one step function over a paged cache."""
+andrei-borcea/liyab, built around one step function over a paged cache.
+
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    engine = Engine(EngineConfig(model="/path/to/folder", dtype="bfloat16"))
+    result = engine.generate_tokens([464, 3290], SamplingParams(temperature=0.0, max_tokens=16))
+"""
 from .status import ErrorCode, LiyabError
+from .sampling.params import SamplingParams
 
 __version__ = "0.1.0"
-__all__ = ["ErrorCode", "LiyabError", "__version__"]
+__all__ = ["ErrorCode", "LiyabError", "SamplingParams", "Engine", "EngineConfig", "generate", "__version__"]
+
+
+def __getattr__(name):
+    # The engine pulls in the CUDA side; config, weights, cache and scheduler import without it.
+    if name in ("Engine", "EngineConfig", "generate", "GenerationResult", "GenerationStats"):
+        from .engine import engine as _engine
+        return getattr(_engine, name)
+    raise AttributeError(name)

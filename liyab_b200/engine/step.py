@@ -21,6 +21,7 @@ from typing import Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache.pages import CacheManager, OutOfPages
 from ..models.decoder import DecoderModel
 from ..parts.base import GroupView, StepContext, Workspace
@@ -41,13 +42,32 @@ class StepOutput:
     rows: List[Tuple[Hashable, int]] = field(default_factory=list)   # (request, index among its tokens) per row
 
 
-class Stepper:
-    """Owns the step's device-side layout buffers and the workspace."""
+class _DecodeGraph:
+    """A captured decode step for a fixed number of requests: its layout buffer, graph and logits view."""
 
-    def __init__(self, model: DecoderModel, cache: CacheManager, max_step_tokens: int = 0):
+    def __init__(self, dev: torch.Tensor, generation: int):
+        self.dev = dev
+        self.generation = generation
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+
+class Stepper:
+    """Owns the step's device-side layout buffers, the workspace and the captured decode graphs.
+
+    A step whose entries all bring one token and want its logits (a decode step)
+    always has the same launches for a given number of requests; with
+    `cuda_graphs` it is captured once per that number and replayed afterwards, its
+    layout arrays (tokens, positions, block tables, slots) rewritten in place
+    before each replay.  The kernels and the cache are the same either way.
+    """
+
+    def __init__(self, model: DecoderModel, cache: CacheManager, max_step_tokens: int = 0, cuda_graphs: bool = False,
+                 max_positions: int = 0):
         self.model = model
         self.cache = cache
         self.device = model.runtime.device
+        self.max_positions = min(max_positions or model.max_positions, model.max_positions)
         self.workspace = Workspace(self.device)
         if max_step_tokens:
             self.workspace.reserve_rows(max_step_tokens)
@@ -57,7 +77,11 @@ class Stepper:
         self._copied: List[Optional[torch.cuda.Event]] = [None, None]
         self._dev: Optional[torch.Tensor] = None
         self._turn = 0
+        self.cuda_graphs = cuda_graphs
+        self._graphs: dict = {}
+        self.graph_launches: dict = {}       # kernels in the captured step, by number of requests
         self.steps = 0
+        self.graph_steps = 0
         self.tokens_run = 0
 
     # -- validation (no side effects) -------------------------------------------
@@ -67,7 +91,7 @@ class Stepper:
             raise invalid_argument("a step needs at least one entry")
         seen = set()
         vocab = self.model.spec.vocab_size
-        limit = self.model.max_positions
+        limit = self.max_positions
         for e in entries:
             if e.request in seen:
                 raise invalid_argument(f"request {e.request!r} appears twice in one step")
@@ -98,15 +122,52 @@ class Stepper:
                              f"pages {cache.free_pages()}")
         for e in entries:
             cache.reserve(e.request, len(e.tokens))
-        ctx, rows = self._layout(entries)
-        logits = self.model.forward(ctx)
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            logits, rows = self._graph_step(entries)
+        else:
+            ctx, rows = self._layout(entries)
+            logits = self.model.forward(ctx)
         for e in entries:
             cache.commit(e.request, len(e.tokens))
         self.steps += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += sum(wants.values())
         return StepOutput(logits=logits, rows=rows)
 
-    def _layout(self, entries: Sequence[StepEntry]) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+    def _graph_step(self, entries: Sequence[StepEntry]):
+        S = len(entries)
+        g = self._graphs.get(S)
+        if g is None or g.generation != self.workspace.generation:
+            # First decode step of this size (or buffers moved since): run it eagerly on a
+            # buffer of its own so every scratch buffer exists, then capture the same launches.
+            widths = [(self.max_positions + grp.page_size - 1) // grp.page_size for grp in self.cache.groups]
+            total = self._layout_size(S, S, S, widths)
+            g = _DecodeGraph(torch.empty(total, dtype=torch.int32, device=self.device), -1)
+            ctx, rows = self._layout(entries, static=g)
+            self.model.forward(ctx)
+            torch.cuda.current_stream().synchronize()
+            g.generation = self.workspace.generation
+            graph = torch.cuda.CUDAGraph()
+            before = ops.LAUNCHES
+            with torch.cuda.graph(graph):
+                g.logits = self.model.forward(ctx)
+            self.graph_launches[S] = ops.LAUNCHES - before
+            if g.generation != self.workspace.generation:
+                raise RuntimeError("a scratch buffer was created while a decode step was being captured")
+            g.graph = graph
+            self._graphs[S] = g
+        else:
+            _, rows = self._layout(entries, static=g)
+        g.graph.replay()
+        self.graph_steps += 1
+        return g.logits, rows
+
+    @staticmethod
+    def _layout_size(S: int, T: int, R: int, widths: Sequence[int]) -> int:
+        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths]
+        return sum((n + 3) // 4 * 4 for n in sizes)
+
+    def _layout(self, entries: Sequence[StepEntry], static: Optional[_DecodeGraph] = None
+                ) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
         cache = self.cache
         S = len(entries)
         q_len = np.array([len(e.tokens) for e in entries], dtype=np.int64)
@@ -125,9 +186,13 @@ class Stepper:
                 rows.append((e.request, int(w)))
                 logit_rows.append(int(q_start[i]) + int(w))
         state_slots = np.array([cache.state_slot(r) for r in requests], dtype=np.int32)
-        tables = [cache.block_table(g, requests) for g in range(len(cache.groups))]
+        G = len(cache.groups)
+        fixed = None
+        if static is not None:      # widths that never change, so the captured launches stay valid
+            fixed = [(self.max_positions + grp.page_size - 1) // grp.page_size for grp in cache.groups]
+        tables = [cache.block_table(g, requests, width=fixed[g] if fixed else None) for g in range(G)]
         slots = [np.concatenate([cache.slot_mapping(g, e.request, int(n_past[i]), int(q_len[i]))
-                                 for i, e in enumerate(entries)]) for g in range(len(cache.groups))]
+                                 for i, e in enumerate(entries)]) for g in range(G)]
         # One staging buffer, one copy to the device; views are carved out of it.
         pieces = [tokens, positions, tok_seq, q_start.astype(np.int32), n_past.astype(np.int32), state_slots,
                   np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
@@ -136,8 +201,13 @@ class Stepper:
             offsets.append(total)
             total += (p.size + 3) // 4 * 4           # keep every view 16-byte aligned
         turn = self._turn = 1 - self._turn
-        if self._dev is None or self._dev.numel() < total:
-            self._dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
+        if static is not None:
+            dev = static.dev
+            assert dev.numel() == total
+        else:
+            if self._dev is None or self._dev.numel() < total:
+                self._dev = torch.empty(max(total, 4096), dtype=torch.int32, device=self.device)
+            dev = self._dev
         if self._host[turn] is None or self._host[turn].numel() < total:
             self._host[turn] = torch.empty(max(total, 4096), dtype=torch.int32).pin_memory()
             self._copied[turn] = torch.cuda.Event()
@@ -146,13 +216,12 @@ class Stepper:
         host = self._host[turn].numpy()
         for p, o in zip(pieces, offsets):
             host[o:o + p.size] = p
-        self._dev[:total].copy_(self._host[turn][:total], non_blocking=True)
+        dev[:total].copy_(self._host[turn][:total], non_blocking=True)
         self._copied[turn].record()
 
         def view(i: int) -> torch.Tensor:
-            return self._dev[offsets[i]:offsets[i] + pieces[i].size]
+            return dev[offsets[i]:offsets[i] + pieces[i].size]
 
-        G = len(cache.groups)
         groups = [GroupView(group=cache.groups[g], block_table=view(7 + g).view(S, tables[g].shape[1]),
                             slot_mapping=view(7 + G + g)) for g in range(G)]
         ctx = StepContext(

@@ -33,6 +33,7 @@ _SIGNATURES = {
 }
 
 _lib = None
+LAUNCHES = 0        # kernel launches issued through this module (a captured graph replays its own count)
 
 
 def lib():
@@ -59,6 +60,8 @@ def declare(name: str, argtypes) -> None:
 
 
 def check(status: int, what: str) -> None:
+    global LAUNCHES
+    LAUNCHES += 1
     if status != 0:
         msg = lib().lb_last_error().decode("utf-8", "replace")
         try:

@@ -47,21 +47,21 @@ class Workspace:
 
     def __init__(self, device: torch.device):
         self.device = device
-        self._buffers: Dict[str, torch.Tensor] = {}
+        self._buffers: Dict[tuple, torch.Tensor] = {}
         self.min_rows = 0
-        self.frozen = False
+        self.generation = 0          # grows whenever a buffer is created or moved (captured graphs check it)
 
     def reserve_rows(self, rows: int) -> None:
         self.min_rows = max(self.min_rows, rows)
 
     def get(self, name: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
-        buf = self._buffers.get(name)
-        if buf is None or buf.shape[0] < rows or buf.shape[1] != cols or buf.dtype != dtype:
-            if self.frozen and buf is not None:
-                raise RuntimeError(f"workspace buffer {name!r} would move while a captured graph uses it")
+        key = (name, cols, dtype)        # layers of different sizes get buffers of their own
+        buf = self._buffers.get(key)
+        if buf is None or buf.shape[0] < rows:
             cap = max(rows, self.min_rows, 1)
             buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
-            self._buffers[name] = buf
+            self._buffers[key] = buf
+            self.generation += 1
         return buf
 
     def bytes(self) -> int:

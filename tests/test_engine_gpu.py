@@ -1,0 +1,138 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import plain_gpt2 as plain
+from tiny_models import CONFIGS, random_tokens, write_model
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = str(tmp_path_factory.mktemp("engine_models"))
+    return {(n, d): write_model(base, n, d) for n in ("A", "B") for d in ("float32", "bfloat16")}
+
+
+def plain_sampled(model, prompt, params, stream, n_new):
+    """The plain sampler on the plain model's logits, with the engine's documented draws."""
+    tokens, out = list(prompt), []
+    for i in range(n_new):
+        logits = plain.forward_logits(model, tokens)[-1].astype(np.float32)
+        probs = plain.sampler_probabilities(logits, params.temperature, params.top_k, params.top_p)
+        nxt = int(np.argmax(probs)) if params.temperature <= 0 else plain.sampler_draw(probs, plain.uniform_draw(params.seed, stream, i))
+        out.append(nxt)
+        tokens.append(nxt)
+    return out
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_greedy_generation_config_a(folders, graphs):
+    """BASELINE workload A: two prompts of 7 and 13 ids, 16 greedy steps, 32-bit."""
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = folders[("A", "float32")]
+    prompts = [random_tokens(1, 7, 512), random_tokens(2, 13, 512)]
+    engine = Engine(EngineConfig(model=folder, dtype="float32", max_requests=4, max_batched_tokens=64, num_pages=16,
+                                 cuda_graphs=graphs))
+    got = engine.generate_batch(prompts, SamplingParams(temperature=0.0, max_tokens=16))
+    oracle = plain.load_plain_model(folder)
+    for p, r in zip(prompts, got):
+        assert r.tokens == plain.generate_greedy(oracle, p, 16) and r.finish_reason == "length"
+        assert r.stats.prompt_tokens == len(p) and r.stats.generated_tokens == 16
+    assert (engine.stepper.graph_steps > 0) == graphs
+    assert all(v == 0 for v in engine.cache.pages_in_use().values())
+
+
+def test_sampled_generation_config_b(folders):
+    """BASELINE workload B: prompts of 1, 5, 33 and 70 ids, prefilled in portions of 16 beside decoding,
+    24 steps at temperature 0.8 with sampler seed 7."""
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = folders[("B", "float32")]
+    prompts = [random_tokens(10 + i, n, 1000) for i, n in enumerate((1, 5, 33, 70))]
+    params = SamplingParams(temperature=0.8, top_k=40, top_p=0.95, seed=7, max_tokens=24)
+    engine = Engine(EngineConfig(model=folder, dtype="float32", max_requests=4, max_batched_tokens=16, num_pages=64))
+    got = engine.generate_batch(prompts, params)
+    oracle = plain.load_plain_model(folder)
+    for stream, (p, r) in enumerate(zip(prompts, got)):
+        assert r.tokens == plain_sampled(oracle, p, params, stream, 24)
+    assert engine.scheduler.stats.prefill_tokens == 1 + 5 + 33 + 70
+    # the same requests one at a time give the same tokens: a draw belongs to (seed, stream, index), not to a batch
+    engine2 = Engine(EngineConfig(model=folder, dtype="float32", max_requests=1, max_batched_tokens=2048, num_pages=64))
+    for stream, (p, r) in enumerate(zip(prompts, got)):
+        alone = engine2.generate_tokens(p, params)
+        assert alone.tokens == r.tokens
+
+
+def test_preemption_does_not_change_the_tokens(folders):
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = folders[("A", "float32")]
+    prompts = [random_tokens(20 + i, n, 512) for i, n in enumerate((30, 25, 20))]
+    params = SamplingParams(temperature=0.7, top_k=0, top_p=1.0, seed=3, max_tokens=40)
+    roomy = Engine(EngineConfig(model=folder, dtype="float32", max_requests=4, max_batched_tokens=32, num_pages=64))
+    want = [r.tokens for r in roomy.generate_batch(prompts, params)]
+    tight = Engine(EngineConfig(model=folder, dtype="float32", max_requests=4, max_batched_tokens=32, num_pages=9))
+    got = tight.generate_batch(prompts, params)
+    assert tight.scheduler.stats.preemptions >= 1
+    assert [r.tokens for r in got] == want
+    assert all(v == 0 for v in tight.cache.pages_in_use().values())
+
+
+def test_bfloat16_generation_stays_close(folders):
+    """In bfloat16 a near-tie may flip a token, so the check is on the logits the engine's own
+    tokens lead to: at every step the chosen token's plain logit is within rounding of the best."""
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = folders[("B", "bfloat16")]
+    prompt = random_tokens(5, 40, 1000)
+    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32))
+    out = engine.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=20)).tokens
+    logits = plain.forward_logits(plain.load_plain_model(folder), prompt + out)
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert row.max() - row[tok] <= 2.5e-2 * np.abs(row).max()
+
+
+def test_callback_stop_and_eos(folders, tmp_path):
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = folders[("A", "float32")]
+    engine = Engine(EngineConfig(model=folder, dtype="float32", max_requests=2, num_pages=16))
+    prompt = random_tokens(1, 7, 512)
+    ref = engine.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=10)).tokens
+    seen = []
+    r = engine.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=10),
+                               callback=lambda t: seen.append(t) or len(seen) < 3)
+    assert r.tokens == ref[:3] and r.finish_reason == "stopped" and seen == ref[:3]
+    # a model whose eos is the token it generates third stops there unless told to ignore it
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    cfg["eos_token_id"] = ref[2]
+    eos_folder = tmp_path / "eos"
+    eos_folder.mkdir()
+    (eos_folder / "config.json").write_text(json.dumps(cfg))
+    os.symlink(os.path.join(folder, "model.safetensors"), eos_folder / "model.safetensors")
+    e2 = Engine(EngineConfig(model=str(eos_folder), dtype="float32", max_requests=2, num_pages=16))
+    first = ref.index(ref[2])
+    r = e2.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=10))
+    assert r.tokens == ref[:first + 1] and r.finish_reason == "eos"
+    r = e2.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))
+    assert r.tokens == ref
+
+
+def test_command_line(folders):
+    folder = folders[("A", "float32")]
+    prompt = random_tokens(1, 7, 512)
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "liyab-cli"), "-m", folder, "-p", ",".join(map(str, prompt)),
+           "-n", "6", "--temp", "0", "--dtype", "float32", "--num-pages", "16", "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
+    assert "load_ms" in lines[0] and lines[1]["generated_tokens"] == 6
+    assert lines[1]["tokens"] == plain.generate_greedy(plain.load_plain_model(folder), prompt, 6)
+    proc = subprocess.run(cmd[:6] + ["--tokenize"], capture_output=True, text=True, timeout=600)
+    assert proc.stdout.split() == [str(t) for t in prompt]
