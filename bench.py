@@ -108,7 +108,7 @@ def decode_run(model_dir, dtype, batch, steps, warmup, count_launches=False):
     from liyab_b200.sampling.params import SamplingParams
     from liyab_b200.sampling.sampler import DeviceSampler
 
-    model, cache, stepper = build_replayer(model_dir, dtype, max_tokens=batch * 1024, page_size=16)
+    model, cache, stepper = build_replayer(model_dir, dtype, max_tokens=batch * 1024, page_size=16, max_requests=batch)
     stepper.cuda_graphs = True
     stepper.workspace.reserve_rows(max(PREFILL_TOKENS, batch))
     P, V = model.max_positions, model.spec.vocab_size
