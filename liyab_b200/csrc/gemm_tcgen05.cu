@@ -1,0 +1,425 @@
+// out[M, N] = epilogue(A[M, K] . W[N, K]^T) for bfloat16 operands on the fifth
+// generation tensor cores: operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), products issued by one thread with
+// tcgen05.mma into an accumulator in tensor memory, read back with tcgen05.ld
+// for the epilogue (bias, activation, residual sum, in the reference's order:
+// src/core/transformer.cpp:111-118, 4903-4912, 5526-5532).
+//
+// The product is computed transposed: the weight tile [128 output features x 64]
+// is the instruction's M operand and the activation tile [BN tokens x 64] its N
+// operand, so a decode step with a handful of tokens still fills the 128 rows of
+// the instruction with weights, and every weight byte crosses HBM once.  In
+// tensor memory lane i holds feature n0 + i and column j holds token m0 + j; the
+// 32 threads of an epilogue warp therefore write 32 consecutive features of one
+// token with each store.
+//
+// One CTA computes one [128 x BN] tile.  Warp 0 issues the TMA loads, warp 1
+// allocates tensor memory and issues the MMAs, warps 2..5 run the epilogue.  A
+// ring of shared-memory stages is handed back and forth through mbarriers
+// (full: TMA bytes landed; empty: tcgen05.commit after the MMAs that read the
+// stage).  Every wait is bounded: after about two seconds without progress the
+// kernel records where it gave up in a device status word, skips the rest, waits
+// for its own copies, frees its tensor memory and returns.
+//
+// Sizes: any M and N (TMA fills out-of-range rows with zeros, stores are
+// masked); K a multiple of 8 and both row strides multiples of 8 elements
+// (16-byte TMA rule); everything else is refused by the host function.
+#include "api.h"
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+namespace {
+
+constexpr int kBlockK = 64;          // one 128-byte swizzle atom of bfloat16
+constexpr int kFeatTile = 128;       // UMMA M
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+
+__device__ int g_status = 0;         // 0 ok; else (site << 8) | detail of the first bounded wait that ran out
+
+// ------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Waits for the barrier's phase; false when the time limit ran out, or when another role already gave up
+// (abort_flag, where given).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = global_ns();
+    for (;;) {
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (abort_flag != nullptr && *abort_flag != 0) return false;
+        if (global_ns() - t0 > kWaitLimitNs) return false;
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile laid out by TMA with the
+// 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+// Fields (PTX "matrix descriptor"): start address >> 4 in bits [0,14), leading
+// byte offset >> 4 in [16,30) (unused for swizzled K-major, set to 1), stride
+// byte offset >> 4 in [32,46) (1024 >> 4), version 1 in [46,48), swizzle mode 2
+// (128 bytes) in [61,64).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: D format F32 (1) in [4,6), A and B format
+// BF16 (1) in [7,10) and [10,13), both operands K-major (bits 15, 16 = 0),
+// N >> 3 in [17,23), M >> 4 in [24,29).
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// ------------------------------------------------------------------ the kernel
+
+template <int BN, int STAGES>
+struct SharedStorage {
+    alignas(1024) __nv_bfloat16 w[STAGES][kFeatTile * kBlockK];   // 16 KB each
+    alignas(1024) __nv_bfloat16 a[STAGES][BN * kBlockK];
+    alignas(8) uint64_t full[STAGES];
+    alignas(8) uint64_t empty[STAGES];
+    alignas(8) uint64_t acc_ready;
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int BN, int STAGES, typename TO>
+__global__ void __launch_bounds__(kThreads)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+                    const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M,
+                    int N, int K, int act) {
+    extern __shared__ uint8_t smem_raw[];
+    using Storage = SharedStorage<BN, STAGES>;
+    Storage& s = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
+    constexpr uint32_t kStageBytes = (kFeatTile + BN) * kBlockK * sizeof(__nv_bfloat16);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * kFeatTile;     // first output feature of the tile
+    const int m0 = blockIdx.y * BN;            // first token of the tile
+    const int n_kb = (K + kBlockK - 1) / kBlockK;
+    volatile int* abort_flag = &s.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) {
+            mbar_init(&s.full[i], 1);
+            mbar_init(&s.empty[i], 1);
+        }
+        mbar_init(&s.acc_ready, 1);
+        s.abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        tmem_alloc(&s.tmem_base, kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = s.tmem_base;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < n_kb; ++kb) {
+                const int st = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag)) {
+                    atomicCAS(&g_status, 0, (1 << 8) | st);
+                    s.abort_flag = 1;
+                    break;
+                }
+                mbar_expect_tx(&s.full[st], kStageBytes);
+                tma_load_2d(s.w[st], &map_w, &s.full[st], kb * kBlockK, n0);
+                tma_load_2d(s.a[st], &map_a, &s.full[st], kb * kBlockK, m0);
+                issued = kb + 1;
+            }
+            if (s.abort_flag != 0 && issued > 0) {
+                // Leave no copy in flight: the last stage issued signals its full barrier when its bytes landed.
+                const int kb = issued - 1;
+                mbar_wait(&s.full[kb % STAGES], (kb / STAGES) & 1, nullptr);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(kFeatTile, BN);
+            bool ok = true;
+            for (int kb = 0; kb < n_kb && ok; ++kb) {
+                const int st = kb % STAGES;
+                const uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&s.full[st], ph, abort_flag)) {
+                    atomicCAS(&g_status, 0, (2 << 8) | st);
+                    s.abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t w_addr = smem_u32(s.w[st]), a_addr = smem_u32(s.a[st]);
+#pragma unroll
+                for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                    const uint32_t off = k * kUmmaK * sizeof(__nv_bfloat16);
+                    umma_bf16(tmem_base, umma_desc(w_addr + off), umma_desc(a_addr + off), idesc, (kb | k) != 0 ? 1u : 0u);
+                }
+                umma_commit(&s.empty[st]);      // the stage is free once these MMAs have read it
+            }
+            if (ok) umma_commit(&s.acc_ready);  // the accumulator is complete once every MMA retired
+        }
+    } else {
+        // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
+        const int quarter = warp & 3;
+        const int f = n0 + quarter * 32 + lane;
+        if (!mbar_wait(&s.acc_ready, 0, abort_flag)) {
+            if (lane == 0) atomicCAS(&g_status, 0, (3 << 8) | quarter);
+            s.abort_flag = 1;
+        } else {
+            tc_fence_after();
+            const float b = (bias != nullptr && f < N) ? bias[f] : 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (m0 + c >= M) break;          // uniform across the warp
+                uint32_t v[16];
+                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (f < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = m0 + c + j;
+                        if (t < M) {
+                            float x = __uint_as_float(v[j]) + b;
+                            x = lb_activate(x, act);
+                            if (residual != nullptr) x += residual[(size_t)t * ldr + f];
+                            out[(size_t)t * ldo + f] = lb_from_float<TO>(x);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();            // the elected lanes rejoin their warps before the block-wide barrier
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in boxes of [box_rows, 64].
+int make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (fn == nullptr) return lb_fail(LB_ERR_BACKEND, "gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
+    const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__nv_bfloat16)};
+    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS)
+        return lb_fail(LB_ERR_BACKEND, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld)", (int)r,
+                       rows, cols, (long long)ld);
+    return LB_OK;
+}
+
+// Tensor maps are cached by what they describe: encoding costs microseconds on the host, a decode step has dozens.
+struct MapKey {
+    const void* base;
+    int rows, cols, box_rows;
+    int64_t ld;
+    bool operator<(const MapKey& o) const {
+        return std::tie(base, rows, cols, box_rows, ld) < std::tie(o.base, o.rows, o.cols, o.box_rows, o.ld);
+    }
+};
+
+int cached_map(CUtensorMap* out, const void* base, int rows, int cols, int64_t ld, int box_rows) {
+    static std::map<MapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    const MapKey key{base, rows, cols, box_rows, ld};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        const int rc = make_map(&m, base, rows, cols, ld, box_rows);
+        if (rc != LB_OK) return rc;
+        if (cache.size() > 4096) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return LB_OK;
+}
+
+template <int BN, int STAGES, typename TO>
+int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const float* bias, const float* residual, int64_t ldr,
+           void* out, int64_t ldo, int M, int N, int K, int act, cudaStream_t stream) {
+    constexpr size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem));
+        configured = true;
+    }
+    dim3 grid((N + kFeatTile - 1) / kFeatTile, (M + BN - 1) / BN);
+    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, kThreads, smem, stream>>>(map_w, map_a, bias, residual, ldr, (TO*)out,
+                                                                         ldo, M, N, K, act);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+template <typename TO>
+int dispatch(int bn, const CUtensorMap& map_w, const CUtensorMap& map_a, const float* bias, const float* residual,
+             int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, cudaStream_t stream) {
+    switch (bn) {
+        case 16: return launch<16, 8, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
+        case 32: return launch<32, 8, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
+        case 64: return launch<64, 6, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
+        case 128: return launch<128, 5, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
+        default: return launch<256, 4, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
+    }
+}
+
+}  // namespace
+
+extern "C" int lb_gemm_tcgen05_token_tile(int M) {
+    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 1024 ? 128 : 256;
+}
+
+extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                               const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                               int token_tile, void* stream) {
+    LB_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0)
+        return lb_fail(LB_ERR_UNSUPPORTED,
+                       "gemm_tcgen05: TMA needs K and both row strides to be multiples of 8 elements and 16-byte aligned "
+                       "bases (K=%d lda=%lld ldw=%lld)", K, (long long)lda, (long long)ldw);
+    LB_CHECK_ARG(lda >= K && ldw >= K && ldo >= N, "gemm_tcgen05: a row stride is shorter than the row");
+    if (M == 0) return LB_OK;
+    const int bn = token_tile > 0 ? token_tile : lb_gemm_tcgen05_token_tile(M);
+    LB_CHECK_ARG(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_tcgen05: token tile %d", bn);
+    LB_CHECK_ARG((M + bn - 1) / bn <= 65535, "gemm_tcgen05: M=%d is too large for one launch", M);
+    CUtensorMap map_w, map_a;
+    int rc = cached_map(&map_w, W, N, K, ldw, kFeatTile);
+    if (rc != LB_OK) return rc;
+    rc = cached_map(&map_a, A, M, K, lda, bn);
+    if (rc != LB_OK) return rc;
+    auto s = static_cast<cudaStream_t>(stream);
+    if (out_dtype == LB_BF16)
+        return dispatch<__nv_bfloat16>(bn, map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, s);
+    if (out_dtype == LB_F32)
+        return dispatch<float>(bn, map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, s);
+    return lb_fail(LB_ERR_INVALID_ARGUMENT, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+}
+
+// Reads and clears the status word of the bounded waits (0: every wait so far completed).  Synchronises the device.
+extern "C" int lb_gemm_tcgen05_status(int* status) {
+    int zero = 0;
+    LB_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_status, sizeof(int)));
+    LB_CHECK_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
+    return LB_OK;
+}

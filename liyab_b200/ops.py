@@ -28,6 +28,8 @@ _SIGNATURES = {
     "lb_layernorm": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "lb_kv_append": [_i, _p, _p, _l, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
+    "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
+    "lb_gemm_tcgen05_status": [_p],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
 }
@@ -151,9 +153,43 @@ def gemm_ffma(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     return out
 
 
+def tcgen05_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core product takes these operands: bfloat16, and TMA's 16-byte rules."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and a.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
+                 activation: str = "none", residual: Optional[torch.Tensor] = None, token_tile: int = 0) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual on the tcgen05 tensor cores (bfloat16 operands)."""
+    n, k = w.shape
+    if a.shape[1] != k or out.stride(1) != 1 or out.shape[1] != n:
+        raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if not tcgen05_accepts(a, w):
+        raise invalid_argument("gemm_tcgen05: operands must be bfloat16 with K and row strides multiples of 8")
+    if residual is not None and (residual.shape[1] != n or residual.stride(1) != 1):
+        raise invalid_argument("gemm: residual has the wrong shape")
+    check(lib().lb_gemm_tcgen05(_code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
+                                _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
+                                residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n,
+                                k, ACTIVATIONS[activation], token_tile, stream_ptr()), "gemm_tcgen05")
+    return out
+
+
+def device_status() -> int:
+    """0 unless a bounded wait inside a kernel ran out since the last call (then where it gave up).
+    Synchronises the device."""
+    status = ctypes.c_int(0)
+    check(lib().lb_gemm_tcgen05_status(ctypes.byref(status)), "device_status")
+    return status.value
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
            activation: str = "none", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[:m] = act(a[:m] @ w.T + bias) + residual: the kernel is chosen by type and size."""
+    if tcgen05_accepts(a, w):
+        return gemm_tcgen05(a, w, bias, out, m, activation, residual)
     return gemm_ffma(a, w, bias, out, m, activation, residual)
 
 

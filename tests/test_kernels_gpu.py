@@ -232,3 +232,49 @@ def test_greedy_takes_the_first_maximum(dev):
     z = torch.zeros(2, device=dev)
     ops.sample(logits, 2, z, torch.zeros(2, dtype=torch.int32, device=dev), z + 1, z.double(), out)
     assert out.tolist() == [77, 0]
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K,tile", [
+    (1, 128, 64, 0), (8, 768, 768, 0), (5, 1000, 96, 0), (16, 130, 72, 0), (33, 50257, 256, 0), (64, 2304, 768, 0),
+    (100, 320, 3072, 0), (300, 777, 200, 0), (1025, 384, 136, 0), (2048, 768, 768, 256), (70, 96, 320, 16),
+    (257, 257, 64, 32), (64, 64, 1024, 64)])
+def test_gemm_tcgen05(dev, out_dtype, M, N, K, tile):
+    """The tensor-core product against float64, over every token tile, ragged edges in M, N and K,
+    a K that wraps the stage ring several times, and all epilogues."""
+    from liyab_b200 import ops
+    a, w = _rand((M, K), 16, dev, torch.bfloat16), _rand((N, K), 17, dev, torch.bfloat16, 0.2)
+    bias, res = _rand((N,), 18, dev), _rand((M, N), 19, dev)
+    base = a.double() @ w.double().t()
+    scale = max(1.0, base.abs().max().item())
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
+    ops.gemm_tcgen05(a, w, None, out, M, token_tile=tile)
+    assert ops.device_status() == 0
+    assert (out.double() - base).abs().max().item() <= tol * scale
+    for act, fn in (("gelu_tanh", plain.gelu_tanh), ("gelu_erf", plain.gelu_erf)):
+        ops.gemm_tcgen05(a, w, bias, out, M, act, token_tile=tile)
+        ref = torch.from_numpy(fn((base + bias.double()).cpu().numpy())).to(dev)
+        assert (out.double() - ref).abs().max().item() <= tol * scale, act
+    if out_dtype == torch.float32:
+        out2 = res.clone()
+        ops.gemm_tcgen05(a, w, bias, out2, M, "none", residual=out2, token_tile=tile)
+        assert (out2.double() - (base + bias.double() + res.double())).abs().max().item() <= tol * scale
+    # a view with a row stride (the attention output inside a wider buffer) and fewer rows than the buffer holds
+    wide = torch.zeros((M + 3, K + 8), dtype=torch.bfloat16, device=dev)
+    wide[:M, :K] = a
+    out3 = torch.full((M + 3, N), 7.0, dtype=out_dtype, device=dev)
+    ops.gemm_tcgen05(wide[:, :K], w, None, out3, M, token_tile=tile)
+    assert (out3[:M].double() - base).abs().max().item() <= tol * scale and (out3[M:] == 7.0).all()
+    assert ops.device_status() == 0
+
+
+def test_gemm_tcgen05_refuses_what_tma_cannot_fetch(dev):
+    from liyab_b200 import ops, LiyabError
+    a, w = _rand((4, 100), 1, dev, torch.bfloat16), _rand((8, 100), 2, dev, torch.bfloat16)
+    out = torch.empty((4, 8), dtype=torch.bfloat16, device=dev)
+    assert not ops.tcgen05_accepts(a, w)
+    with pytest.raises(LiyabError):
+        ops.gemm_tcgen05(a, w, None, out, 4)
+    ops.linear(a, w, None, out, 4)          # the dispatcher falls back to the 32-bit units
+    assert (out.double() - a.double() @ w.double().t()).abs().max().item() < 0.1
