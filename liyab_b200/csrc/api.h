@@ -63,6 +63,20 @@ int lb_paged_attention_generic(int dtype, const void* q, int64_t q_stride, const
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
                                int page_size, float scale, int window, void* stream);
 
+/* Decode attention, bfloat16: token i is the one new token of request i (row i of
+ * positions and of block_table).  The keys are split n_splits ways; with more than
+ * one split, `partial` (lb_decode_attention_scratch_floats floats) and `counters`
+ * (n_seq * n_kv_head ints, zero before the first call; the kernel leaves them zero)
+ * are scratch that launches on one stream may share.  lb_decode_attention_supports
+ * says whether a shape is taken (head_dim 16..256 in powers of two, 1/2/4/8 query
+ * heads per key/value head, page_size a power of two). */
+int lb_decode_attention(const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
+                        const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial,
+                        int* counters, int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
+                        int window, int n_splits, void* stream);
+int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+int64_t lb_decode_attention_scratch_floats(int n_seq, int n_head, int head_dim, int n_splits);
+
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw
  * uniform[r] in [0,1).  out_probs (optional, [n_rows, vocab]) receives the

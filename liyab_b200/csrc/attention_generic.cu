@@ -22,6 +22,37 @@ constexpr int kWarps = 4;
 constexpr int kTile = 32;       // keys per step, one per lane
 constexpr int kMaxHeadDim = 256;
 
+// Copies the rows of up to 32 keys (lane i knows the row of key i: `base`, negative if there is none) into
+// the warp's tile as floats.  Eight loads are issued before any is used, so a lone warp (a decode step of
+// one request) still keeps several requests to memory in flight.
+template <typename T>
+__device__ __forceinline__ void load_tile(const T* __restrict__ cache, long long base, long long offset, float* tile,
+                                          int tile_stride, int head_dim, int lane) {
+    constexpr int kBatch = 8;
+    const int total = kTile * head_dim;        // a multiple of 32: every lane makes the same number of trips
+    for (int idx0 = lane; idx0 < total; idx0 += 32 * kBatch) {
+        float r[kBatch];
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int idx = idx0 + 32 * u;
+            r[u] = 0.0f;
+            if (idx < total) {                 // uniform across the warp
+                const int key = idx / head_dim, d = idx - key * head_dim;
+                const long long b = __shfl_sync(0xffffffffu, base, key);
+                if (b >= 0) r[u] = lb_to_float(cache[b + offset + d]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < kBatch; ++u) {
+            const int idx = idx0 + 32 * u;
+            if (idx < total) {
+                const int key = idx / head_dim;
+                tile[key * tile_stride + (idx - key * head_dim)] = r[u];
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ cache,
@@ -63,11 +94,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
             base = (long long)page * 2 * (long long)plane + ((long long)kvh * page_size + (j % page_size)) * head_dim;
         }
         __syncwarp();
-        for (int idx = lane; idx < kTile * head_dim; idx += 32) {
-            const int key = idx / head_dim, d = idx - key * head_dim;
-            const long long b = __shfl_sync(0xffffffffu, base, key);
-            tile[key * tile_stride + d] = b >= 0 ? lb_to_float(cache[b + d]) : 0.0f;
-        }
+        load_tile(cache, base, 0, tile, tile_stride, head_dim, lane);
         __syncwarp();
         float s = -CUDART_INF_F;
         if (lane < n_keys) {
@@ -83,11 +110,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
         m = m_new;
         p_s[lane] = p;
         __syncwarp();
-        for (int idx = lane; idx < kTile * head_dim; idx += 32) {
-            const int key = idx / head_dim, d = idx - key * head_dim;
-            const long long b = __shfl_sync(0xffffffffu, base, key);
-            tile[key * tile_stride + d] = b >= 0 ? lb_to_float(cache[b + (long long)plane + d]) : 0.0f;
-        }
+        load_tile(cache, base, (long long)plane, tile, tile_stride, head_dim, lane);
         __syncwarp();
 #pragma unroll
         for (int i = 0; i < kMaxHeadDim / 32; ++i) {

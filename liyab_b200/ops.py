@@ -31,6 +31,8 @@ _SIGNATURES = {
     "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
+    "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "lb_decode_attention_supports": [_i, _i, _i, _i],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
 }
 
@@ -209,6 +211,37 @@ def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, tok_seq: torch
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         n_tokens, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), stream_ptr()),
         "paged_attention_generic")
+    return out
+
+
+def decode_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> bool:
+    return bool(lib().lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
+
+
+def decode_splits(n_seq: int, n_kv_head: int) -> int:
+    """How many ways each request's keys are split: enough blocks to fill the GPU about four times over,
+    a function of the batch's shape only (so a captured step and an eager one split alike)."""
+    return max(1, min(32, -(-592 // max(1, n_seq * n_kv_head))))
+
+
+def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                     out: torch.Tensor, partial: Optional[torch.Tensor], counters: Optional[torch.Tensor], n_seq: int,
+                     n_head: int, n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int,
+                     n_splits: int) -> torch.Tensor:
+    """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways."""
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise invalid_argument("decode attention takes bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1 or q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0:
+        raise invalid_argument("decode attention: q rows must be dense, 16-byte aligned and a multiple of 8 elements apart")
+    if n_splits > 1:
+        need = n_seq * n_head * n_splits * (head_dim + 2)
+        if partial is None or counters is None or partial.numel() < need or counters.numel() < n_seq * n_kv_head:
+            raise invalid_argument("decode attention: scratch buffers are missing or too small")
+    check(lib().lb_decode_attention(
+        _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(positions, "positions", torch.int32),
+        _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
+        _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
+        head_dim, page_size, float(scale), int(window), int(n_splits), stream_ptr()), "decode_attention")
     return out
 
 

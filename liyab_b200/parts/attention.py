@@ -52,6 +52,24 @@ class CausalSelfAttention:
     def state_need(self) -> Optional[StateNeed]:
         return None
 
+    def _attend(self, ctx: StepContext, q, cache, view, att, page_size: int) -> None:
+        """Chooses the attention kernel: for bfloat16 steps of single tokens the split-key decode kernel
+        where it takes the shape; else the generic kernel (all of the 32-bit engine runs on it, so that a
+        position's result has the same bits however the work was cut)."""
+        s, T = self.spec, ctx.n_tokens
+        if (ctx.decode_only and self.runtime.dtype == torch.bfloat16
+                and ops.decode_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):
+            splits = ops.decode_splits(T, s.n_kv_head)
+            partial = counters = None
+            if splits > 1:
+                partial = ctx.workspace.flat("attn.decode.partial", T * s.n_head * splits * (s.head_dim + 2), torch.float32)
+                counters = ctx.workspace.flat("attn.decode.counters", T * s.n_kv_head, torch.int32, zero=True)
+            ops.decode_attention(q, cache, ctx.positions, view.block_table, att, partial, counters, T, s.n_head,
+                                 s.n_kv_head, s.head_dim, page_size, s.scale, s.window, splits)
+            return
+        ops.paged_attention_generic(q, cache, ctx.tok_seq, ctx.positions, view.block_table, att, T, s.n_head,
+                                    s.n_kv_head, s.head_dim, page_size, s.scale, s.window)
+
     def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor, unit: CacheUnit) -> None:
         s, T, dt = self.spec, ctx.n_tokens, self.runtime.dtype
         ws = ctx.workspace
@@ -65,6 +83,5 @@ class CausalSelfAttention:
             v = qkv[:, self.q_dim + self.kv_dim:]
             ops.kv_append(k, v, view.slot_mapping, cache, T, s.n_kv_head, s.head_dim, page_size)
         att = ws.get("attn.out", T, self.q_dim, dt)
-        ops.paged_attention_generic(q, cache, ctx.tok_seq, ctx.positions, view.block_table, att, T, s.n_head,
-                                    s.n_kv_head, s.head_dim, page_size, s.scale, s.window)
+        self._attend(ctx, q, cache, view, att, page_size)
         self.out.forward(att, x, T, residual=x)

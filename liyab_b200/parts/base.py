@@ -64,6 +64,18 @@ class Workspace:
             self.generation += 1
         return buf
 
+    def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A one-dimensional scratch buffer of at least `numel` elements (not subject to the row floor).
+        `zero`: filled with zeros when created (for counters that kernels leave at zero)."""
+        key = (name, "flat", dtype)
+        buf = self._buffers.get(key)
+        if buf is None or buf.numel() < numel:
+            cap = 1 << max(10, (max(numel, 1) - 1).bit_length())
+            buf = (torch.zeros if zero else torch.empty)(cap, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+            self.generation += 1
+        return buf
+
     def bytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._buffers.values())
 

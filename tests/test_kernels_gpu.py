@@ -278,3 +278,46 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_fetch(dev):
         ops.gemm_tcgen05(a, w, None, out, 4)
     ops.linear(a, w, None, out, 4)          # the dispatcher falls back to the 32-bit units
     assert (out.double() - a.double() @ w.double().t()).abs().max().item() < 0.1
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window,splits", [
+    (12, 12, 64, 16, 0, 1), (12, 12, 64, 16, 0, 5), (4, 4, 16, 16, 0, 3), (3, 3, 32, 32, 0, 32), (8, 2, 128, 16, 0, 4),
+    (16, 2, 64, 64, 0, 7), (2, 1, 256, 16, 0, 2), (6, 3, 64, 16, 33, 4), (4, 4, 32, 16, 5, 16)])
+def test_decode_attention(dev, n_head, n_kv_head, head_dim, page_size, window, splits):
+    """One new token per request over its pages, keys split several ways, against float64; the same
+    scratch is used by two launches in a row (the kernel must leave its counters at zero)."""
+    from liyab_b200 import ops
+    assert ops.decode_attention_supports(n_head, n_kv_head, head_dim, page_size)
+    lens = [1, 2, 17, 64, 65, 300, 1024, 33]
+    scale = 0.5 / math.sqrt(head_dim)
+    q, cache, tok_seq, positions, table, refs = _paged_case(dev, torch.bfloat16, n_head, n_kv_head, head_dim, page_size,
+                                                            lens, [1] * len(lens), seed=7 * head_dim + splits)
+    S = len(lens)
+    partial = torch.full((S * n_head * splits * (head_dim + 2),), float("nan"), device=dev)
+    counters = torch.zeros(S * n_kv_head, dtype=torch.int32, device=dev)
+    ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
+    for _ in range(2):
+        out = torch.full_like(q, float("nan"))
+        ops.decode_attention(q, cache, positions, table, out, partial, counters, S, n_head, n_kv_head, head_dim,
+                             page_size, scale, window, splits)
+        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2
+        assert int(counters.abs().sum()) == 0
+    generic = torch.empty_like(q)
+    ops.paged_attention_generic(q, cache, tok_seq, positions, table, generic, S, n_head, n_kv_head, head_dim, page_size,
+                                scale, window)
+    assert (out.float() - generic.float()).abs().max().item() < 1.5e-2
+
+
+def test_decode_attention_finds_a_far_key(dev):
+    from liyab_b200 import ops
+    n_head, n_kv_head, head_dim, page_size = 4, 2, 64, 16
+    for key_pos, splits in ((0, 4), (15, 1), (16, 9), (271, 4), (1023, 32), (511, 3)):
+        q, cache, _, positions, table, refs = _paged_case(dev, torch.bfloat16, n_head, n_kv_head, head_dim, page_size,
+                                                          [1024], [1], seed=key_pos, boost=(key_pos, 4.0))
+        partial = torch.zeros(n_head * splits * (head_dim + 2), device=dev)
+        counters = torch.zeros(n_kv_head, dtype=torch.int32, device=dev)
+        out = torch.empty_like(q)
+        ops.decode_attention(q, cache, positions, table, out, partial, counters, 1, n_head, n_kv_head, head_dim,
+                             page_size, 1.0 / math.sqrt(head_dim), 0, splits)
+        ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
+        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
