@@ -77,6 +77,18 @@ int lb_decode_attention(const void* q, int64_t q_stride, const void* cache, cons
 int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
 int64_t lb_decode_attention_scratch_floats(int n_seq, int n_head, int head_dim, int n_splits);
 
+/* Prefill attention, bfloat16, products on the tensor cores: request i brings the
+ * tokens of rows q_start[i] .. q_start[i+1]-1 (q_start has n_seq + 1 entries), the
+ * first of them at position n_past[i]; max_q_len is the longest such run.  Keys
+ * and values, those of this step included, are read from the pages.
+ * lb_prefill_attention_supports: head_dim 16..128 in steps of 16, page_size a
+ * power of two. */
+int lb_prefill_attention(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start,
+                         const int32_t* n_past, const int32_t* block_table, int table_stride, void* out,
+                         int64_t out_stride, int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim,
+                         int page_size, float scale, int window, void* stream);
+int lb_prefill_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw
  * uniform[r] in [0,1).  out_probs (optional, [n_rows, vocab]) receives the

@@ -33,6 +33,8 @@ _SIGNATURES = {
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
+    "lb_prefill_attention": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "lb_prefill_attention_supports": [_i, _i, _i, _i],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
 }
 
@@ -242,6 +244,26 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
         head_dim, page_size, float(scale), int(window), int(n_splits), stream_ptr()), "decode_attention")
+    return out
+
+
+def prefill_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> bool:
+    return bool(lib().lb_prefill_attention_supports(n_head, n_kv_head, head_dim, page_size))
+
+
+def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tensor, n_past: torch.Tensor,
+                      block_table: torch.Tensor, out: torch.Tensor, n_seq: int, max_q_len: int, n_head: int,
+                      n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Attention of the step's prompt portions over their pages (bfloat16, tensor cores)."""
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise invalid_argument("prefill attention takes bfloat16 only")
+    if q.stride(1) != 1 or out.stride(1) != 1:
+        raise invalid_argument("prefill attention: q and out must be dense within a row")
+    check(lib().lb_prefill_attention(
+        _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(q_start, "q_start", torch.int32),
+        _dev(n_past, "n_past", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.stride(0),
+        _dev(out, "out"), out.stride(0), n_seq, max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale),
+        int(window), stream_ptr()), "prefill_attention")
     return out
 
 

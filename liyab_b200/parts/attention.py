@@ -53,9 +53,10 @@ class CausalSelfAttention:
         return None
 
     def _attend(self, ctx: StepContext, q, cache, view, att, page_size: int) -> None:
-        """Chooses the attention kernel: for bfloat16 steps of single tokens the split-key decode kernel
-        where it takes the shape; else the generic kernel (all of the 32-bit engine runs on it, so that a
-        position's result has the same bits however the work was cut)."""
+        """Chooses the attention kernel.  bfloat16: the split-key decode kernel for steps of single tokens,
+        the tensor-core kernel for steps with prompt portions, where they take the shape.  Else the generic
+        kernel; all of the 32-bit engine runs on it, so that there a position's result has the same bits
+        however the work was cut."""
         s, T = self.spec, ctx.n_tokens
         if (ctx.decode_only and self.runtime.dtype == torch.bfloat16
                 and ops.decode_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):
@@ -66,6 +67,11 @@ class CausalSelfAttention:
                 counters = ctx.workspace.flat("attn.decode.counters", T * s.n_kv_head, torch.int32, zero=True)
             ops.decode_attention(q, cache, ctx.positions, view.block_table, att, partial, counters, T, s.n_head,
                                  s.n_kv_head, s.head_dim, page_size, s.scale, s.window, splits)
+            return
+        if (self.runtime.dtype == torch.bfloat16
+                and ops.prefill_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):
+            ops.prefill_attention(q, cache, ctx.q_start, ctx.n_past, view.block_table, att, ctx.n_seq, ctx.max_q_len,
+                                  s.n_head, s.n_kv_head, s.head_dim, page_size, s.scale, s.window)
             return
         ops.paged_attention_generic(q, cache, ctx.tok_seq, ctx.positions, view.block_table, att, T, s.n_head,
                                     s.n_kv_head, s.head_dim, page_size, s.scale, s.window)

@@ -321,3 +321,43 @@ def test_decode_attention_finds_a_far_key(dev):
                              page_size, 1.0 / math.sqrt(head_dim), 0, splits)
         ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
         assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
+
+
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [
+    (12, 12, 64, 16, 0), (4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0), (5, 1, 64, 64, 0), (2, 2, 128, 16, 0),
+    (7, 7, 80, 16, 0), (4, 2, 96, 8, 0), (2, 1, 112, 16, 0), (4, 4, 32, 16, 40), (2, 1, 64, 32, 7), (3, 3, 64, 16, 100)])
+def test_prefill_attention(dev, n_head, n_kv_head, head_dim, page_size, window):
+    """Prompt portions of every kind in one launch: a whole prompt, a portion that continues a long
+    context, single tokens, two-token portions, portions that end inside a page and a tile."""
+    from liyab_b200 import ops
+    assert ops.prefill_attention_supports(n_head, n_kv_head, head_dim, page_size)
+    lens = [1, 37, 130, 64, 300, 2, 129, 1024]
+    q_lens = [1, 37, 2, 1, 45, 2, 65, 200]
+    scale = 0.6 / math.sqrt(head_dim)
+    q, cache, tok_seq, positions, table, refs = _paged_case(dev, torch.bfloat16, n_head, n_kv_head, head_dim, page_size,
+                                                            lens, q_lens, seed=head_dim + n_head + window)
+    q_start = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=dev)
+    n_past = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=dev)
+    out = torch.full_like(q, float("nan"))
+    ops.prefill_attention(q, cache, q_start, n_past, table, out, len(lens), max(q_lens), n_head, n_kv_head, head_dim,
+                          page_size, scale, window)
+    ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
+    err = (out.double().cpu() - ref).abs().max().item()
+    assert err < 1.5e-2, err
+
+
+def test_prefill_attention_finds_a_far_key_and_the_diagonal(dev):
+    """A key scaled so that its score stands out, placed at a page's edge, a tile's edge, position 0 and on the
+    diagonal of the last query: dropping a tile, a page or the query's own key shows."""
+    from liyab_b200 import ops
+    n_head, n_kv_head, head_dim, page_size = 4, 2, 64, 16
+    for key_pos in (0, 15, 16, 63, 64, 271, 511):
+        q, cache, _, _, table, refs = _paged_case(dev, torch.bfloat16, n_head, n_kv_head, head_dim, page_size, [512], [100],
+                                                  seed=key_pos, boost=(key_pos, 4.0))
+        q_start = torch.tensor([0, 100], dtype=torch.int32, device=dev)
+        n_past = torch.tensor([412], dtype=torch.int32, device=dev)
+        out = torch.empty_like(q)
+        ops.prefill_attention(q, cache, q_start, n_past, table, out, 1, 100, n_head, n_kv_head, head_dim, page_size,
+                              1.0 / math.sqrt(head_dim), 0)
+        ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
+        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
