@@ -45,11 +45,13 @@ int lb_gemm_ffma(int in_dtype, int out_dtype, const void* A, int64_t lda, const 
 /* The same product for bfloat16 operands on the tcgen05 tensor cores (TMA-fed,
  * accumulator in tensor memory).  Needs K, lda and ldw to be multiples of 8 and
  * 16-byte aligned bases, else LB_ERR_UNSUPPORTED (4).  token_tile 0 picks the tile
- * from M (lb_gemm_tcgen05_token_tile); out is LB_BF16 or LB_F32. */
+ * (lb_gemm_tcgen05_token_tile): 16, 32, 64 put the weights on the accumulator's
+ * lanes and that many tokens on its columns; 128 and 256 put 128 tokens on the
+ * lanes and that many features on the columns.  out is LB_BF16 or LB_F32. */
 int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
                     int token_tile, void* stream);
-int lb_gemm_tcgen05_token_tile(int M);
+int lb_gemm_tcgen05_token_tile(int M, int N);
 /* Reads and clears the status word that a bounded wait sets when it runs out
  * (0: none did).  Synchronises the device. */
 int lb_gemm_tcgen05_status(int* status);

@@ -36,10 +36,10 @@
 namespace {
 
 constexpr int kBlockK = 64;          // one 128-byte swizzle atom of bfloat16
-constexpr int kFeatTile = 128;       // UMMA M
+constexpr int kLaneTile = 128;       // UMMA M
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;
+constexpr long long kWaitLimitCycles = 4000000000ll;     // about two seconds at the SM's top clock
 
 __device__ int g_status = 0;         // 0 ok; else (site << 8) | detail of the first bounded wait that ran out
 
@@ -67,23 +67,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 
-__device__ __forceinline__ unsigned long long global_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-// Waits for the barrier's phase; false when the time limit ran out, or when another role already gave up
-// (abort_flag, where given).
+// Waits for the barrier's phase; false when the limit ran out, or when another role already gave up
+// (abort_flag, where given).  The limit is counted on the SM's own cycle counter, which costs a few cycles
+// to read, and only after a few hundred polls have failed: the common wait never reads a clock.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = global_ns();
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
     for (;;) {
+#pragma unroll 1
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (abort_flag != nullptr && *abort_flag != 0) return false;
-        if (global_ns() - t0 > kWaitLimitNs) return false;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
     }
+}
+
+__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
 
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
@@ -156,14 +158,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         : "memory");
 }
 
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------ the kernel
 
+// `lane operand`: the matrix whose rows become the 128 lanes of the accumulator (the instruction's M);
+// `column operand`: the matrix whose BN rows become its columns (the instruction's N).
 template <int BN, int STAGES>
 struct SharedStorage {
-    alignas(1024) __nv_bfloat16 w[STAGES][kFeatTile * kBlockK];   // 16 KB each
-    alignas(1024) __nv_bfloat16 a[STAGES][BN * kBlockK];
+    alignas(1024) __nv_bfloat16 lane_tile[STAGES][kLaneTile * kBlockK];   // 16 KB each
+    alignas(1024) __nv_bfloat16 col_tile[STAGES][BN * kBlockK];
     alignas(8) uint64_t full[STAGES];
     alignas(8) uint64_t empty[STAGES];
     alignas(8) uint64_t acc_ready;
@@ -171,24 +180,47 @@ struct SharedStorage {
     int abort_flag;
 };
 
-template <int BN, int STAGES, typename TO>
+__device__ __forceinline__ void store_row16(float* dst, const float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) reinterpret_cast<float4*>(dst)[i] = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+}
+
+__device__ __forceinline__ void store_row16(__nv_bfloat16* dst, const float (&x)[16]) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        uint4 v;
+        v.x = pack2(x[8 * i], x[8 * i + 1]);
+        v.y = pack2(x[8 * i + 2], x[8 * i + 3]);
+        v.z = pack2(x[8 * i + 4], x[8 * i + 5]);
+        v.w = pack2(x[8 * i + 6], x[8 * i + 7]);
+        reinterpret_cast<uint4*>(dst)[i] = v;
+    }
+}
+
+// TOKENS_ON_LANES = false (few tokens): the weights are the lane operand, lane i = feature n0 + i, column
+// j = token m0 + j.  TOKENS_ON_LANES = true (many tokens): the activations are the lane operand, lane i =
+// token m0 + i, column j = feature n0 + j, so a thread owns a run of one token's features and stores vectors.
+template <int BN, int STAGES, bool TOKENS_ON_LANES, typename TO>
 __global__ void __launch_bounds__(kThreads)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_constant__ CUtensorMap map_col,
                     const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M,
-                    int N, int K, int act) {
+                    int N, int K, int act, int vec_ok) {
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
     Storage& s = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t kTmemCols = BN < 32 ? 32 : BN;
-    constexpr uint32_t kStageBytes = (kFeatTile + BN) * kBlockK * sizeof(__nv_bfloat16);
+    constexpr uint32_t kStageBytes = (kLaneTile + BN) * kBlockK * sizeof(__nv_bfloat16);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * kFeatTile;     // first output feature of the tile
-    const int m0 = blockIdx.y * BN;            // first token of the tile
+    const int n0 = blockIdx.x * (TOKENS_ON_LANES ? BN : kLaneTile);     // first output feature of the tile
+    const int m0 = blockIdx.y * (TOKENS_ON_LANES ? kLaneTile : BN);     // first token of the tile
+    const int lane_row0 = TOKENS_ON_LANES ? m0 : n0, col_row0 = TOKENS_ON_LANES ? n0 : m0;
     const int n_kb = (K + kBlockK - 1) / kBlockK;
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
+        prefetch_tensormap(&map_lane);
+        prefetch_tensormap(&map_col);
         for (int i = 0; i < STAGES; ++i) {
             mbar_init(&s.full[i], 1);
             mbar_init(&s.empty[i], 1);
@@ -218,8 +250,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     break;
                 }
                 mbar_expect_tx(&s.full[st], kStageBytes);
-                tma_load_2d(s.w[st], &map_w, &s.full[st], kb * kBlockK, n0);
-                tma_load_2d(s.a[st], &map_a, &s.full[st], kb * kBlockK, m0);
+                tma_load_2d(s.lane_tile[st], &map_lane, &s.full[st], kb * kBlockK, lane_row0);
+                tma_load_2d(s.col_tile[st], &map_col, &s.full[st], kb * kBlockK, col_row0);
                 issued = kb + 1;
             }
             if (s.abort_flag != 0 && issued > 0) {
@@ -230,7 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc(kFeatTile, BN);
+            constexpr uint32_t idesc = umma_idesc(kLaneTile, BN);
             bool ok = true;
             for (int kb = 0; kb < n_kb && ok; ++kb) {
                 const int st = kb % STAGES;
@@ -242,11 +274,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
                     break;
                 }
                 tc_fence_after();
-                const uint32_t w_addr = smem_u32(s.w[st]), a_addr = smem_u32(s.a[st]);
+                const uint32_t l_addr = smem_u32(s.lane_tile[st]), c_addr = smem_u32(s.col_tile[st]);
 #pragma unroll
                 for (int k = 0; k < kBlockK / kUmmaK; ++k) {
                     const uint32_t off = k * kUmmaK * sizeof(__nv_bfloat16);
-                    umma_bf16(tmem_base, umma_desc(w_addr + off), umma_desc(a_addr + off), idesc, (kb | k) != 0 ? 1u : 0u);
+                    umma_bf16(tmem_base, umma_desc(l_addr + off), umma_desc(c_addr + off), idesc, (kb | k) != 0 ? 1u : 0u);
                 }
                 umma_commit(&s.empty[st]);      // the stage is free once these MMAs have read it
             }
@@ -255,29 +287,78 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     } else {
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
-        const int f = n0 + quarter * 32 + lane;
+        const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
         if (!mbar_wait(&s.acc_ready, 0, abort_flag)) {
             if (lane == 0) atomicCAS(&g_status, 0, (3 << 8) | quarter);
             s.abort_flag = 1;
+        } else if (TOKENS_ON_LANES) {
+            tc_fence_after();
+            const int t = m0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                const int f0 = n0 + c;
+                if (f0 >= N) break;              // uniform across the block
+                uint32_t v[16];
+                tmem_ld16(tmem_row + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (t >= M) continue;
+                float x[16];
+                if (vec_ok && f0 + 16 <= N) {
+                    float r[16];
+                    if (residual != nullptr) {
+                        const float4* rp = reinterpret_cast<const float4*>(residual + (size_t)t * ldr + f0);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const float4 q = rp[i];
+                            r[4 * i] = q.x; r[4 * i + 1] = q.y; r[4 * i + 2] = q.z; r[4 * i + 3] = q.w;
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float y = __uint_as_float(v[j]);
+                        if (bias != nullptr) y += __ldg(bias + f0 + j);
+                        y = lb_activate(y, act);
+                        if (residual != nullptr) y += r[j];
+                        x[j] = y;
+                    }
+                    store_row16(out + (size_t)t * ldo + f0, x);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int f = f0 + j;
+                        if (f < N) {
+                            float y = __uint_as_float(v[j]);
+                            if (bias != nullptr) y += bias[f];
+                            y = lb_activate(y, act);
+                            if (residual != nullptr) y += residual[(size_t)t * ldr + f];
+                            out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
+                        }
+                    }
+                }
+            }
         } else {
             tc_fence_after();
+            const int f = n0 + quarter * 32 + lane;
             const float b = (bias != nullptr && f < N) ? bias[f] : 0.0f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
-                if (m0 + c >= M) break;          // uniform across the warp
+                if (m0 + c >= M) break;          // uniform across the block
                 uint32_t v[16];
-                tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c, v);
+                tmem_ld16(tmem_row + (uint32_t)c, v);
                 tmem_ld_wait();
                 if (f < N) {
+                    // All of the chunk's residual values are requested before the first store: the output may
+                    // be the residual buffer itself, and a load queued behind a store would wait for it.
+                    float r[16];
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = m0 + c + j;
-                        if (t < M) {
-                            float x = __uint_as_float(v[j]) + b;
-                            x = lb_activate(x, act);
-                            if (residual != nullptr) x += residual[(size_t)t * ldr + f];
-                            out[(size_t)t * ldo + f] = lb_from_float<TO>(x);
-                        }
+                        r[j] = (residual != nullptr && t < M) ? residual[(size_t)t * ldr + f] : 0.0f;
+                    }
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = m0 + c + j;
+                        if (t < M) out[(size_t)t * ldo + f] = lb_from_float<TO>(lb_activate(__uint_as_float(v[j]) + b, act) + r[j]);
                     }
                 }
             }
@@ -355,39 +436,35 @@ int cached_map(CUtensorMap* out, const void* base, int rows, int cols, int64_t l
     return LB_OK;
 }
 
-template <int BN, int STAGES, typename TO>
-int launch(const CUtensorMap& map_w, const CUtensorMap& map_a, const float* bias, const float* residual, int64_t ldr,
-           void* out, int64_t ldo, int M, int N, int K, int act, cudaStream_t stream) {
+template <int BN, int STAGES, bool TOKENS_ON_LANES, typename TO>
+int launch(const CUtensorMap& map_lane, const CUtensorMap& map_col, const float* bias, const float* residual, int64_t ldr,
+           void* out, int64_t ldo, int M, int N, int K, int act, int vec_ok, cudaStream_t stream) {
     constexpr size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
-        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)smem));
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_tcgen05_kernel<BN, STAGES, TOKENS_ON_LANES, TO>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
-    dim3 grid((N + kFeatTile - 1) / kFeatTile, (M + BN - 1) / BN);
-    gemm_tcgen05_kernel<BN, STAGES, TO><<<grid, kThreads, smem, stream>>>(map_w, map_a, bias, residual, ldr, (TO*)out,
-                                                                         ldo, M, N, K, act);
+    dim3 grid(TOKENS_ON_LANES ? (N + BN - 1) / BN : (N + kLaneTile - 1) / kLaneTile,
+              TOKENS_ON_LANES ? (M + kLaneTile - 1) / kLaneTile : (M + BN - 1) / BN);
+    gemm_tcgen05_kernel<BN, STAGES, TOKENS_ON_LANES, TO><<<grid, kThreads, smem, stream>>>(
+        map_lane, map_col, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, vec_ok);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
 
-template <typename TO>
-int dispatch(int bn, const CUtensorMap& map_w, const CUtensorMap& map_a, const float* bias, const float* residual,
-             int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, cudaStream_t stream) {
-    switch (bn) {
-        case 16: return launch<16, 8, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
-        case 32: return launch<32, 8, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
-        case 64: return launch<64, 6, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
-        case 128: return launch<128, 5, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
-        default: return launch<256, 4, TO>(map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, stream);
-    }
-}
-
 }  // namespace
 
-extern "C" int lb_gemm_tcgen05_token_tile(int M) {
-    return M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 1024 ? 128 : 256;
+// The tile along the tokens for M tokens: 16, 32 or 64 tokens as accumulator columns (weights on the
+// lanes) up to 64 tokens; beyond that 128 tokens on the lanes (reported as 128, or 256 when the product is
+// large enough to fill the GPU several times with 128 x 256 tiles).
+extern "C" int lb_gemm_tcgen05_token_tile(int M, int N) {
+    if (M <= 16) return 16;
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    const long long big_tiles = (long long)((M + 127) / 128) * ((N + 255) / 256);
+    return big_tiles >= 4 * 148 ? 256 : 128;
 }
 
 extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
@@ -399,21 +476,44 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
                        "gemm_tcgen05: TMA needs K and both row strides to be multiples of 8 elements and 16-byte aligned "
                        "bases (K=%d lda=%lld ldw=%lld)", K, (long long)lda, (long long)ldw);
     LB_CHECK_ARG(lda >= K && ldw >= K && ldo >= N, "gemm_tcgen05: a row stride is shorter than the row");
+    LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_tcgen05: unknown output dtype %d", out_dtype);
     if (M == 0) return LB_OK;
-    const int bn = token_tile > 0 ? token_tile : lb_gemm_tcgen05_token_tile(M);
-    LB_CHECK_ARG(bn == 16 || bn == 32 || bn == 64 || bn == 128 || bn == 256, "gemm_tcgen05: token tile %d", bn);
-    LB_CHECK_ARG((M + bn - 1) / bn <= 65535, "gemm_tcgen05: M=%d is too large for one launch", M);
+    const int tile = token_tile > 0 ? token_tile : lb_gemm_tcgen05_token_tile(M, N);
+    LB_CHECK_ARG(tile == 16 || tile == 32 || tile == 64 || tile == 128 || tile == 256, "gemm_tcgen05: token tile %d", tile);
+    const bool tokens_on_lanes = tile >= 128;
+    const int token_box = tokens_on_lanes ? kLaneTile : tile;
+    const int feature_box = tokens_on_lanes ? tile : kLaneTile;       // tile 128/256 names the feature columns there
+    LB_CHECK_ARG((M + token_box - 1) / token_box <= 65535, "gemm_tcgen05: M=%d is too large for one launch", M);
     CUtensorMap map_w, map_a;
-    int rc = cached_map(&map_w, W, N, K, ldw, kFeatTile);
+    int rc = cached_map(&map_w, W, N, K, ldw, feature_box);
     if (rc != LB_OK) return rc;
-    rc = cached_map(&map_a, A, M, K, lda, bn);
+    rc = cached_map(&map_a, A, M, K, lda, token_box);
     if (rc != LB_OK) return rc;
     auto s = static_cast<cudaStream_t>(stream);
-    if (out_dtype == LB_BF16)
-        return dispatch<__nv_bfloat16>(bn, map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, s);
-    if (out_dtype == LB_F32)
-        return dispatch<float>(bn, map_w, map_a, bias, residual, ldr, out, ldo, M, N, K, act, s);
-    return lb_fail(LB_ERR_INVALID_ARGUMENT, "gemm_tcgen05: unknown output dtype %d", out_dtype);
+    // Vector stores need 16-byte aligned rows of the output (and of the residual and bias when given).
+    const int elem = out_dtype == LB_F32 ? 4 : 2;
+    const int vec_ok = ((uintptr_t)out & 15) == 0 && (ldo * elem) % 16 == 0 &&
+                       (residual == nullptr || (((uintptr_t)residual & 15) == 0 && (ldr * 4) % 16 == 0));
+#define LB_GO(BN, STAGES, TOL, TO)                                                                                \
+    return launch<BN, STAGES, TOL, TO>(TOL ? map_a : map_w, TOL ? map_w : map_a, bias, residual, ldr, out, ldo, M, N, K, \
+                                       act, vec_ok, s)
+    if (out_dtype == LB_BF16) {
+        switch (tile) {
+            case 16: LB_GO(16, 8, false, __nv_bfloat16);
+            case 32: LB_GO(32, 8, false, __nv_bfloat16);
+            case 64: LB_GO(64, 6, false, __nv_bfloat16);
+            case 128: LB_GO(128, 3, true, __nv_bfloat16);
+            default: LB_GO(256, 4, true, __nv_bfloat16);
+        }
+    }
+    switch (tile) {
+        case 16: LB_GO(16, 8, false, float);
+        case 32: LB_GO(32, 8, false, float);
+        case 64: LB_GO(64, 6, false, float);
+        case 128: LB_GO(128, 3, true, float);
+        default: LB_GO(256, 4, true, float);
+    }
+#undef LB_GO
 }
 
 // Reads and clears the status word of the bounded waits (0: every wait so far completed).  Synchronises the device.
