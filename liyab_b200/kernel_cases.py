@@ -1,0 +1,161 @@
+"""Small, self-timed workloads of single kernels and single steps, for profiling.
+
+    python -m liyab_b200.kernel_cases gemm --m 2048 --n 768 --k 3072 --out float32 --reps 20
+    python -m liyab_b200.kernel_cases decode-attention --batch 64 --context 768 --reps 20
+    python -m liyab_b200.kernel_cases decode-step --batch 8 --layers 12 --reps 20 [--eager]
+    python -m liyab_b200.kernel_cases prefill-step --tokens 2048 --layers 12 --reps 3
+
+Each prints one line with the CUDA-event time per repetition and the achieved rate.  The cases are what the
+ncu summaries under profiles/ were captured on (one kernel, a few launches, inputs of a few hundred MB at most).
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+import tempfile
+import time
+
+import numpy as np
+import torch
+
+GPT2_SMALL = dict(model_type="gpt2", n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257,
+                  n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+
+
+def _timed(fn, reps: int, warmup: int = 2) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(reps):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / reps
+
+
+def case_gemm(args) -> None:
+    from . import ops
+    dev = torch.device("cuda:0")
+    odt = torch.float32 if args.out == "float32" else torch.bfloat16
+    a = torch.randn(args.m, args.k, device=dev).to(torch.bfloat16)
+    w = (torch.randn(args.n, args.k, device=dev) * 0.05).to(torch.bfloat16)
+    bias = torch.randn(args.n, device=dev)
+    out = torch.zeros(args.m, args.n, dtype=odt, device=dev)
+    res = out if odt == torch.float32 else None
+    ms = _timed(lambda: ops.gemm_tcgen05(a, w, bias, out, args.m, args.act, residual=res, token_tile=args.tile), args.reps)
+    print(f"gemm M={args.m} N={args.n} K={args.k} out={args.out}: {ms * 1e3:.1f} us per launch (includes the host's "
+          f"launch cost when the kernel is shorter), {2 * args.m * args.n * args.k / ms / 1e9:.1f} TFLOP/s, "
+          f"{(args.n * args.k * 2) / ms / 1e6:.1f} GB/s of weights, status {ops.device_status()}")
+
+
+def case_decode_attention(args) -> None:
+    from . import ops
+    dev = torch.device("cuda:0")
+    B, H, hd, ps, ctx = args.batch, args.heads, args.head_dim, 16, args.context
+    pages_per = -(-ctx // ps)
+    cache = torch.randn(B * pages_per, 2, H, ps, hd, device=dev).to(torch.bfloat16)
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+    q = torch.randn(B, H * hd, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
+    splits = ops.decode_splits(B, H)
+    partial = torch.empty(B * H * splits * (hd + 2), device=dev)
+    counters = torch.zeros(B * H, dtype=torch.int32, device=dev)
+    ms = _timed(lambda: ops.decode_attention(q, cache, positions, table, out, partial, counters, B, H, H, hd, ps,
+                                             hd ** -0.5, 0, splits), args.reps)
+    nbytes = B * ctx * 2 * H * hd * 2
+    print(f"decode-attention batch={B} heads={H} head_dim={hd} context={ctx} splits={splits}: {ms * 1e3:.1f} us, "
+          f"{nbytes / ms / 1e6:.1f} GB/s of cache ({nbytes / 1e6:.1f} MB)")
+
+
+def _model_folder(layers: int, dtype: str) -> str:
+    from .config import parse_config
+    from .weights import write_random_model
+    tmp = tempfile.mkdtemp(prefix="liyab_b200_case_")
+    return write_random_model(os.path.join(tmp, "m"), parse_config(dict(GPT2_SMALL, n_layer=layers)), 0, dtype)
+
+
+def case_decode_step(args) -> None:
+    from .engine import StepEntry
+    from .engine.replay import build_replayer
+    B = args.batch
+    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype), args.dtype, max_tokens=B * 1024,
+                                           max_requests=B)
+    stepper.cuda_graphs = not args.eager
+    stepper.workspace.reserve_rows(max(1024, B))
+    V = model.spec.vocab_size
+    rng = np.random.default_rng(0)
+    ids = [f"b{i}" for i in range(B)]
+    for r in ids:
+        cache.open(r)
+    for i in range(0, B, 2):
+        stepper.step([StepEntry(r, rng.integers(0, V, size=args.context).tolist(), []) for r in ids[i:i + 2]])
+
+    def one():
+        if cache.length(ids[0]) + 1 > model.max_positions:
+            for r in ids:
+                cache.truncate(r, args.context)
+        stepper.step([StepEntry(r, [1], [0]) for r in ids])
+
+    ms = _timed(one, args.reps, warmup=3)
+    print(f"decode-step batch={B} layers={args.layers} context~{args.context} graphs={not args.eager}: "
+          f"{ms * 1e3:.1f} us per step, {B / ms * 1e3:.0f} tokens/s")
+
+
+def case_prefill_step(args) -> None:
+    from .engine import StepEntry
+    from .engine.replay import build_replayer
+    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype), args.dtype, max_tokens=2 * args.tokens)
+    V = model.spec.vocab_size
+    rng = np.random.default_rng(0)
+    n_seq = max(1, args.tokens // 1024)
+    per = args.tokens // n_seq
+
+    def one():
+        for i in range(n_seq):
+            cache.open(f"p{i}")
+        stepper.step([StepEntry(f"p{i}", rng.integers(0, V, size=per).tolist(), [per - 1]) for i in range(n_seq)])
+        for i in range(n_seq):
+            cache.close(f"p{i}")
+
+    ms = _timed(one, args.reps, warmup=2)
+    print(f"prefill-step tokens={n_seq}x{per} layers={args.layers}: {ms:.3f} ms per step, {n_seq * per / ms * 1e3:.0f} tokens/s")
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="python -m liyab_b200.kernel_cases")
+    sub = ap.add_subparsers(dest="case", required=True)
+    g = sub.add_parser("gemm")
+    g.add_argument("--m", type=int, default=2048)
+    g.add_argument("--n", type=int, default=768)
+    g.add_argument("--k", type=int, default=3072)
+    g.add_argument("--out", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--act", default="none", choices=["none", "gelu_tanh", "gelu_erf"])
+    g.add_argument("--tile", type=int, default=0)
+    g.add_argument("--reps", type=int, default=20)
+    d = sub.add_parser("decode-attention")
+    d.add_argument("--batch", type=int, default=64)
+    d.add_argument("--heads", type=int, default=12)
+    d.add_argument("--head-dim", type=int, default=64)
+    d.add_argument("--context", type=int, default=768)
+    d.add_argument("--reps", type=int, default=20)
+    for name in ("decode-step", "prefill-step"):
+        p = sub.add_parser(name)
+        p.add_argument("--batch", type=int, default=8)
+        p.add_argument("--tokens", type=int, default=2048)
+        p.add_argument("--context", type=int, default=512)
+        p.add_argument("--layers", type=int, default=12)
+        p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+        p.add_argument("--reps", type=int, default=10)
+        p.add_argument("--eager", action="store_true")
+    args = ap.parse_args(argv)
+    {"gemm": case_gemm, "decode-attention": case_decode_attention, "decode-step": case_decode_step,
+     "prefill-step": case_prefill_step}[args.case](args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
