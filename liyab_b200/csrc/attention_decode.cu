@@ -294,3 +294,77 @@ extern "C" int lb_decode_attention(const void* q, int64_t q_stride, const void* 
 #undef LB_HD
     return lb_fail(LB_ERR_INTERNAL, "decode attention: unreachable");
 }
+
+// ------------------------------------------------------------------ the entry point that allocates nothing
+//
+// See no_alloc.h for what it promises.  The scratch lives in the two arrays below.  In host code their
+// names stand for the arrays but are not device addresses; the addresses a kernel can use are looked up
+// once per device with cudaGetSymbolAddress and kept in g_noalloc.
+#include "no_alloc.h"
+
+#include <mutex>
+
+static __device__ __align__(256) float g_noalloc_partial[LB_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_counters[LB_NOALLOC_COUNTER_INTS];
+
+namespace {
+
+constexpr int kMaxDevices = 64;
+
+struct NoAllocScratch {
+    float* partial = nullptr;
+    int* counters = nullptr;
+};
+
+NoAllocScratch g_noalloc[kMaxDevices];
+std::mutex g_noalloc_mutex;
+
+// The scratch addresses on the current device, looked up at the first call on that device.
+int noalloc_scratch(NoAllocScratch* out) {
+    int device = -1;
+    LB_CHECK_CUDA(cudaGetDevice(&device));
+    LB_CHECK_ARG(device >= 0 && device < kMaxDevices, "decode attention (no-alloc): device ordinal %d is not supported", device);
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocScratch& slot = g_noalloc[device];
+    if (slot.partial == nullptr) {
+        float* partial = nullptr;
+        int* counters = nullptr;
+        LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&partial, g_noalloc_partial));
+        LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&counters, g_noalloc_counters));
+        slot.partial = partial;
+        slot.counters = counters;
+    }
+    *out = slot;
+    return LB_OK;
+}
+
+}  // namespace
+
+extern "C" int lb_decode_attention_noalloc(const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
+                                           const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
+                                           int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
+                                           int window, int n_splits, void* stream) {
+    LB_CHECK_ARG(n_seq >= 0 && n_splits >= 1, "decode attention (no-alloc): bad sizes n_seq=%d n_splits=%d", n_seq, n_splits);
+    if (!lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
+        return lb_fail(LB_ERR_UNSUPPORTED, "decode attention (no-alloc): unsupported shape heads %d/%d head_dim %d page_size %d",
+                       n_head, n_kv_head, head_dim, page_size);
+    const long long floats = (long long)n_seq * n_head * n_splits * (head_dim + 2);
+    const long long ints = (long long)n_seq * n_kv_head;
+    LB_CHECK_ARG(floats <= LB_NOALLOC_SCRATCH_FLOATS,
+                 "decode attention (no-alloc): %lld floats of scratch needed (n_seq %d x n_head %d x n_splits %d x (head_dim %d + 2)), "
+                 "the built-in scratch holds %d; use fewer splits or requests, or lb_decode_attention with your own scratch",
+                 floats, n_seq, n_head, n_splits, head_dim, LB_NOALLOC_SCRATCH_FLOATS);
+    LB_CHECK_ARG(ints <= LB_NOALLOC_COUNTER_INTS,
+                 "decode attention (no-alloc): %lld counters needed (n_seq %d x n_kv_head %d), the built-in scratch holds %d",
+                 ints, n_seq, n_kv_head, LB_NOALLOC_COUNTER_INTS);
+    if (n_seq == 0) return LB_OK;
+    NoAllocScratch scratch;
+    const int rc = noalloc_scratch(&scratch);
+    if (rc != LB_OK) return rc;
+    auto s = static_cast<cudaStream_t>(stream);
+    // The array keeps the last call's contents; the counters have to start at zero.
+    LB_CHECK_CUDA(cudaMemsetAsync(scratch.counters, 0, (size_t)ints * sizeof(int), s));
+    return lb_decode_attention(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, scratch.partial,
+                               scratch.counters, n_seq, n_head, n_kv_head, head_dim, page_size, scale, window, n_splits,
+                               stream);
+}
