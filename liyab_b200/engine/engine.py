@@ -38,6 +38,7 @@ class EngineConfig:
     num_pages: int = 0                 # 0: enough for max_requests full contexts, within kv_memory_fraction
     kv_memory_fraction: float = 0.5    # of the free device memory, at most, for the cache when num_pages is 0
     cuda_graphs: bool = True           # replay captured graphs for decode-only steps
+    fused_decode: bool = True          # one persistent kernel for decode steps of up to 16 requests (bfloat16)
 
 
 @dataclass
@@ -89,7 +90,8 @@ class Engine:
         self.cache = CacheManager(kv_needs, state_needs, cfg.page_size, num_pages, cfg.max_requests,
                                   dtype=self.model.runtime.dtype, device=self.device)
         self.stepper = Stepper(self.model, self.cache, max_step_tokens=cfg.max_batched_tokens,
-                               cuda_graphs=cfg.cuda_graphs, max_positions=self.max_positions)
+                               cuda_graphs=cfg.cuda_graphs, max_positions=self.max_positions,
+                               fused_decode=cfg.fused_decode)
         self.scheduler = Scheduler(self.cache, self.max_positions, cfg.max_batched_tokens, cfg.max_requests,
                                    eos_token_id=self.model.spec.eos_token_id)
         self.sampler = DeviceSampler(self.device, cfg.max_requests)

@@ -32,12 +32,12 @@ MAX_LIVE_REQUESTS = 16
 
 
 def build_replayer(model_dir: str, dtype: str, max_tokens: int, device: str = "cuda:0",
-                   page_size: int = REPLAY_PAGE_SIZE, max_requests: int = MAX_LIVE_REQUESTS):
+                   page_size: int = REPLAY_PAGE_SIZE, max_requests: int = MAX_LIVE_REQUESTS, fused_decode: bool = True):
     model, _ = load_model(model_dir, dtype, device)
     num_pages = max(1, (max_tokens + page_size - 1) // page_size)
     cache = CacheManager(model.kv_needs(), model.state_needs(), page_size, num_pages, max_requests,
                          dtype=model.runtime.dtype, device=model.runtime.device)
-    return model, cache, Stepper(model, cache)
+    return model, cache, Stepper(model, cache, fused_decode=fused_decode)
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[str], done: Optional[IO[str]] = None,

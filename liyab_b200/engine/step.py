@@ -26,6 +26,7 @@ from ..cache.pages import CacheManager, OutOfPages
 from ..models.decoder import DecoderModel
 from ..parts.base import GroupView, StepContext, Workspace
 from ..status import context_full, invalid_argument
+from .fused_decode import FusedDecodeStack
 
 
 @dataclass
@@ -63,7 +64,7 @@ class Stepper:
     """
 
     def __init__(self, model: DecoderModel, cache: CacheManager, max_step_tokens: int = 0, cuda_graphs: bool = False,
-                 max_positions: int = 0):
+                 max_positions: int = 0, fused_decode: bool = True):
         self.model = model
         self.cache = cache
         self.device = model.runtime.device
@@ -78,6 +79,9 @@ class Stepper:
         self._dev: Optional[torch.Tensor] = None
         self._turn = 0
         self.cuda_graphs = cuda_graphs
+        # Decode steps of a few tokens go to the one-kernel path where the model is made of standard parts.
+        self.fused = FusedDecodeStack.try_build(model, cache) if fused_decode else None
+        self.fused_steps = 0
         self._graphs: dict = {}
         self.graph_launches: dict = {}       # kernels in the captured step, by number of requests
         self.steps = 0
@@ -122,7 +126,12 @@ class Stepper:
                              f"pages {cache.free_pages()}")
         for e in entries:
             cache.reserve(e.request, len(e.tokens))
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+        decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if decode and self.fused is not None and self.fused.accepts(len(entries)):
+            ctx, rows = self._layout(entries)
+            logits = self.fused.run(ctx)
+            self.fused_steps += 1
+        elif decode and self.cuda_graphs:
             logits, rows = self._graph_step(entries)
         else:
             ctx, rows = self._layout(entries)

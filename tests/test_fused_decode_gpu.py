@@ -1,0 +1,90 @@
+"""The one-kernel decode step against the plain implementation and against the part-by-part path."""
+from __future__ import annotations
+
+import numpy as np
+import pytest
+
+import plain_gpt2 as plain
+import trace_tools as tt
+from tiny_models import CONFIGS, random_tokens, write_model
+
+pytestmark = pytest.mark.gpu
+REL_TOL = 2.5e-2
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    base = str(tmp_path_factory.mktemp("fused_models"))
+    return {n: write_model(base, n, "bfloat16") for n in ("D", "E")}
+
+
+def requests_for(name):
+    raw, seed = CONFIGS[name]
+    P, V = raw["n_positions"], raw["vocab_size"]
+    return {f"r{i}": random_tokens(50 * seed + i, n, V) for i, n in enumerate((P, 77, 40, 33, 150, 9))}
+
+
+def decode_heavy(reqs, live=4):
+    """Each request: a short prompt portion, then every further token alone, up to `live` requests side by side."""
+    return tt.mixed(reqs, max_live=live, seed=11, prompt_frac=0.25)
+
+
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_fused_decode_matches_plain_and_parts(name, folders):
+    from liyab_b200.engine.fused_decode import FusedDecodeStack
+    from liyab_b200.engine.replay import build_replayer
+    reqs = requests_for(name)
+    oracle = plain.load_plain_model(folders[name])
+    want = {r: plain.forward_logits(oracle, toks) for r, toks in reqs.items()}
+    steps = decode_heavy(reqs)
+    results = {}
+    for fused in (True, False):
+        _, cache, stepper = build_replayer(folders[name], "bfloat16", max_tokens=4 * 320, fused_decode=fused)
+        assert (stepper.fused is not None) == fused
+        results[fused] = tt.collect(stepper, cache, steps)
+        if fused:
+            assert stepper.fused_steps > 50, "most steps of this trace are decode steps"
+            assert FusedDecodeStack.status() == 0
+    for (r, pos), row in results[True].items():
+        scale = np.abs(want[r]).max()
+        assert np.abs(row - want[r][pos]).max() <= REL_TOL * scale, (r, pos)
+        assert np.abs(row - results[False][(r, pos)]).max() <= REL_TOL * scale, (r, pos)
+
+
+def test_fused_decode_up_to_sixteen_requests_and_long_contexts(folders):
+    """Sixteen requests decode side by side (the kernel's limit) at contexts from 1 to the model's last position."""
+    from liyab_b200.engine import StepEntry
+    from liyab_b200.engine.replay import build_replayer
+    raw, _ = CONFIGS["D"]
+    P, V = raw["n_positions"], raw["vocab_size"]
+    _, cache, stepper = build_replayer(folders["D"], "bfloat16", max_tokens=17 * 320, max_requests=17)
+    oracle = plain.load_plain_model(folders["D"])
+    lens = [1, 2, 15, 16, 17, 31, 64, 65, 100, 128, 129, 200, 255, 256, 290, P - 1]
+    toks = {f"s{i}": random_tokens(900 + i, n + 1, V) for i, n in enumerate(lens)}
+    for r, t in toks.items():
+        cache.open(r)
+        stepper.step([StepEntry(r, t[:-1], [])])
+    out = stepper.step([StepEntry(r, [t[-1]], [0]) for r, t in toks.items()])
+    assert stepper.fused_steps == 1
+    got = out.logits.float().cpu().numpy()
+    for i, (r, t) in enumerate(toks.items()):
+        ref = plain.forward_logits(oracle, t)
+        assert np.abs(got[i] - ref[-1]).max() <= REL_TOL * np.abs(ref).max(), r
+    # seventeen requests are one too many for the kernel: the step takes the other path and still agrees
+    cache.open("extra")
+    extra = random_tokens(5, 10, V)
+    stepper.step([StepEntry("extra", extra[:-1], [])])
+    for r in toks:
+        cache.truncate(r, len(toks[r]) - 1)
+    out = stepper.step([StepEntry(r, [t[-1]], [0]) for r, t in toks.items()] + [StepEntry("extra", [extra[-1]], [0])])
+    assert stepper.fused_steps == 1
+    got2 = out.logits.float().cpu().numpy()
+    assert np.abs(got2[:16] - got).max() <= REL_TOL * np.abs(got).max()
+
+
+def test_models_of_other_parts_do_not_take_the_fused_path(tmp_path):
+    from liyab_b200.engine.replay import build_replayer
+    _, _, stepper = build_replayer(write_model(str(tmp_path), "B", "bfloat16"), "bfloat16", max_tokens=256)
+    assert stepper.fused is None            # head size 32 is not one the kernel takes
+    _, _, stepper = build_replayer(write_model(str(tmp_path), "D", "float32"), "float32", max_tokens=256)
+    assert stepper.fused is None            # the 32-bit engine keeps its part-by-part kernels

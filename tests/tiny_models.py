@@ -21,7 +21,14 @@ CONFIG_B = dict(model_type="gpt2", n_layer=3, n_embd=96, n_head=3, n_inner=320, 
 CONFIG_C = dict(model_type="gpt2", n_layer=1, n_embd=240, n_head=5, n_inner=136, vocab_size=777, n_positions=320,
                 layer_norm_epsilon=1e-3, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=True,
                 scale_attn_weights=True, tie_word_embeddings=True)
-CONFIGS = {"A": (CONFIG_A, 0), "B": (CONFIG_B, 1), "C": (CONFIG_C, 2)}
+# Head sizes 64 and 128: the shapes the fused decode step takes.
+CONFIG_D = dict(model_type="gpt2", n_layer=3, n_embd=128, n_head=2, n_inner=328, vocab_size=777, n_positions=300,
+                layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_by_inverse_layer_idx=False,
+                tie_word_embeddings=True)
+CONFIG_E = dict(model_type="gpt2", n_layer=2, n_embd=384, n_head=3, n_inner=1000, vocab_size=1031, n_positions=200,
+                layer_norm_epsilon=1e-6, activation_function="gelu", scale_attn_by_inverse_layer_idx=True,
+                tie_word_embeddings=True)
+CONFIGS = {"A": (CONFIG_A, 0), "B": (CONFIG_B, 1), "C": (CONFIG_C, 2), "D": (CONFIG_D, 3), "E": (CONFIG_E, 4)}
 
 
 def write_model(folder: str, name: str, dtype: str = "float32") -> str:
