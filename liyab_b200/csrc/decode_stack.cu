@@ -92,6 +92,7 @@ struct StackParams {
     unsigned* barrier;
     int* status;
     int n_splits, act_ld;
+    unsigned long long* timing;      // optional: block 0 stamps the global timer after every barrier
 };
 
 __device__ int g_stack_status = 0;
@@ -127,6 +128,11 @@ __device__ bool grid_sync(const StackParams& p, unsigned& epoch, int phase_code)
         }
         __threadfence();
         ok_s = ok;
+        if (p.timing != nullptr && blockIdx.x == 0) {
+            unsigned long long now;
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+            p.timing[epoch] = now;
+        }
     } else {
         ++epoch;
     }
@@ -141,30 +147,90 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // Rows of x (float32, written by other blocks: read through L2) -> LayerNorm -> bfloat16 rows in shared memory.
+// One warp per row.  Up to 2048 columns the row is fetched once, as 16-byte loads that are all in flight
+// together, and kept in registers for both statistics and the output; wider rows are read three times.
 __device__ void layernorm_to_smem(const float* x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                   int n_rows, int width, __nv_bfloat16* act_s, int ld, int k_pad) {
+    constexpr int kVecs = 16;                       // float4 per lane held in registers
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool in_regs = width % 4 == 0 && width <= kVecs * 32 * 4;
     for (int r = warp; r < n_rows; r += kWarps) {
         const float* row = x + (size_t)r * width;
-        float sum = 0.0f;
-        for (int i = lane; i < width; i += 32) sum += __ldcg(row + i);
-        const float mean = warp_sum(sum) / (float)width;
-        float ss = 0.0f;
-        for (int i = lane; i < width; i += 32) {
-            const float d = __ldcg(row + i) - mean;
-            ss = fmaf(d, d, ss);
-        }
-        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
-        for (int i = lane; i < k_pad; i += 32) {
-            float v = 0.0f;
-            if (i < width) {
-                v = (__ldcg(row + i) - mean) * inv;
-                if (w != nullptr) v *= w[i];
-                if (b != nullptr) v += b[i];
+        __nv_bfloat16* dst = act_s + r * ld;
+        if (in_regs) {
+            const int n_vec = width / 4;
+            float4 v[kVecs];
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int i = lane + 32 * j;
+                v[j] = i < n_vec ? __ldcg(reinterpret_cast<const float4*>(row) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            act_s[r * ld + i] = __float2bfloat16_rn(v);
+            float sum = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+            const float mean = warp_sum(sum) / (float)width;
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                if (lane + 32 * j < n_vec) {
+                    const float d0 = v[j].x - mean, d1 = v[j].y - mean, d2 = v[j].z - mean, d3 = v[j].w - mean;
+                    ss = fmaf(d0, d0, ss);
+                    ss = fmaf(d1, d1, ss);
+                    ss = fmaf(d2, d2, ss);
+                    ss = fmaf(d3, d3, ss);
+                }
+            }
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
+#pragma unroll
+            for (int j = 0; j < kVecs; ++j) {
+                const int i = lane + 32 * j;
+                if (i < n_vec) {
+                    float4 g = make_float4(1.f, 1.f, 1.f, 1.f), o = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (w != nullptr) g = __ldg(reinterpret_cast<const float4*>(w) + i);
+                    if (b != nullptr) o = __ldg(reinterpret_cast<const float4*>(b) + i);
+                    const __nv_bfloat162 lo = __floats2bfloat162_rn((v[j].x - mean) * inv * g.x + o.x, (v[j].y - mean) * inv * g.y + o.y);
+                    const __nv_bfloat162 hi = __floats2bfloat162_rn((v[j].z - mean) * inv * g.z + o.z, (v[j].w - mean) * inv * g.w + o.w);
+                    uint2 packed;
+                    packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                    packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                    *reinterpret_cast<uint2*>(dst + 4 * i) = packed;
+                }
+            }
+            for (int i = width + lane; i < k_pad; i += 32) dst[i] = __float2bfloat16_rn(0.0f);
+        } else {
+            float sum = 0.0f;
+            for (int i = lane; i < width; i += 32) sum += __ldcg(row + i);
+            const float mean = warp_sum(sum) / (float)width;
+            float ss = 0.0f;
+            for (int i = lane; i < width; i += 32) {
+                const float d = __ldcg(row + i) - mean;
+                ss = fmaf(d, d, ss);
+            }
+            const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
+            for (int i = lane; i < k_pad; i += 32) {
+                float y = 0.0f;
+                if (i < width) {
+                    y = (__ldcg(row + i) - mean) * inv;
+                    if (w != nullptr) y *= w[i];
+                    if (b != nullptr) y += b[i];
+                }
+                dst[i] = __float2bfloat16_rn(y);
+            }
         }
     }
+}
+
+// Asks L2 for this block's slice of a weight matrix (the rows gemm_phase will give it), one request per
+// 128 bytes.  Issued a phase or two ahead, so that the slice streams from HBM while other work runs and the
+// matrix phase finds it in L2.
+__device__ void prefetch_slice(const __nv_bfloat16* __restrict__ W, int N, int K) {
+    const int n_groups = (N + 7) / 8;
+    const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int f0 = min(N, (int)blockIdx.x * per_cta * 8), f1 = min(N, f0 + per_cta * 8);
+    const char* base = reinterpret_cast<const char*>(W + (size_t)f0 * K);
+    const size_t bytes = (size_t)(f1 - f0) * K * sizeof(__nv_bfloat16);
+    for (size_t off = (size_t)threadIdx.x * 128; off < bytes; off += (size_t)kThreads * 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
 }
 
 // Rows of a bfloat16 matrix written by other blocks -> shared memory, the tail up to k_pad zeroed.
@@ -200,16 +266,33 @@ __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, co
         float acc[kGC][4];
 #pragma unroll
         for (int i = 0; i < kGC; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
-        if (ng <= 2) {
-            // Few features, long K: four k-blocks of both groups are requested before the first is used.
+        if (ng == 1) {
+            // One group, long K: eight k-blocks are requested before the first is used.
+            for (int kb = kb0; kb < kb1; kb += 8) {
+                uint4 w[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    w[u] = kb + u < kb1 ? load_w(W, N, K, gp * 8 + g, (kb + u) * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (kb + u < kb1) {
+                        const uint4 lo = *reinterpret_cast<const uint4*>(a_lo + (kb + u) * 32);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + (kb + u) * 32);
+                        mma_bf16(acc[0], lo.x, hi.x, lo.y, hi.y, w[u].x, w[u].y);
+                        mma_bf16(acc[0], lo.z, hi.z, lo.w, hi.w, w[u].z, w[u].w);
+                    }
+                }
+            }
+        } else if (ng == 2) {
+            // Two groups: four k-blocks of both are requested before the first is used.
             for (int kb = kb0; kb < kb1; kb += 4) {
                 uint4 w[2][4];
 #pragma unroll
                 for (int gi = 0; gi < 2; ++gi)
 #pragma unroll
                     for (int u = 0; u < 4; ++u)
-                        w[gi][u] = (gi < ng && kb + u < kb1) ? load_w(W, N, K, (gp + gi) * 8 + g, (kb + u) * 32 + t * 8)
-                                                            : make_uint4(0, 0, 0, 0);
+                        w[gi][u] = kb + u < kb1 ? load_w(W, N, K, (gp + gi) * 8 + g, (kb + u) * 32 + t * 8)
+                                                : make_uint4(0, 0, 0, 0);
 #pragma unroll
                 for (int u = 0; u < 4; ++u) {
                     if (kb + u < kb1) {
@@ -217,6 +300,29 @@ __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, co
                         const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + (kb + u) * 32);
 #pragma unroll
                         for (int gi = 0; gi < 2; ++gi) {
+                            mma_bf16(acc[gi], lo.x, hi.x, lo.y, hi.y, w[gi][u].x, w[gi][u].y);
+                            mma_bf16(acc[gi], lo.z, hi.z, lo.w, hi.w, w[gi][u].z, w[gi][u].w);
+                        }
+                    }
+                }
+            }
+        } else if (ng <= 4) {
+            // Up to four groups: two k-blocks of all of them are requested before the first is used.
+            for (int kb = kb0; kb < kb1; kb += 2) {
+                uint4 w[4][2];
+#pragma unroll
+                for (int gi = 0; gi < 4; ++gi)
+#pragma unroll
+                    for (int u = 0; u < 2; ++u)
+                        w[gi][u] = (gi < ng && kb + u < kb1) ? load_w(W, N, K, (gp + gi) * 8 + g, (kb + u) * 32 + t * 8)
+                                                            : make_uint4(0, 0, 0, 0);
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+                    if (kb + u < kb1) {
+                        const uint4 lo = *reinterpret_cast<const uint4*>(a_lo + (kb + u) * 32);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + (kb + u) * 32);
+#pragma unroll
+                        for (int gi = 0; gi < 4; ++gi) {
                             if (gi < ng) {
                                 mma_bf16(acc[gi], lo.x, hi.x, lo.y, hi.y, w[gi][u].x, w[gi][u].y);
                                 mma_bf16(acc[gi], lo.z, hi.z, lo.w, hi.w, w[gi][u].z, w[gi][u].w);
@@ -285,7 +391,7 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 // Attention of every (token, head) over its pages; work items (token, head, key range) go round-robin to the blocks.
 template <int HD>
 __device__ void attention_phase(const StackParams& p, const StackLayer& L, float* att_s) {
-    constexpr int TPK = HD / 8, KPW = 32 / TPK, STATE = HD + 2, U = 4;
+    constexpr int TPK = HD / 8, KPW = 32 / TPK, STATE = HD + 2, U = 8;
     __shared__ int last_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane % TPK, kgroup = lane / TPK;
     const int B = p.n_tokens, H = L.n_head, G = H / L.n_kv_head, splits = p.n_splits;
@@ -430,6 +536,11 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
     float* att_s = red_s + kWarps * kGC * 128;
     const int B = p.n_tokens, d = p.width, ld = p.act_ld;
     unsigned epoch = 0;
+    if (p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        p.timing[0] = now;
+    }
 
     // Embedding (+ learned position) into the residual stream.
     for (int idx = blockIdx.x * kThreads + threadIdx.x; idx < B * d; idx += gridDim.x * kThreads) {
@@ -447,6 +558,8 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
         const int code = (li + 1) << 4;
 
         // LayerNorm 1, fused projection, keys and values into their pages.
+        prefetch_slice(L.w_qkv, qd + 2 * kvd, d);
+        prefetch_slice(L.w_out, d, qd);
         layernorm_to_smem(p.x, L.ln1_w, L.ln1_b, L.ln1_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
         __syncthreads();
         gemm_phase(L.w_qkv, qd + 2 * kvd, d, act_s, ld, red_s, B, [&](int b, int f, float v) {
@@ -481,6 +594,9 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
         if (!grid_sync(p, epoch, code | 3)) return;
 
         // LayerNorm 2, up projection, activation.
+        prefetch_slice(L.w_up, L.inner, d);
+        prefetch_slice(L.w_down, d, L.inner);
+        if (li + 1 == p.n_layers) prefetch_slice(p.head_w, p.vocab, d);
         layernorm_to_smem(p.x, L.ln2_w, L.ln2_b, L.ln2_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
         __syncthreads();
         gemm_phase(L.w_up, L.inner, d, act_s, ld, red_s, B, [&](int b, int f, float v) {
@@ -527,7 +643,7 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
                                const int32_t* tokens, const int32_t* positions, const int32_t* block_table,
                                int table_stride, const int32_t* slot_mapping, int page_size, float* x, void* q, void* att,
                                void* inner, float* partial, int* counters, float* logits, unsigned* barrier, int max_k,
-                               int head_dim, int n_splits, void* stream) {
+                               int head_dim, int n_splits, unsigned long long* timing, void* stream) {
     LB_CHECK_ARG(n_layers >= 0 && n_tokens >= 1 && n_tokens <= kMaxTokens, "decode stack: %d tokens (1..%d are taken)", n_tokens,
                  kMaxTokens);
     LB_CHECK_ARG(width > 0 && width % 8 == 0 && max_k >= width && max_k % 8 == 0 && vocab > 0,
@@ -576,6 +692,7 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
     LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&status, g_stack_status));
     p.status = status;
     p.n_splits = n_splits;
+    p.timing = timing;
     p.act_ld = (max_k + 63) / 64 * 64 + 32;       // row stride = 64 bytes mod 128: conflict-free 16-byte reads
     const size_t smem = (size_t)kMaxTokens * p.act_ld * sizeof(__nv_bfloat16) + (size_t)kWarps * kGC * 128 * sizeof(float) +
                         (size_t)kWarps * (128 + 2) * sizeof(float);

@@ -34,7 +34,7 @@ _c = ctypes
 _p, _i, _f = _c.c_void_p, _c.c_int, _c.c_float
 
 ops.declare("lb_decode_stack", [_p, _i, _i, _i, _i, _p, _p, _f, _p, _p, _f, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _p,
-                                _p, _p, _p, _p, _i, _i, _i, _p])
+                                _p, _p, _p, _p, _i, _i, _i, _p, _p])
 ops.declare("lb_decode_stack_status", [_p])
 ops.declare("lb_decode_stack_layer_bytes", [])
 
@@ -114,13 +114,16 @@ class FusedDecodeStack:
         self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
         self.pos_table = getattr(model.position, "table", None)
         self.launches = 0
+        self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
+        self.timing: Optional[torch.Tensor] = None     # int64 [2 + 5 * layers + 1] when phase stamps are wanted
 
     def accepts(self, n_tokens: int) -> bool:
         return 1 <= n_tokens <= MAX_TOKENS
 
     def splits(self, n_tokens: int) -> int:
-        """Key ranges per (token, head): about two work items per SM, a function of the batch's shape only."""
-        return max(1, min(32, -(-296 // (n_tokens * self.max_heads))))
+        """Key ranges per (token, head): as many as give every SM at most one work item, a function of the
+        batch's shape only."""
+        return max(1, min(32, self.n_sm // (n_tokens * self.max_heads)))
 
     def run(self, ctx: StepContext) -> torch.Tensor:
         m, spec = self.model, self.model.spec
@@ -133,7 +136,7 @@ class FusedDecodeStack:
             ctx.positions.data_ptr(), view.block_table.data_ptr(), view.block_table.stride(0), view.slot_mapping.data_ptr(),
             self.cache.page_size, self.x.data_ptr(), self.q.data_ptr(), self.att.data_ptr(), self.inner.data_ptr(),
             self.partial.data_ptr(), self.counters.data_ptr(), self.logits.data_ptr(), self.barrier.data_ptr(), self.max_k,
-            self.head_dim, self.splits(B), ops.stream_ptr()), "decode_stack")
+            self.head_dim, self.splits(B), _ptr(self.timing), ops.stream_ptr()), "decode_stack")
         self.launches += 1
         return self.logits[:B]
 
