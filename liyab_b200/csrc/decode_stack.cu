@@ -111,22 +111,25 @@ __device__ bool grid_sync(const StackParams& p, unsigned& epoch, int phase_code)
     if (threadIdx.x == 0) {
         ++epoch;
         const unsigned target = epoch * gridDim.x;
-        __threadfence();
-        atomicAdd(p.barrier, 1u);
+        // The release on the add publishes what this block wrote before the barrier (the block-wide
+        // barrier above ordered its threads' writes before this thread); the acquire on the load makes
+        // the other blocks' writes visible to everything after the barrier.
+        asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.barrier) : "memory");
         int ok = 1;
         const long long t0 = clock64();
-        for (;;) {
+        for (unsigned spins = 1;; ++spins) {
             unsigned seen;
             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(seen) : "l"(p.barrier) : "memory");
             if (seen >= target) break;
-            if (*(volatile int*)p.status != 0) { ok = 0; break; }
-            if (clock64() - t0 > kSpinLimit) {
-                atomicCAS(p.status, 0, phase_code);
-                ok = 0;
-                break;
+            if ((spins & 1023u) == 0) {
+                if (*(volatile int*)p.status != 0) { ok = 0; break; }
+                if (clock64() - t0 > kSpinLimit) {
+                    atomicCAS(p.status, 0, phase_code);
+                    ok = 0;
+                    break;
+                }
             }
         }
-        __threadfence();
         ok_s = ok;
         if (p.timing != nullptr && blockIdx.x == 0) {
             unsigned long long now;
@@ -140,6 +143,15 @@ __device__ bool grid_sync(const StackParams& p, unsigned& epoch, int phase_code)
     return ok_s != 0;
 }
 
+// Optional fine-grained stamps of block 0 (work done before a barrier, staging done, ...), after the barrier stamps.
+__device__ __forceinline__ void stamp(const StackParams& p, int slot) {
+    if (p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        p.timing[slot] = now;
+    }
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -147,11 +159,11 @@ __device__ __forceinline__ float warp_sum(float v) {
 }
 
 // Rows of x (float32, written by other blocks: read through L2) -> LayerNorm -> bfloat16 rows in shared memory.
-// One warp per row.  Up to 2048 columns the row is fetched once, as 16-byte loads that are all in flight
+// One warp per row.  Up to 1024 columns the row is fetched once, as 16-byte loads that are all in flight
 // together, and kept in registers for both statistics and the output; wider rows are read three times.
 __device__ void layernorm_to_smem(const float* x, const float* __restrict__ w, const float* __restrict__ b, float eps,
                                   int n_rows, int width, __nv_bfloat16* act_s, int ld, int k_pad) {
-    constexpr int kVecs = 16;                       // float4 per lane held in registers
+    constexpr int kVecs = 8;                        // float4 per lane held in registers (row, gains, offsets)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const bool in_regs = width % 4 == 0 && width <= kVecs * 32 * 4;
     for (int r = warp; r < n_rows; r += kWarps) {
@@ -159,11 +171,15 @@ __device__ void layernorm_to_smem(const float* x, const float* __restrict__ w, c
         __nv_bfloat16* dst = act_s + r * ld;
         if (in_regs) {
             const int n_vec = width / 4;
-            float4 v[kVecs];
+            // The row, the gains and the offsets are all requested before anything is used: one round trip.
+            float4 v[kVecs], gain[kVecs], offs[kVecs];
 #pragma unroll
             for (int j = 0; j < kVecs; ++j) {
                 const int i = lane + 32 * j;
-                v[j] = i < n_vec ? __ldcg(reinterpret_cast<const float4*>(row) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                const bool in = i < n_vec;
+                v[j] = in ? __ldcg(reinterpret_cast<const float4*>(row) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+                gain[j] = (in && w != nullptr) ? __ldg(reinterpret_cast<const float4*>(w) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+                offs[j] = (in && b != nullptr) ? __ldg(reinterpret_cast<const float4*>(b) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
             float sum = 0.0f;
 #pragma unroll
@@ -185,9 +201,7 @@ __device__ void layernorm_to_smem(const float* x, const float* __restrict__ w, c
             for (int j = 0; j < kVecs; ++j) {
                 const int i = lane + 32 * j;
                 if (i < n_vec) {
-                    float4 g = make_float4(1.f, 1.f, 1.f, 1.f), o = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (w != nullptr) g = __ldg(reinterpret_cast<const float4*>(w) + i);
-                    if (b != nullptr) o = __ldg(reinterpret_cast<const float4*>(b) + i);
+                    const float4 g = gain[j], o = offs[j];
                     const __nv_bfloat162 lo = __floats2bfloat162_rn((v[j].x - mean) * inv * g.x + o.x, (v[j].y - mean) * inv * g.y + o.y);
                     const __nv_bfloat162 hi = __floats2bfloat162_rn((v[j].z - mean) * inv * g.z + o.z, (v[j].w - mean) * inv * g.w + o.w);
                     uint2 packed;
@@ -235,6 +249,7 @@ __device__ void prefetch_slice(const __nv_bfloat16* __restrict__ W, int N, int K
 
 // Rows of a bfloat16 matrix written by other blocks -> shared memory, the tail up to k_pad zeroed.
 __device__ void rows_to_smem(const __nv_bfloat16* src, int n_rows, int width, __nv_bfloat16* act_s, int ld, int k_pad) {
+    // Stores go to shared memory, so the compiler is free to request the loads of several trips ahead of them.
     const int chunks = k_pad / 8;
     for (int idx = threadIdx.x; idx < n_rows * chunks; idx += kThreads) {
         const int r = idx / chunks, c = idx - r * chunks;
@@ -249,10 +264,12 @@ __device__ __forceinline__ uint4 load_w(const __nv_bfloat16* __restrict__ W, int
     return make_uint4(0, 0, 0, 0);
 }
 
-// out[b, f] = sum_k act[b, k] * W[f, k] for this block's slice of the features; epi(b, f, value) finishes an element.
-template <typename Epi>
+// out[b, f] = sum_k act[b, k] * W[f, k] for this block's slice of the features.  An element (b, f) is finished by
+// post(b, f, value, pre(b, f)); pre() is called before the weights are streamed, so whatever it loads from global
+// memory (a bias, the residual) travels together with the weights instead of after them.
+template <typename Pre, typename Post>
 __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, const __nv_bfloat16* act_s, int ld,
-                           float* red_s, int n_tokens, Epi epi) {
+                           float* red_s, int n_tokens, Pre pre, Post post) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n_groups = (N + 7) / 8;
     const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -263,6 +280,13 @@ __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, co
     const __nv_bfloat16* a_hi = a_lo + 8 * ld;
     for (int gp = g_begin; gp < g_end; gp += kGC) {
         const int ng = min(kGC, g_end - gp);
+        float2 early[kGC * 128 / kThreads];
+#pragma unroll
+        for (int e = 0; e < kGC * 128 / kThreads; ++e) {
+            const int idx = threadIdx.x + e * kThreads;
+            const int gi = idx >> 7, r = (idx >> 3) & 15, f = (gp + gi) * 8 + (idx & 7);
+            early[e] = (idx < ng * 128 && r < n_tokens && f < N) ? pre(r, f) : make_float2(0.f, 0.f);
+        }
         float acc[kGC][4];
 #pragma unroll
         for (int i = 0; i < kGC; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.0f;
@@ -362,13 +386,17 @@ __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, co
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < ng * 128; idx += kThreads) {
-            const int gi = idx >> 7, r = (idx >> 3) & 15, c = idx & 7;
-            float v = 0.0f;
 #pragma unroll
-            for (int w = 0; w < kWarps; ++w) v += red_s[(w * kGC + gi) * 128 + r * 8 + c];
-            const int f = (gp + gi) * 8 + c;
-            if (r < n_tokens && f < N) epi(r, f, v);
+        for (int e = 0; e < kGC * 128 / kThreads; ++e) {
+            const int idx = threadIdx.x + e * kThreads;
+            if (idx < ng * 128) {
+                const int gi = idx >> 7, r = (idx >> 3) & 15, c = idx & 7;
+                float v = 0.0f;
+#pragma unroll
+                for (int w = 0; w < kWarps; ++w) v += red_s[(w * kGC + gi) * 128 + r * 8 + c];
+                const int f = (gp + gi) * 8 + c;
+                if (r < n_tokens && f < N) post(r, f, v, early[e]);
+            }
         }
         __syncthreads();
     }
@@ -389,24 +417,34 @@ __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
 }
 
 // Attention of every (token, head) over its pages; work items (token, head, key range) go round-robin to the blocks.
+// `table_s` holds the block-table rows of this block's first kCachedItems work items and `pos_s` the tokens'
+// positions, copied once per step (they are the same for every layer) when `cached_heads` equals the layer's heads.
+constexpr int kCachedItems = 2;
+
 template <int HD>
-__device__ void attention_phase(const StackParams& p, const StackLayer& L, float* att_s) {
+__device__ void attention_phase(const StackParams& p, const StackLayer& L, float* att_s, const int32_t* table_s,
+                                const int32_t* pos_s, int cached_heads) {
     constexpr int TPK = HD / 8, KPW = 32 / TPK, STATE = HD + 2, U = 8;
     __shared__ int last_s;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, sub = lane % TPK, kgroup = lane / TPK;
     const int B = p.n_tokens, H = L.n_head, G = H / L.n_kv_head, splits = p.n_splits;
     const int qd = H * HD, page_size = 1 << p.page_shift;
     const size_t plane = (size_t)L.n_kv_head * page_size * HD;
-    for (int item = blockIdx.x; item < B * H * splits; item += gridDim.x) {
+    int item_slot = 0;
+    for (int item = blockIdx.x; item < B * H * splits; item += gridDim.x, ++item_slot) {
         const int split = item % splits, bh = item / splits, h = bh % H, b = bh / H, kvh = h / G;
-        const int pos = p.positions[b];
+        const int pos = pos_s[b];
         const int first = L.window > 0 ? max(0, pos - L.window + 1) : 0;
         const int n_keys = pos + 1 - first;
         const int chunk = (n_keys + splits - 1) / splits;
         const int begin = first + split * chunk, end = min(pos + 1, begin + chunk);
-        const int32_t* table = p.block_table + (size_t)b * p.table_stride;
+        const uint4 q_raw = __ldcg(reinterpret_cast<const uint4*>(p.q + (size_t)b * qd + (size_t)h * HD + sub * 8));
+        // Page ids: from the rows copied to shared memory at the start of the step, else from global memory.
+        const int32_t* table = (cached_heads == H && item_slot < kCachedItems)
+                                   ? table_s + (size_t)item_slot * p.table_stride
+                                   : p.block_table + (size_t)b * p.table_stride;
         float qf[8];
-        unpack8(__ldcg(reinterpret_cast<const uint4*>(p.q + (size_t)b * qd + (size_t)h * HD + sub * 8)), qf);
+        unpack8(q_raw, qf);
 #pragma unroll
         for (int i = 0; i < 8; ++i) qf[i] *= L.scale * kLog2e;
         float m = -CUDART_INF_F, l = 0.0f, acc[8];
@@ -534,12 +572,26 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
     __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
     float* red_s = reinterpret_cast<float*>(smem_bytes + (size_t)kMaxTokens * p.act_ld * sizeof(__nv_bfloat16));
     float* att_s = red_s + kWarps * kGC * 128;
+    int32_t* pos_s = reinterpret_cast<int32_t*>(att_s + kWarps * (128 + 2));       // [kMaxTokens] positions
+    int32_t* table_s = pos_s + kMaxTokens;                                          // [kCachedItems][table_stride] page ids
     const int B = p.n_tokens, d = p.width, ld = p.act_ld;
     unsigned epoch = 0;
     if (p.timing != nullptr && blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long now;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
         p.timing[0] = now;
+    }
+
+    // Positions and the block-table rows of this block's attention work items: the same for every layer.
+    const int cached_heads = p.n_layers > 0 ? p.layers[0].n_head : 0;
+    for (int i = threadIdx.x; i < B; i += kThreads) pos_s[i] = p.positions[i];
+    for (int slot = 0; slot < kCachedItems; ++slot) {
+        const int item = blockIdx.x + slot * gridDim.x;
+        if (item < B * cached_heads * p.n_splits) {
+            const int b = item / p.n_splits / cached_heads;
+            for (int i = threadIdx.x; i < p.table_stride; i += kThreads)
+                table_s[(size_t)slot * p.table_stride + i] = p.block_table[(size_t)b * p.table_stride + i];
+        }
     }
 
     // Embedding (+ learned position) into the residual stream.
@@ -558,18 +610,23 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
         const int code = (li + 1) << 4;
 
         // LayerNorm 1, fused projection, keys and values into their pages.
+        stamp(p, 128 + li * 8 + 4);
         prefetch_slice(L.w_qkv, qd + 2 * kvd, d);
         prefetch_slice(L.w_out, d, qd);
+        stamp(p, 128 + li * 8 + 5);
         layernorm_to_smem(p.x, L.ln1_w, L.ln1_b, L.ln1_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
         __syncthreads();
-        gemm_phase(L.w_qkv, qd + 2 * kvd, d, act_s, ld, red_s, B, [&](int b, int f, float v) {
-            if (L.b_qkv != nullptr) v += L.b_qkv[f];
+        stamp(p, 128 + li * 8 + 0);
+        gemm_phase(L.w_qkv, qd + 2 * kvd, d, act_s, ld, red_s, B, [&](int b, int f) {
+            return make_float2(L.b_qkv != nullptr ? __ldg(L.b_qkv + f) : 0.0f, __int_as_float(f >= qd ? __ldg(p.slot_mapping + b) : 0));
+        }, [&](int b, int f, float v, float2 e) {
+            v += e.x;
             if (f < qd) {
                 p.q[(size_t)b * qd + f] = __float2bfloat16_rn(v);
             } else {
                 const int kvf = f - qd, which = kvf >= kvd ? 1 : 0, within = kvf - which * kvd;
                 const int head = within / hd, dd = within - head * hd;
-                const int slot = p.slot_mapping[b];
+                const int slot = __float_as_int(e.y);
                 if (slot >= 0) {
                     const int page = slot >> p.page_shift, off = slot & (page_size - 1);
                     L.cache[(size_t)page * 2 * plane + (size_t)which * plane + ((size_t)head * page_size + off) * hd + dd] =
@@ -577,20 +634,21 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
                 }
             }
         });
+        stamp(p, 128 + li * 8 + 1);
         if (!grid_sync(p, epoch, code | 1)) return;
 
-        if (hd == 64) attention_phase<64>(p, L, att_s);
-        else attention_phase<128>(p, L, att_s);
+        if (hd == 64) attention_phase<64>(p, L, att_s, table_s, pos_s, cached_heads);
+        else attention_phase<128>(p, L, att_s, table_s, pos_s, cached_heads);
+        stamp(p, 128 + li * 8 + 2);
         if (!grid_sync(p, epoch, code | 2)) return;
 
         // Output projection + residual.
         rows_to_smem(p.att, B, qd, act_s, ld, (qd + 63) / 64 * 64);
         __syncthreads();
-        gemm_phase(L.w_out, d, qd, act_s, ld, red_s, B, [&](int b, int f, float v) {
-            if (L.b_out != nullptr) v += L.b_out[f];
-            float* dst = p.x + (size_t)b * d + f;
-            *dst = __ldcg(dst) + v;
-        });
+        gemm_phase(L.w_out, d, qd, act_s, ld, red_s, B, [&](int b, int f) {
+            return make_float2(L.b_out != nullptr ? __ldg(L.b_out + f) : 0.0f, __ldcg(p.x + (size_t)b * d + f));
+        }, [&](int b, int f, float v, float2 e) { p.x[(size_t)b * d + f] = e.y + (v + e.x); });
+        stamp(p, 128 + li * 8 + 3);
         if (!grid_sync(p, epoch, code | 3)) return;
 
         // LayerNorm 2, up projection, activation.
@@ -599,30 +657,28 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
         if (li + 1 == p.n_layers) prefetch_slice(p.head_w, p.vocab, d);
         layernorm_to_smem(p.x, L.ln2_w, L.ln2_b, L.ln2_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
         __syncthreads();
-        gemm_phase(L.w_up, L.inner, d, act_s, ld, red_s, B, [&](int b, int f, float v) {
-            if (L.b_up != nullptr) v += L.b_up[f];
-            p.inner[(size_t)b * L.inner + f] = __float2bfloat16_rn(lb_activate(v, L.act));
+        gemm_phase(L.w_up, L.inner, d, act_s, ld, red_s, B, [&](int b, int f) {
+            return make_float2(L.b_up != nullptr ? __ldg(L.b_up + f) : 0.0f, 0.0f);
+        }, [&](int b, int f, float v, float2 e) {
+            p.inner[(size_t)b * L.inner + f] = __float2bfloat16_rn(lb_activate(v + e.x, L.act));
         });
         if (!grid_sync(p, epoch, code | 4)) return;
 
         // Down projection + residual.
         rows_to_smem(p.inner, B, L.inner, act_s, ld, (L.inner + 63) / 64 * 64);
         __syncthreads();
-        gemm_phase(L.w_down, d, L.inner, act_s, ld, red_s, B, [&](int b, int f, float v) {
-            if (L.b_down != nullptr) v += L.b_down[f];
-            float* dst = p.x + (size_t)b * d + f;
-            *dst = __ldcg(dst) + v;
-        });
+        gemm_phase(L.w_down, d, L.inner, act_s, ld, red_s, B, [&](int b, int f) {
+            return make_float2(L.b_down != nullptr ? __ldg(L.b_down + f) : 0.0f, __ldcg(p.x + (size_t)b * d + f));
+        }, [&](int b, int f, float v, float2 e) { p.x[(size_t)b * d + f] = e.y + (v + e.x); });
         if (!grid_sync(p, epoch, code | 5)) return;
     }
 
     // Final norm and the head.
     layernorm_to_smem(p.x, p.lnf_w, p.lnf_b, p.lnf_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
     __syncthreads();
-    gemm_phase(p.head_w, p.vocab, d, act_s, ld, red_s, B, [&](int b, int f, float v) {
-        if (p.head_b != nullptr) v += p.head_b[f];
-        p.logits[(size_t)b * p.vocab + f] = v;
-    });
+    gemm_phase(p.head_w, p.vocab, d, act_s, ld, red_s, B, [&](int b, int f) {
+        return make_float2(p.head_b != nullptr ? __ldg(p.head_b + f) : 0.0f, 0.0f);
+    }, [&](int b, int f, float v, float2 e) { p.logits[(size_t)b * p.vocab + f] = v + e.x; });
 }
 
 int g_sm_count = 0;
@@ -695,7 +751,7 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
     p.timing = timing;
     p.act_ld = (max_k + 63) / 64 * 64 + 32;       // row stride = 64 bytes mod 128: conflict-free 16-byte reads
     const size_t smem = (size_t)kMaxTokens * p.act_ld * sizeof(__nv_bfloat16) + (size_t)kWarps * kGC * 128 * sizeof(float) +
-                        (size_t)kWarps * (128 + 2) * sizeof(float);
+                        (size_t)kWarps * (128 + 2) * sizeof(float) + (size_t)(kMaxTokens + kCachedItems * table_stride) * sizeof(int32_t);
     LB_CHECK_ARG(smem <= 227 * 1024, "decode stack: a reduction length of %d needs %zu bytes of shared memory, the SM has 232448",
                  max_k, smem);
     static size_t configured = 0;
