@@ -60,7 +60,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
         except OSError:
             self.proc = None
@@ -72,7 +72,7 @@ class ClockSampler:
     def stop(self):
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=2)
@@ -98,7 +98,7 @@ def model_bytes_and_flops(cfg, n_layers, dtype_bytes):
     return weight_bytes, kv_per_pos, prefill_flops
 
 
-def decode_run(model_dir, dtype, batch, steps, warmup, count_launches=False):
+def decode_run(model_dir, dtype, batch, steps, warmup, clocks=None):
     """Device-timed decode: K steps of `batch` requests after 512-token prompts; returns a dict of measurements."""
     import numpy as np
     import torch
@@ -138,6 +138,10 @@ def decode_run(model_dir, dtype, batch, steps, warmup, count_launches=False):
 
     for _ in range(warmup):
         one_step()
+    if clocks is not None:          # clocks are sampled while the timed steps run, not while the model loads
+        clocks.start()
+        for _ in range(max(warmup, 20)):
+            one_step()
     ctx_sum = 0
     ops.LAUNCHES = 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -150,12 +154,14 @@ def decode_run(model_dir, dtype, batch, steps, warmup, count_launches=False):
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3
     ms = start.elapsed_time(end)
+    clock_info = clocks.stop() if clocks is not None else None
     per_graph = getattr(stepper, "graph_launches", {}).get(batch, 0)
     launches = ops.LAUNCHES + per_graph * steps
     for r in ids:
         cache.close(r)
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "mean_ctx": ctx_sum / (steps * batch),
-            "launches": launches, "wall_ms_per_step": wall_ms / steps, "weight_bytes": model.weight_bytes()}
+            "launches": launches, "wall_ms_per_step": wall_ms / steps, "weight_bytes": model.weight_bytes(),
+            "clocks": clock_info, "fused_steps": stepper.fused_steps, "graph_steps": stepper.graph_steps}
 
 
 def prefill_run(model_dir, dtype, repeats=5):
@@ -232,10 +238,8 @@ def main() -> int:
     pk = peaks()
     with tempfile.TemporaryDirectory(prefix="liyab_b200_bench_") as tmp:
         model_dir = write_random_model(os.path.join(tmp, "gpt2_small"), parse_config(cfg), seed=0, dtype=args.dtype)
-        clocks = ClockSampler()
-        clocks.start()
-        main_run = decode_run(model_dir, args.dtype, args.batch, args.steps, args.warmup)
-        clock_info = clocks.stop()
+        main_run = decode_run(model_dir, args.dtype, args.batch, args.steps, args.warmup, clocks=ClockSampler())
+        clock_info = main_run["clocks"]
         weight_bytes, kv_per_pos, prefill_flops = model_bytes_and_flops(cfg, args.layers, dtype_bytes)
         step_bytes = weight_bytes + args.batch * main_run["mean_ctx"] * kv_per_pos
         achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
@@ -250,7 +254,7 @@ def main() -> int:
                        "n_positions": cfg["n_positions"], "global_batch": args.batch, "seq_len": 1024,
                        "prompt_len": PROMPT_LEN, "mean_context": round(main_run["mean_ctx"], 1), "page_size": 16,
                        "parallelism": "single-gpu", "l2": "each step reads %.0f MB of weights and cache > 126 MB L2" % (step_bytes / 1e6),
-                       "peaks": pk["source"]},
+                       "peaks": pk["source"], "decode_path": "fused" if main_run["fused_steps"] else "graph"},
             "gpu_launches": main_run["launches"],
             "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": round(achieved / pk["hbm_gbs"], 4)},

@@ -19,13 +19,20 @@ beside the cache in the sequence's context (src/core/transformer.h:854-865,
 1283-1308).  Here one pool serves all requests, which is what lets a finished
 request's pages serve the next one.
 
-Nothing in this file touches a GPU except allocating the storage tensors; all
-bookkeeping is host-side and runs in the CPU tests.
+Bookkeeping is host-side and runs in the CPU tests; only the storage tensors
+live on the GPU.  Every open request has a *row* (its state slot); tables and
+lengths are NumPy arrays indexed by row, so a step of many requests is laid out
+with a handful of array operations (`reserve_rows`, `commit_rows`,
+`table_rows`, `decode_slots`) instead of a Python loop per request.
+
+Invariant of a request's table in a group: logical pages below `released` are
+unmapped for good, pages in [released, n_logical) are all mapped, and nothing
+exists beyond n_logical.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Hashable, Iterable, List, Mapping, Optional, Sequence, Tuple
+from typing import Dict, Hashable, Iterator, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -65,7 +72,7 @@ class PagePool:
             raise invalid_argument(f"a page pool needs at least one page (got {num_pages})")
         self.num_pages = num_pages
         self._free: List[int] = list(range(num_pages - 1, -1, -1))   # pop() hands out 0 first
-        self._held = [False] * num_pages
+        self._held = np.zeros(num_pages, dtype=bool)
 
     @property
     def free_count(self) -> int:
@@ -88,7 +95,7 @@ class PagePool:
         if not (0 <= page < self.num_pages) or not self._held[page]:
             raise LiyabError(ErrorCode.INTERNAL, f"page {page} is given back but not held")
         self._held[page] = False
-        self._free.append(page)
+        self._free.append(int(page))
 
     def check(self) -> None:
         """No page lost, none held twice, none free twice."""
@@ -97,20 +104,43 @@ class PagePool:
         for p in self._free:
             if self._held[p]:
                 raise LiyabError(ErrorCode.INTERNAL, f"page {p} is both free and held")
-        if sum(self._held) + len(self._free) != self.num_pages:
+        if int(self._held.sum()) + len(self._free) != self.num_pages:
             raise LiyabError(ErrorCode.INTERNAL, "a page is lost")
 
 
-class KvGroup:
-    """Units with the same needs: one storage tensor, one free list, one table per request."""
+class _Tables:
+    """Read-only, dictionary-like view of a group's tables: request -> its page ids (a NumPy row)."""
 
-    def __init__(self, need: KvNeed, units: Sequence[int], page_size: int, num_pages: int):
+    def __init__(self, group: "KvGroup", rows: Mapping[Hashable, int]):
+        self._g, self._rows = group, rows
+
+    def __getitem__(self, request: Hashable) -> np.ndarray:
+        row = self._rows[request]
+        return self._g.table[row, :self._g.n_logical[row]]
+
+    def __contains__(self, request: Hashable) -> bool:
+        return request in self._rows
+
+    def items(self) -> Iterator[Tuple[Hashable, np.ndarray]]:
+        return ((r, self[r]) for r in self._rows)
+
+    def __len__(self) -> int:
+        return len(self._rows)
+
+
+class KvGroup:
+    """Units with the same needs: one storage tensor, one free list, one table row per request."""
+
+    def __init__(self, need: KvNeed, units: Sequence[int], page_size: int, num_pages: int, max_requests: int,
+                 rows: Mapping[Hashable, int]):
         self.need = need
         self.units = list(units)
         self.page_size = page_size
         self.pool = PagePool(num_pages)
-        self.tables: Dict[Hashable, List[int]] = {}
-        self._released: Dict[Hashable, int] = {}     # logical pages below this were freed by the window
+        self.table = np.full((max_requests, 16), UNMAPPED, dtype=np.int32)      # columns grow on demand
+        self.n_logical = np.zeros(max_requests, dtype=np.int64)                  # pages a row's table spans
+        self.released = np.zeros(max_requests, dtype=np.int64)                   # pages below this were freed by the window
+        self.tables = _Tables(self, rows)
         self.storage: Optional[torch.Tensor] = None
 
     def unit_index(self, unit: int) -> int:
@@ -127,75 +157,72 @@ class KvGroup:
     def bytes_per_token(self, element_size: int) -> int:
         return 2 * len(self.units) * self.need.n_kv_head * self.need.head_dim * element_size
 
-    # -- per request ------------------------------------------------------
+    # -- by row -------------------------------------------------------------
 
-    def pages_to_map(self, request: Hashable, end: int) -> int:
-        """Pages that `reserve(request, end)` would take."""
-        table = self.tables[request]
-        n_logical = (end + self.page_size - 1) // self.page_size
-        need = 0
-        for i in range(self._released.get(request, 0), n_logical):
-            if i >= len(table) or table[i] == UNMAPPED:
-                need += 1
-        return need
+    def pages_for(self, end: np.ndarray) -> np.ndarray:
+        return (end + self.page_size - 1) // self.page_size
 
-    def reserve(self, request: Hashable, end: int) -> None:
-        """Maps every page that positions < end need; all or nothing."""
-        need = self.pages_to_map(request, end)
-        if need > self.pool.free_count:
-            raise OutOfPages(f"request {request!r} needs {need} more page(s) of {self.page_size} positions, "
-                             f"{self.pool.free_count} of {self.pool.num_pages} are free")
-        table = self.tables[request]
-        n_logical = (end + self.page_size - 1) // self.page_size
-        while len(table) < n_logical:
-            table.append(UNMAPPED)
-        for i in range(self._released.get(request, 0), n_logical):   # released pages are never mapped again
-            if table[i] == UNMAPPED:
-                table[i] = self.pool.take()
+    def need_rows(self, rows: np.ndarray, end: np.ndarray) -> np.ndarray:
+        """Pages each row would take to cover positions < end."""
+        return np.maximum(self.pages_for(end) - np.maximum(self.n_logical[rows], self.released[rows]), 0)
 
-    def release_unreachable(self, request: Hashable, length: int) -> int:
-        """Windowed groups: frees the pages that no query at a position >= length
-        can see (its earliest visible key is length - window + 1)."""
+    def map_rows(self, rows: np.ndarray, end: np.ndarray) -> None:
+        """Maps what `need_rows` counted (the caller has checked that the pool can cover it)."""
+        want = self.pages_for(end)
+        have = self.n_logical[rows]
+        grow = np.nonzero(want > have)[0]
+        if grow.size == 0:
+            return
+        top = int(want.max())
+        if top > self.table.shape[1]:
+            wider = np.full((self.table.shape[0], max(top, 2 * self.table.shape[1])), UNMAPPED, dtype=np.int32)
+            wider[:, :self.table.shape[1]] = self.table
+            self.table = wider
+        for i in grow:
+            row, lo, hi = int(rows[i]), int(have[i]), int(want[i])
+            for j in range(max(lo, int(self.released[row])), hi):      # released pages are never mapped again
+                self.table[row, j] = self.pool.take()
+            self.n_logical[row] = hi
+
+    def release_unreachable_rows(self, rows: np.ndarray, length: np.ndarray) -> None:
+        """Windowed groups: frees the pages that no query at a position >= length can see
+        (its earliest visible key is length - window + 1)."""
         w = self.need.window
         if w <= 0:
-            return 0
-        table = self.tables[request]
-        first_visible = max(0, length - w + 1)
-        n_dead = min(first_visible // self.page_size, len(table))
-        freed = 0
-        for i in range(self._released.get(request, 0), n_dead):
-            if table[i] != UNMAPPED:
-                self.pool.give_back(table[i])
-                table[i] = UNMAPPED
-                freed += 1
-        self._released[request] = max(self._released.get(request, 0), n_dead)
-        return freed
+            return
+        dead = np.minimum(np.maximum(length - w + 1, 0) // self.page_size, self.n_logical[rows])
+        for i in np.nonzero(dead > self.released[rows])[0]:
+            row = int(rows[i])
+            for j in range(int(self.released[row]), int(dead[i])):
+                if self.table[row, j] != UNMAPPED:
+                    self.pool.give_back(int(self.table[row, j]))
+                    self.table[row, j] = UNMAPPED
+            self.released[row] = int(dead[i])
 
-    def truncate(self, request: Hashable, length: int) -> None:
+    def truncate_row(self, row: int, length: int, request: Hashable) -> None:
         """Frees the pages that start at or after `length` (a roll-back)."""
-        if self.need.window > 0 and \
-                self._released.get(request, 0) * self.page_size > max(0, length - self.need.window + 1):
+        if self.need.window > 0 and self.released[row] * self.page_size > max(0, length - self.need.window + 1):
             raise invalid_argument(f"request {request!r} cannot be cut back to {length}: a windowed group has "
                                    f"already released pages that position would need")
-        table = self.tables[request]
         keep = (length + self.page_size - 1) // self.page_size
-        for i in range(keep, len(table)):
-            if table[i] != UNMAPPED:
-                self.pool.give_back(table[i])
-        del table[keep:]
+        for j in range(keep, int(self.n_logical[row])):
+            if self.table[row, j] != UNMAPPED:
+                self.pool.give_back(int(self.table[row, j]))
+                self.table[row, j] = UNMAPPED
+        self.n_logical[row] = min(int(self.n_logical[row]), keep)
 
-    def open(self, request: Hashable) -> None:
-        self.tables[request] = []
-
-    def close(self, request: Hashable) -> None:
-        for page in self.tables.pop(request):
-            if page != UNMAPPED:
-                self.pool.give_back(page)
-        self._released.pop(request, None)
+    def clear_row(self, row: int) -> None:
+        for j in range(int(self.n_logical[row])):
+            if self.table[row, j] != UNMAPPED:
+                self.pool.give_back(int(self.table[row, j]))
+        self.table[row, :] = UNMAPPED
+        self.n_logical[row] = 0
+        self.released[row] = 0
 
 
 class StateSlots:
-    """Slots of fixed size, one per live request, for units that keep state."""
+    """Slots of fixed size, one per live request, for units that keep state.  A request's slot is also its
+    row in the cache manager's tables."""
 
     def __init__(self, needs: Mapping[int, StateNeed], n_slots: int):
         self.needs = dict(needs)
@@ -230,6 +257,9 @@ class CacheManager:
         self.page_size = page_size
         self.max_requests = max_requests
         self.dtype = dtype
+        self.states = StateSlots(state_needs, max_requests)
+        self.row_of = self.states.slot_of                       # request -> row
+        self.length_arr = np.zeros(max_requests, dtype=np.int64)
         by_need: Dict[KvNeed, List[int]] = {}
         for unit in sorted(kv_needs):
             by_need.setdefault(kv_needs[unit], []).append(unit)
@@ -237,12 +267,11 @@ class CacheManager:
         self.group_of_unit: Dict[int, int] = {}
         for need, units in by_need.items():
             n = (pages_per_group or {}).get(need, num_pages)
-            g = KvGroup(need, units, page_size, n)
+            g = KvGroup(need, units, page_size, n, max_requests, self.row_of)
             for u in units:
                 self.group_of_unit[u] = len(self.groups)
             self.groups.append(g)
-        self.states = StateSlots(state_needs, max_requests)
-        self.lengths: Dict[Hashable, int] = {}
+        self.windowed = any(g.need.window > 0 for g in self.groups)
         if device is not None:
             for g in self.groups:
                 g.allocate_storage(dtype, device)
@@ -250,98 +279,127 @@ class CacheManager:
 
     # -- requests -----------------------------------------------------------
 
+    @property
+    def lengths(self) -> Dict[Hashable, int]:
+        return {r: int(self.length_arr[row]) for r, row in self.row_of.items()}
+
     def open(self, request: Hashable) -> None:
-        if request in self.lengths:
+        if request in self.row_of:
             raise LiyabError(ErrorCode.BUSY, f"request {request!r} is already open")
-        if len(self.lengths) >= self.max_requests:
+        if len(self.row_of) >= self.max_requests:
             raise LiyabError(ErrorCode.BUSY, f"{self.max_requests} requests are open already")
-        self.lengths[request] = 0
-        for g in self.groups:
-            g.open(request)
-        self.states.open(request)
+        row = self.states.open(request)
+        self.length_arr[row] = 0
 
     def close(self, request: Hashable) -> None:
-        if request not in self.lengths:
+        if request not in self.row_of:
             raise invalid_argument(f"request {request!r} is not open")
-        del self.lengths[request]
+        row = self.row_of[request]
         for g in self.groups:
-            g.close(request)
+            g.clear_row(row)
+        self.length_arr[row] = 0
         self.states.close(request)
 
     def is_open(self, request: Hashable) -> bool:
-        return request in self.lengths
+        return request in self.row_of
 
     def length(self, request: Hashable) -> int:
-        return self.lengths[request]
+        return int(self.length_arr[self.row_of[request]])
+
+    def rows(self, requests: Sequence[Hashable]) -> np.ndarray:
+        return np.fromiter((self.row_of[r] for r in requests), dtype=np.int64, count=len(requests))
+
+    # -- reserving and committing, by row ---------------------------------------
+
+    def need_rows(self, rows: np.ndarray, n_new: np.ndarray) -> List[int]:
+        """Per group, the pages that appending n_new[i] tokens to row rows[i] would take, summed over the rows."""
+        end = self.length_arr[rows] + n_new
+        return [int(g.need_rows(rows, end).sum()) for g in self.groups]
+
+    def reserve_rows(self, rows: np.ndarray, n_new: np.ndarray) -> None:
+        """Maps pages for positions [length, length + n_new) of every row in every group, or none at all."""
+        end = self.length_arr[rows] + n_new
+        for g in self.groups:
+            need = int(g.need_rows(rows, end).sum())
+            if need > g.pool.free_count:
+                raise OutOfPages(f"{len(rows)} request(s) need {need} more page(s) of {self.page_size} positions; "
+                                 f"{g.pool.free_count} of {g.pool.num_pages} are free")
+        for g in self.groups:
+            g.map_rows(rows, end)
+
+    def commit_rows(self, rows: np.ndarray, n_new: np.ndarray) -> None:
+        """The step ran: the rows are n_new tokens longer; windows move on."""
+        self.length_arr[rows] += n_new
+        if self.windowed:
+            for g in self.groups:
+                g.release_unreachable_rows(rows, self.length_arr[rows])
+
+    # -- the same by request ---------------------------------------------------------
 
     def pages_needed(self, request: Hashable, n_new: int) -> Dict[int, int]:
         """Per group, the pages that appending n_new tokens would take."""
-        end = self.lengths[request] + n_new
-        return {i: g.pages_to_map(request, end) for i, g in enumerate(self.groups)}
+        rows, n = self.rows([request]), np.array([n_new])
+        return dict(enumerate(self.need_rows(rows, n)))
 
     def can_reserve(self, wants: Mapping[Hashable, int]) -> bool:
         """Whether all of {request: n_new} fit the free pages together."""
-        for i, g in enumerate(self.groups):
-            need = sum(g.pages_to_map(r, self.lengths[r] + n) for r, n in wants.items())
-            if need > g.pool.free_count:
-                return False
-        return True
+        if not wants:
+            return True
+        rows = self.rows(list(wants))
+        need = self.need_rows(rows, np.fromiter(wants.values(), dtype=np.int64, count=len(wants)))
+        return all(n <= g.pool.free_count for n, g in zip(need, self.groups))
 
     def reserve(self, request: Hashable, n_new: int) -> None:
-        """Maps pages for positions [length, length + n_new) in every group, or none at all."""
         if n_new <= 0:
             raise invalid_argument(f"request {request!r}: a reservation needs at least one token")
-        end = self.lengths[request] + n_new
-        for g in self.groups:
-            need = g.pages_to_map(request, end)
-            if need > g.pool.free_count:
-                raise OutOfPages(f"request {request!r} needs {need} more page(s) of {self.page_size} positions "
-                                 f"for {end} tokens; {g.pool.free_count} of {g.pool.num_pages} are free")
-        for g in self.groups:
-            g.reserve(request, end)
+        self.reserve_rows(self.rows([request]), np.array([n_new], dtype=np.int64))
 
     def commit(self, request: Hashable, n_new: int) -> None:
-        """The step ran: the request is n_new tokens longer; windows move on."""
-        self.lengths[request] += n_new
-        for g in self.groups:
-            g.release_unreachable(request, self.lengths[request])
+        self.commit_rows(self.rows([request]), np.array([n_new], dtype=np.int64))
 
     def truncate(self, request: Hashable, length: int) -> None:
-        if not (0 <= length <= self.lengths[request]):
-            raise invalid_argument(f"request {request!r} holds {self.lengths[request]} tokens, cannot cut to {length}")
-        if self.states.needs and length != self.lengths[request]:
+        row = self.row_of[request]
+        if not (0 <= length <= self.length_arr[row]):
+            raise invalid_argument(f"request {request!r} holds {int(self.length_arr[row])} tokens, cannot cut to {length}")
+        if self.states.needs and length != self.length_arr[row]:
             raise LiyabError(ErrorCode.UNSUPPORTED, "per-request state cannot be rolled back")
         for g in self.groups:
-            g.truncate(request, length)
-        self.lengths[request] = length
+            g.truncate_row(row, length, request)
+        self.length_arr[row] = length
 
     # -- what a step needs ----------------------------------------------------
 
-    def block_table(self, group: int, requests: Sequence[Hashable], width: Optional[int] = None) -> np.ndarray:
+    def table_rows(self, group: int, rows: np.ndarray, width: Optional[int] = None) -> np.ndarray:
+        """The block tables of `rows`, [len(rows), width] int32 (width: the widest of them unless given)."""
         g = self.groups[group]
-        w = max([len(g.tables[r]) for r in requests] + [1])
+        w = max(int(g.n_logical[rows].max()) if len(rows) else 1, 1)
         if width is not None:
             if width < w:
                 raise invalid_argument(f"block table of width {width} cannot hold {w} pages")
             w = width
-        out = np.full((len(requests), w), UNMAPPED, dtype=np.int32)
-        for i, r in enumerate(requests):
-            t = g.tables[r]
-            out[i, :len(t)] = t
+        if w <= g.table.shape[1]:
+            return g.table[rows, :w]
+        out = np.full((len(rows), w), UNMAPPED, dtype=np.int32)
+        out[:, :g.table.shape[1]] = g.table[rows]
         return out
 
-    def slot_mapping(self, group: int, request: Hashable, start: int, n: int) -> np.ndarray:
-        """Flat slot (page * page_size + offset) of positions start .. start+n-1."""
+    def block_table(self, group: int, requests: Sequence[Hashable], width: Optional[int] = None) -> np.ndarray:
+        return self.table_rows(group, self.rows(requests), width)
+
+    def slots_of(self, group: int, token_rows: np.ndarray, positions: np.ndarray) -> np.ndarray:
+        """Flat slot (page * page_size + offset) of each (row, position) pair."""
         g = self.groups[group]
-        pos = np.arange(start, start + n, dtype=np.int64)
-        table = np.asarray(g.tables[request], dtype=np.int64)
-        pages = table[pos // self.page_size]
+        pages = g.table[token_rows, positions // self.page_size].astype(np.int64)
         if (pages < 0).any():
-            raise LiyabError(ErrorCode.INTERNAL, f"request {request!r}: a position of the step has no page")
-        return (pages * self.page_size + pos % self.page_size).astype(np.int32)
+            raise LiyabError(ErrorCode.INTERNAL, "a position of the step has no page")
+        return (pages * self.page_size + positions % self.page_size).astype(np.int32)
+
+    def slot_mapping(self, group: int, request: Hashable, start: int, n: int) -> np.ndarray:
+        pos = np.arange(start, start + n, dtype=np.int64)
+        return self.slots_of(group, np.full(n, self.row_of[request], dtype=np.int64), pos)
 
     def state_slot(self, request: Hashable) -> int:
-        return self.states.slot_of[request]
+        return self.row_of[request]
 
     # -- accounting -----------------------------------------------------------
 
@@ -356,14 +414,18 @@ class CacheManager:
         return sum(g.bytes_per_token(es) for g in self.groups)
 
     def check(self) -> None:
-        """Invariants: every held page is in exactly one table, pools are consistent."""
+        """Invariants: every held page is in exactly one table, pools are consistent, rows of closed requests are empty."""
+        live = set(self.row_of.values())
         for g in self.groups:
             g.pool.check()
             seen = set()
-            for r, table in g.tables.items():
-                for p in table:
-                    if p == UNMAPPED:
-                        continue
+            for row in range(self.max_requests):
+                pages = g.table[row][g.table[row] != UNMAPPED]
+                if row not in live and pages.size:
+                    raise LiyabError(ErrorCode.INTERNAL, f"row {row} of a closed request still holds pages")
+                if (g.table[row, int(g.n_logical[row]):] != UNMAPPED).any():
+                    raise LiyabError(ErrorCode.INTERNAL, f"row {row} has pages beyond its end")
+                for p in pages.tolist():
                     if p in seen:
                         raise LiyabError(ErrorCode.INTERNAL, f"page {p} is in two tables")
                     seen.add(p)

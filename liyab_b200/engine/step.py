@@ -90,59 +90,65 @@ class Stepper:
 
     # -- validation (no side effects) -------------------------------------------
 
-    def validate(self, entries: Sequence[StepEntry]) -> None:
+    def validate(self, entries: Sequence[StepEntry]):
+        """Checks a step before anything is touched; returns (rows, q_len, tokens) as arrays."""
         if not entries:
             raise invalid_argument("a step needs at least one entry")
-        seen = set()
-        vocab = self.model.spec.vocab_size
-        limit = self.max_positions
-        for e in entries:
-            if e.request in seen:
-                raise invalid_argument(f"request {e.request!r} appears twice in one step")
-            seen.add(e.request)
-            if not self.cache.is_open(e.request):
-                raise invalid_argument(f"request {e.request!r} is not open")
-            n = len(e.tokens)
-            if n == 0:
-                raise invalid_argument(f"request {e.request!r} brings no tokens")
-            toks = np.asarray(e.tokens)
-            if toks.min() < 0 or toks.max() >= vocab:
-                raise invalid_argument(f"request {e.request!r} has a token id outside [0, {vocab})")
-            if self.cache.length(e.request) + n > limit:
-                raise context_full(f"request {e.request!r} would reach {self.cache.length(e.request) + n} tokens; "
-                                   f"the model has {limit} positions")
+        cache = self.cache
+        S = len(entries)
+        try:
+            rows = cache.rows([e.request for e in entries])
+        except KeyError as e:
+            raise invalid_argument(f"request {e.args[0]!r} is not open") from None
+        if len(np.unique(rows)) != S:
+            seen = set()
+            for e in entries:
+                if e.request in seen:
+                    raise invalid_argument(f"request {e.request!r} appears twice in one step")
+                seen.add(e.request)
+        q_len = np.fromiter((len(e.tokens) for e in entries), dtype=np.int64, count=S)
+        if (q_len == 0).any():
+            raise invalid_argument(f"request {entries[int(np.argmin(q_len))].request!r} brings no tokens")
+        if S > 1 and int(q_len.max()) == 1:
+            tokens = np.fromiter((e.tokens[0] for e in entries), dtype=np.int64, count=S)
+        else:
+            tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int64) for e in entries])
+        if tokens.min() < 0 or tokens.max() >= self.model.spec.vocab_size:
+            bad = next(e for e in entries if min(e.tokens) < 0 or max(e.tokens) >= self.model.spec.vocab_size)
+            raise invalid_argument(f"request {bad.request!r} has a token id outside [0, {self.model.spec.vocab_size})")
+        over = cache.length_arr[rows] + q_len > self.max_positions
+        if over.any():
+            i = int(np.argmax(over))
+            raise context_full(f"request {entries[i].request!r} would reach {int(cache.length_arr[rows[i]] + q_len[i])} "
+                               f"tokens; the model has {self.max_positions} positions")
+        for e, n in zip(entries, q_len):
             for w in e.want:
                 if not (0 <= w < n):
-                    raise invalid_argument(f"request {e.request!r} wants logits at {w}, outside its {n} tokens")
+                    raise invalid_argument(f"request {e.request!r} wants logits at {w}, outside its {int(n)} tokens")
+        return rows, q_len, tokens.astype(np.int32)
 
     # -- the step -----------------------------------------------------------------
 
     def step(self, entries: Sequence[StepEntry]) -> StepOutput:
-        self.validate(entries)
+        rows, q_len, tokens = self.validate(entries)
         cache = self.cache
-        wants = {e.request: len(e.tokens) for e in entries}
-        if not cache.can_reserve(wants):
-            raise OutOfPages(f"the step's {sum(wants.values())} tokens of {len(wants)} request(s) do not fit the free "
-                             f"pages {cache.free_pages()}")
-        for e in entries:
-            cache.reserve(e.request, len(e.tokens))
-        decode = all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        cache.reserve_rows(rows, q_len)          # all or nothing: raises OutOfPages and takes no page
+        decode = int(q_len.max()) == 1 and all(len(e.want) == 1 for e in entries)
         if decode and self.fused is not None and self.fused.accepts(len(entries)):
-            ctx, rows = self._layout(entries)
+            ctx, out_rows = self._layout(entries, rows, q_len, tokens)
             logits = self.fused.run(ctx)
             self.fused_steps += 1
         elif decode and self.cuda_graphs:
-            logits, rows = self._graph_step(entries)
+            logits, out_rows = self._graph_step(entries, rows, q_len, tokens)
         else:
-            ctx, rows = self._layout(entries)
+            ctx, out_rows = self._layout(entries, rows, q_len, tokens)
             logits = self.model.forward(ctx)
-        for e in entries:
-            cache.commit(e.request, len(e.tokens))
+        cache.commit_rows(rows, q_len)
         self.steps += 1
-        self.tokens_run += sum(wants.values())
-        return StepOutput(logits=logits, rows=rows)
+        self.tokens_run += int(q_len.sum())
+        return StepOutput(logits=logits, rows=out_rows)
 
-    def _graph_step(self, entries: Sequence[StepEntry]):
+    def _graph_step(self, entries: Sequence[StepEntry], rows, q_len, tokens):
         S = len(entries)
         g = self._graphs.get(S)
         if g is None or g.generation != self.workspace.generation:
@@ -151,7 +157,7 @@ class Stepper:
             widths = [(self.max_positions + grp.page_size - 1) // grp.page_size for grp in self.cache.groups]
             total = self._layout_size(S, S, S, widths)
             g = _DecodeGraph(torch.empty(total, dtype=torch.int32, device=self.device), -1)
-            ctx, rows = self._layout(entries, static=g)
+            ctx, out_rows = self._layout(entries, rows, q_len, tokens, static=g)
             self.model.forward(ctx)
             torch.cuda.current_stream().synchronize()
             g.generation = self.workspace.generation
@@ -165,43 +171,48 @@ class Stepper:
             g.graph = graph
             self._graphs[S] = g
         else:
-            _, rows = self._layout(entries, static=g)
+            _, out_rows = self._layout(entries, rows, q_len, tokens, static=g)
         g.graph.replay()
         self.graph_steps += 1
-        return g.logits, rows
+        return g.logits, out_rows
 
     @staticmethod
     def _layout_size(S: int, T: int, R: int, widths: Sequence[int]) -> int:
         sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths]
         return sum((n + 3) // 4 * 4 for n in sizes)
 
-    def _layout(self, entries: Sequence[StepEntry], static: Optional[_DecodeGraph] = None
-                ) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+    def _layout(self, entries: Sequence[StepEntry], rows: np.ndarray, q_len: np.ndarray, tokens: np.ndarray,
+                static: Optional[_DecodeGraph] = None) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
         cache = self.cache
         S = len(entries)
-        q_len = np.array([len(e.tokens) for e in entries], dtype=np.int64)
-        n_past = np.array([cache.length(e.request) for e in entries], dtype=np.int64)
+        n_past = cache.length_arr[rows]
         q_start = np.zeros(S + 1, dtype=np.int64)
         np.cumsum(q_len, out=q_start[1:])
         T = int(q_start[-1])
-        tokens = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
-        tok_seq = np.repeat(np.arange(S, dtype=np.int32), q_len)
-        positions = (np.arange(T, dtype=np.int64) - np.repeat(q_start[:-1], q_len) + np.repeat(n_past, q_len)).astype(np.int32)
         requests = [e.request for e in entries]
-        rows: List[Tuple[Hashable, int]] = []
+        if T == S:                                  # one token each
+            tok_seq = np.arange(S, dtype=np.int32)
+            positions = n_past
+            token_rows = rows
+        else:
+            tok_seq = np.repeat(np.arange(S, dtype=np.int32), q_len)
+            positions = np.arange(T, dtype=np.int64) - np.repeat(q_start[:-1], q_len) + np.repeat(n_past, q_len)
+            token_rows = np.repeat(rows, q_len)
+        out_rows: List[Tuple[Hashable, int]] = []
         logit_rows: List[int] = []
         for i, e in enumerate(entries):
             for w in e.want:
-                rows.append((e.request, int(w)))
+                out_rows.append((e.request, int(w)))
                 logit_rows.append(int(q_start[i]) + int(w))
-        state_slots = np.array([cache.state_slot(r) for r in requests], dtype=np.int32)
         G = len(cache.groups)
         fixed = None
         if static is not None:      # widths that never change, so the captured launches stay valid
             fixed = [(self.max_positions + grp.page_size - 1) // grp.page_size for grp in cache.groups]
-        tables = [cache.block_table(g, requests, width=fixed[g] if fixed else None) for g in range(G)]
-        slots = [np.concatenate([cache.slot_mapping(g, e.request, int(n_past[i]), int(q_len[i]))
-                                 for i, e in enumerate(entries)]) for g in range(G)]
+        tables = [cache.table_rows(g, rows, width=fixed[g] if fixed else None) for g in range(G)]
+        slots = [cache.slots_of(g, token_rows, positions) for g in range(G)]
+        pieces = [tokens, positions.astype(np.int32), tok_seq, q_start.astype(np.int32), n_past.astype(np.int32),
+                  rows.astype(np.int32), np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
+        rows_out = out_rows
         # One staging buffer, one copy to the device; views are carved out of it.
         pieces = [tokens, positions, tok_seq, q_start.astype(np.int32), n_past.astype(np.int32), state_slots,
                   np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
@@ -238,5 +249,5 @@ class Stepper:
             tokens=view(0), positions=view(1), tok_seq=view(2), q_start=view(3), n_past=view(4), state_slots=view(5),
             logit_rows=view(6), n_logit_rows=len(logit_rows), groups=groups, requests=requests,
             host_q_start=q_start.tolist(), host_n_past=n_past.tolist(), max_q_len=int(q_len.max()),
-            max_kv_len=int((n_past + q_len).max()), decode_only=bool((q_len == 1).all()))
-        return ctx, rows
+            max_kv_len=int((n_past + q_len).max()), decode_only=T == S)
+        return ctx, rows_out

@@ -20,12 +20,14 @@ class DeviceSampler:
     def __init__(self, device: torch.device, max_rows: int = 256):
         self.device = device
         self._cap = 0
+        self._last_key, self._last_params, self._last_greedy = None, None, False
         self._grow(max_rows)
 
     def _grow(self, rows: int) -> None:
         if rows <= self._cap:
             return
         self._cap = rows
+        self._last_key = None
         # [temperature f32 | top_p f32 | top_k i32 | pad | uniform f64] per row, as 5 x 4-byte words... kept
         # as separate arrays inside one allocation so that one copy moves them all.
         self._host = torch.empty(rows * 6, dtype=torch.int32).pin_memory()
@@ -39,12 +41,19 @@ class DeviceSampler:
         n = len(params)
         self._grow(n)
         cap = self._cap
-        h = self._host.numpy()
-        h[0:n].view(np.float32)[:] = [p.temperature for p in params]
-        h[cap:cap + n].view(np.float32)[:] = [p.top_p for p in params]
-        h[2 * cap:2 * cap + n] = [min(p.top_k, 2 ** 31 - 1) for p in params]
-        h[4 * cap:4 * cap + 2 * n].view(np.float64)[:] = uniforms
-        self._dev.copy_(self._host, non_blocking=True)
+        key = tuple(map(id, params))
+        same = key == self._last_key
+        greedy = same and self._last_greedy
+        if not greedy:
+            h = self._host.numpy()
+            if not same:
+                h[0:n].view(np.float32)[:] = [p.temperature for p in params]
+                h[cap:cap + n].view(np.float32)[:] = [p.top_p for p in params]
+                h[2 * cap:2 * cap + n] = [min(p.top_k, 2 ** 31 - 1) for p in params]
+                self._last_key, self._last_params = key, list(params)      # the list keeps the ids from being reused
+                self._last_greedy = all(p.temperature <= 0 for p in params)
+            h[4 * cap:4 * cap + 2 * n].view(np.float64)[:] = uniforms
+            self._dev.copy_(self._host, non_blocking=True)
         d = self._dev
         ops.sample(logits, n, d[0:cap].view(torch.float32), d[2 * cap:3 * cap], d[cap:2 * cap].view(torch.float32),
                    d[4 * cap:6 * cap].view(torch.float64), self.out_ids, out_probs)

@@ -39,8 +39,9 @@ def context_for(stepper, cache, entries):
     for e in batch:
         if not cache.is_open(e.request):
             cache.open(e.request)
-        cache.reserve(e.request, len(e.tokens))
-    ctx, _ = stepper._layout(batch)
+    rows, q_len, tokens = stepper.validate(batch)
+    cache.reserve_rows(rows, q_len)
+    ctx, _ = stepper._layout(batch, rows, q_len, tokens)
     return ctx
 
 
