@@ -214,8 +214,6 @@ class Stepper:
                   rows.astype(np.int32), np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
         rows_out = out_rows
         # One staging buffer, one copy to the device; views are carved out of it.
-        pieces = [tokens, positions, tok_seq, q_start.astype(np.int32), n_past.astype(np.int32), state_slots,
-                  np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
         offsets, total = [], 0
         for p in pieces:
             offsets.append(total)
