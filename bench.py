@@ -116,25 +116,32 @@ def decode_run(model_dir, dtype, batch, steps, warmup, clocks=None):
     sampler = DeviceSampler(model.runtime.device, batch)
     greedy = [SamplingParams(temperature=0.0)] * batch
     ids = [f"b{i}" for i in range(batch)]
-    last = []
     for r in ids:                       # prompts, two at a time (2 x 512 tokens a step)
         cache.open(r)
     for i in range(0, batch, 2):
         chunk = ids[i:i + 2]
         out = stepper.step([StepEntry(r, rng.integers(0, V, size=PROMPT_LEN).tolist(), [PROMPT_LEN - 1]) for r in chunk])
-        sampler.sample(out.logits, greedy[:len(chunk)], [0.0] * len(chunk))
-        last += sampler.to_host(len(chunk))
+    sampler.out_ids[:batch].fill_(1)      # any valid ids start the decode loop; from then on they are the sampled ones
     ctx_sum, launches = 0, 0
 
+    from liyab_b200.engine.step import DeviceTokens
+    identity = list(range(batch))
+    pending = [None]
+
     def one_step():
-        nonlocal last, ctx_sum
+        """One decode step the way the engine runs it: the ids of the step before stay on the device and feed
+        this step; they are copied to the host while this step computes, and waited for after it is launched."""
+        nonlocal ctx_sum
         if cache.length(ids[0]) + 1 > P:
             for r in ids:
                 cache.truncate(r, PROMPT_LEN)
         ctx_sum += sum(cache.length(r) + 1 for r in ids)
-        out = stepper.step([StepEntry(r, [t], [0]) for r, t in zip(ids, last)])
+        out = stepper.step([StepEntry(r, [0], [0]) for r in ids], DeviceTokens(sampler.out_ids, identity))
         sampler.sample(out.logits, greedy, [0.0] * batch)
-        last = sampler.to_host(batch)
+        ticket = sampler.fetch_async(batch)
+        if pending[0] is not None:
+            sampler.wait(pending[0], batch)
+        pending[0] = ticket
 
     for _ in range(warmup):
         one_step()
@@ -150,6 +157,8 @@ def decode_run(model_dir, dtype, batch, steps, warmup, clocks=None):
     start.record()
     for _ in range(steps):
         one_step()
+    sampler.wait(pending[0], batch)
+    pending[0] = None
     end.record()
     torch.cuda.synchronize()
     wall_ms = (time.perf_counter() - t0) * 1e3

@@ -25,6 +25,9 @@ int lb_abi_version(void);
 int lb_embed_positions(int dtype, const int32_t* tokens, const int32_t* positions, const void* table,
                        const void* pos_table, float* x, int n_tokens, int width, float scale, void* stream);
 
+/* dst[i] = src[map[i]] where map[i] >= 0; other entries of dst are left alone. */
+int lb_gather_tokens(int32_t* dst, const int32_t* src, const int32_t* map, int n, void* stream);
+
 /* y[r,:] = LayerNorm(x[rows ? rows[r] : r, :]) with 32-bit statistics; weight and
  * bias are float and may be null; y is `out_dtype`. */
 int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight, const float* bias, void* y,

@@ -158,3 +158,21 @@ extern "C" int lb_kv_append(int dtype, const void* k, const void* v, int64_t row
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
+
+// ---------------------------------------------------------------- tokens that are still on the device
+
+// dst[i] = src[map[i]] where map[i] >= 0 (else dst[i] stays): the tokens a step sampled go straight into the next
+// step's token array, without a round trip through the host.
+__global__ void gather_tokens_kernel(int32_t* __restrict__ dst, const int32_t* __restrict__ src,
+                                     const int32_t* __restrict__ map, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n && map[i] >= 0) dst[i] = src[map[i]];
+}
+
+extern "C" int lb_gather_tokens(int32_t* dst, const int32_t* src, const int32_t* map, int n, void* stream) {
+    LB_CHECK_ARG(n >= 0, "gather_tokens: bad size %d", n);
+    if (n == 0) return LB_OK;
+    gather_tokens_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(dst, src, map, n);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}

@@ -21,7 +21,7 @@ from ..sampling.params import SamplingParams
 from ..sampling.sampler import DeviceSampler
 from ..status import ErrorCode, LiyabError, invalid_argument
 from .scheduler import Request, RequestState, Scheduler
-from .step import StepEntry, Stepper
+from .step import DeviceTokens, StepEntry, Stepper
 
 
 @dataclass
@@ -39,6 +39,7 @@ class EngineConfig:
     kv_memory_fraction: float = 0.5    # of the free device memory, at most, for the cache when num_pages is 0
     cuda_graphs: bool = True           # replay captured graphs for decode-only steps
     fused_decode: bool = True          # one persistent kernel for decode steps of up to 16 requests (bfloat16)
+    pipeline: bool = True              # plan and launch step n+1 while step n runs (tokens stay on the device)
 
 
 @dataclass
@@ -143,44 +144,83 @@ class Engine:
         self.scheduler.cancel(request_id)
 
     def run(self, watch: Optional[Sequence[Request]] = None) -> None:
-        """Steps until the scheduler has no work (or all of `watch` have finished)."""
+        """Steps until the scheduler has no work (or all of `watch` have finished).
+
+        With `pipeline` the host runs one step ahead of the GPU: step n+1 is planned, laid out and launched
+        while step n computes; the ids step n samples go into step n+1's token array on the device, and
+        reach the host (for end-of-sequence checks, callbacks and the results) while step n+1 runs.
+        Every step still copies its layout from pinned host memory to the device and its ids back."""
         sched = self.scheduler
-        t_start = time.perf_counter()
-        times: Dict[Hashable, Dict[str, float]] = {}
-        self._times = times
+        self._times = times = {}
+        self._t_start = self._t_last = time.perf_counter()
+        inflight = None
         idle = 0
-        while sched.has_work():
-            if watch is not None and all(r.state == RequestState.FINISHED for r in watch):
-                break
-            plan, _ = sched.plan()
-            if not plan.entries:
+        while True:
+            watching = watch is not None and all(r.state == RequestState.FINISHED for r in watch)
+            launched = None
+            if sched.has_work() and not watching:
+                plan, _ = sched.plan()
+                if plan.entries:
+                    launched = self._launch(plan)
+                    sched.begin_step(plan)
+                    if not self.config.pipeline:
+                        self._resolve(launched)
+                        launched = None
+            if inflight is not None:
+                self._resolve(inflight)
+            inflight = launched
+            if inflight is None:
+                if not sched.has_work() or (watch is not None and all(r.state == RequestState.FINISHED for r in watch)):
+                    break
                 idle += 1
-                if idle > 2 and sched.has_work():
+                if idle > 3:
                     raise LiyabError(ErrorCode.INTERNAL, "the scheduler has work but plans no step")
-                continue
-            idle = 0
-            t0 = time.perf_counter()
-            entries = [StepEntry(request=e.request.id, tokens=e.tokens, want=[e.count - 1] if e.sample else [])
-                       for e in plan.entries]
-            sampling = [e.request for e in plan.entries if e.sample]
-            out = self.stepper.step(entries)
-            ids: List[int] = []
-            if sampling:
-                self.sampler.sample(out.logits, [r.params for r in sampling], [r.next_uniform() for r in sampling])
-                ids = self.sampler.to_host(len(sampling))
             else:
-                torch.cuda.current_stream().synchronize()
-            dt = (time.perf_counter() - t0) * 1e3
-            for e in plan.entries:
-                t = times.setdefault(e.request.id, dict(prefill=0.0, decode=0.0, ttft=0.0))
-                first = len(e.request.tokens) == len(e.request.prompt)
-                if e.start + e.count <= len(e.request.prompt) or first:
-                    t["prefill"] += dt
-                    if e.sample and first:
-                        t["ttft"] = (time.perf_counter() - t_start) * 1e3
-                else:
-                    t["decode"] += dt
-            sched.update(plan, ids)
+                idle = 0
+
+    def _launch(self, plan):
+        """Lays the plan out, launches its kernels and its sampling, and starts the copy of the ids to the host."""
+        sampling = [e.request for e in plan.entries if e.sample]
+        index, entries, on_device = [], [], False
+        for e in plan.entries:
+            toks = e.tokens
+            if e.count == 1 and toks[0] < 0:           # sampled by the step in flight: still on the device
+                index.append(e.request.sample_slot)
+                toks = [0]
+                on_device = True
+            else:
+                index.append(-1)
+            entries.append(StepEntry(request=e.request.id, tokens=toks, want=[e.count - 1] if e.sample else []))
+        uniforms = [r.next_uniform() for r in sampling]
+        out = self.stepper.step(entries, DeviceTokens(self.sampler.out_ids, index) if on_device else None)
+        ticket = None
+        if sampling:
+            self.sampler.sample(out.logits, [r.params for r in sampling], uniforms)
+            ticket = self.sampler.fetch_async(len(sampling))
+            for slot, r in enumerate(sampling):
+                r.sample_slot = slot
+        return plan, sampling, ticket
+
+    def _resolve(self, launched) -> None:
+        """Waits for a launched step's ids and lets the scheduler finish the step."""
+        plan, sampling, ticket = launched
+        if ticket is not None:
+            ids = self.sampler.wait(ticket, len(sampling))
+        else:
+            ids = []
+            torch.cuda.current_stream().synchronize()
+        now = time.perf_counter()
+        dt, self._t_last = (now - self._t_last) * 1e3, now
+        for e in plan.entries:
+            t = self._times.setdefault(e.request.id, dict(prefill=0.0, decode=0.0, ttft=0.0))
+            first = e.sample and e.token_index == len(e.request.prompt)
+            if e.start + e.count <= len(e.request.prompt) or first:
+                t["prefill"] += dt
+                if first:
+                    t["ttft"] = (now - self._t_start) * 1e3
+            else:
+                t["decode"] += dt
+        self.scheduler.finish_step(plan, ids)
 
     def _result(self, r: Request) -> GenerationResult:
         t = getattr(self, "_times", {}).get(r.id, dict(prefill=0.0, decode=0.0, ttft=0.0))

@@ -35,6 +35,16 @@ run and are tested without a GPU:
   callback returns False, or when cancelled; its pages and state slot are freed
   at once.  The last sampled token is returned but never run, as in the
   reference (engine.cpp:4388-4393).
+* A step is accounted for in two halves, so that the host can run one step ahead of
+  the GPU: `begin_step` (right after the step is launched) advances every request and
+  appends a placeholder for each token the step will sample; `finish_step` (when the
+  sampled ids have arrived) puts the real tokens in, calls callbacks and finishes
+  requests.  Between the two, the next step may already be planned and launched with
+  the placeholders standing for tokens that are still on the device.  What the length
+  limits decide is known at `begin_step`; what depends on a token's value (end of
+  sequence, a callback's verdict) is decided at `finish_step`, one step later, so a
+  request may have run one token too many; that token is dropped.  `update` is both
+  halves at once.
 """
 from __future__ import annotations
 
@@ -46,6 +56,9 @@ from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence, Tu
 from ..cache.pages import CacheManager
 from ..sampling.params import SamplingParams, uniform_draw
 from ..status import ErrorCode, LiyabError, invalid_argument
+
+
+PLACEHOLDER = -1        # stands in a request's tokens for an id sampled by a step whose result is not back yet
 
 
 class RequestState(enum.Enum):
@@ -70,6 +83,7 @@ class Request:
     seed: int = 0
     stream: int = 0
     admitted_at: int = -1
+    sample_slot: int = -1                                 # where the step in flight will put this request's token
 
     @property
     def generated(self) -> List[int]:
@@ -78,6 +92,11 @@ class Request:
     @property
     def pending(self) -> int:
         return len(self.tokens) - self.n_computed
+
+    @property
+    def unresolved(self) -> bool:
+        """Whether the last token is still a placeholder for an id that has not come back from the device."""
+        return bool(self.tokens) and self.tokens[-1] == PLACEHOLDER
 
     def next_uniform(self) -> float:
         """The draw for this request's next generated token."""
@@ -90,6 +109,8 @@ class PlannedEntry:
     start: int          # first token of the portion (index into request.tokens)
     count: int
     sample: bool        # the portion ends the known tokens: a new token is sampled after it
+    token_index: int = -1   # where in request.tokens the sampled token goes (set by begin_step)
+    ends: Optional[str] = None  # the length limit that this very token reaches, if any (set by begin_step)
 
     @property
     def tokens(self) -> List[int]:
@@ -165,6 +186,9 @@ class Scheduler:
         return (n_tokens + ps - 1) // ps
 
     def _finish(self, r: Request, reason: str, error: Optional[LiyabError] = None) -> None:
+        if r.state == RequestState.FINISHED:
+            r.finish_reason = reason
+            return
         if r.state == RequestState.RUNNING:
             self.running.remove(r)
             self.cache.close(r.id)
@@ -246,13 +270,11 @@ class Scheduler:
         self.stats.peak_running = max(self.stats.peak_running, len(self.running))
         return StepPlan(entries=entries, preempted=preempted), finished
 
-    # -- after the step ran ----------------------------------------------------------
+    # -- after the step was launched, and after its tokens came back ---------------------
 
-    def update(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
-        """Records what the step computed and the tokens sampled for the entries with `sample`,
-        in the plan's order; returns the requests that finished."""
-        finished: List[Request] = []
-        it = iter(sampled)
+    def begin_step(self, plan: StepPlan) -> None:
+        """The step is on its way: its tokens count as computed, a placeholder stands for each token it
+        samples, and a request that its length limits end is taken out of the running set already."""
         self.stats.steps += 1
         self.stats.batched_tokens += plan.n_tokens
         for e in plan.entries:
@@ -264,23 +286,47 @@ class Scheduler:
                 self.stats.prefill_tokens += e.count
             if not e.sample:
                 continue
+            r.tokens.append(PLACEHOLDER)
+            e.token_index = len(r.tokens) - 1
+            if len(r.tokens) - len(r.prompt) >= r.params.max_tokens:
+                e.ends = "length"
+            elif len(r.tokens) > self.max_positions:
+                e.ends = "context"                # the new token has no position left to run at
+            if e.ends is not None:
+                self._finish(r, e.ends)
+
+    def finish_step(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """The ids sampled for the plan's entries with `sample`, in the plan's order, have arrived.
+        Returns the requests whose generation is now complete."""
+        done: List[Request] = []
+        it = iter(sampled)
+        for e in plan.entries:
+            if not e.sample:
+                continue
             token = int(next(it))
-            r.tokens.append(token)
+            r = e.request
+            if e.token_index >= len(r.tokens):
+                continue                           # the request ended on an earlier token; this one was one too many
+            r.tokens[e.token_index] = token
             keep_going = True
             if r.callback is not None:
                 keep_going = r.callback(token) is not False
             reason = None
             if not r.params.ignore_eos and self.eos_token_id is not None and token == self.eos_token_id:
                 reason = "eos"
-            elif len(r.tokens) - len(r.prompt) >= r.params.max_tokens:
-                reason = "length"
+            elif e.ends is not None:
+                reason = e.ends                      # this token reached a length limit (known since begin_step)
             elif not keep_going:
                 reason = "stopped"
             elif r.cancelled:
                 reason = "cancelled"
-            elif len(r.tokens) > self.max_positions:
-                reason = "context"        # the new token has no position left to run at
             if reason is not None:
+                del r.tokens[e.token_index + 1:]     # a placeholder of the step after this one, if any
                 self._finish(r, reason)
-                finished.append(r)
-        return finished
+                done.append(r)
+        return done
+
+    def update(self, plan: StepPlan, sampled: Sequence[int]) -> List[Request]:
+        """Both halves at once, for a caller that waits for every step's tokens before planning the next."""
+        self.begin_step(plan)
+        return self.finish_step(plan, sampled)

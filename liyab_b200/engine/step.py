@@ -38,6 +38,14 @@ class StepEntry:
 
 
 @dataclass
+class DeviceTokens:
+    """Tokens of a step that are still on the device: entry i's (single) token is source[index[i]] where
+    index[i] >= 0; other entries bring their tokens from the host as usual."""
+    source: torch.Tensor          # int32 on the device, e.g. the ids the previous step sampled
+    index: Sequence[int]
+
+
+@dataclass
 class StepOutput:
     logits: Optional[torch.Tensor]                 # [R, vocab] float32 on the device; valid until the next step
     rows: List[Tuple[Hashable, int]] = field(default_factory=list)   # (request, index among its tokens) per row
@@ -84,6 +92,7 @@ class Stepper:
         self.fused_steps = 0
         self._graphs: dict = {}
         self.graph_launches: dict = {}       # kernels in the captured step, by number of requests
+        self._device_tokens: Optional[DeviceTokens] = None
         self.steps = 0
         self.graph_steps = 0
         self.tokens_run = 0
@@ -129,8 +138,9 @@ class Stepper:
 
     # -- the step -----------------------------------------------------------------
 
-    def step(self, entries: Sequence[StepEntry]) -> StepOutput:
+    def step(self, entries: Sequence[StepEntry], device_tokens: Optional[DeviceTokens] = None) -> StepOutput:
         rows, q_len, tokens = self.validate(entries)
+        self._device_tokens = device_tokens
         cache = self.cache
         cache.reserve_rows(rows, q_len)          # all or nothing: raises OutOfPages and takes no page
         decode = int(q_len.max()) == 1 and all(len(e.want) == 1 for e in entries)
@@ -178,7 +188,7 @@ class Stepper:
 
     @staticmethod
     def _layout_size(S: int, T: int, R: int, widths: Sequence[int]) -> int:
-        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths]
+        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths] + [S]
         return sum((n + 3) // 4 * 4 for n in sizes)
 
     def _layout(self, entries: Sequence[StepEntry], rows: np.ndarray, q_len: np.ndarray, tokens: np.ndarray,
@@ -213,6 +223,13 @@ class Stepper:
         pieces = [tokens, positions.astype(np.int32), tok_seq, q_start.astype(np.int32), n_past.astype(np.int32),
                   rows.astype(np.int32), np.asarray(logit_rows, dtype=np.int32)] + [t.reshape(-1) for t in tables] + slots
         rows_out = out_rows
+        dt = self._device_tokens
+        if dt is not None:          # where each token comes from on the device (-1: from the host array)
+            if T != S or len(dt.index) != S:
+                raise invalid_argument("tokens can stay on the device only for steps of one token per request")
+            pieces.append(np.asarray(dt.index, dtype=np.int32))
+        elif static is not None:
+            pieces.append(np.full(S, -1, dtype=np.int32))      # a captured step keeps room for the map
         # One staging buffer, one copy to the device; views are carved out of it.
         offsets, total = [], 0
         for p in pieces:
@@ -240,6 +257,8 @@ class Stepper:
         def view(i: int) -> torch.Tensor:
             return dev[offsets[i]:offsets[i] + pieces[i].size]
 
+        if dt is not None:
+            ops.gather_tokens(view(0), dt.source, view(len(pieces) - 1), S)
         groups = [GroupView(group=cache.groups[g], block_table=view(7 + g).view(S, tables[g].shape[1]),
                             slot_mapping=view(7 + G + g)) for g in range(G)]
         ctx = StepContext(

@@ -25,6 +25,7 @@ _p, _i, _l, _f = _c.c_void_p, _c.c_int, _c.c_int64, _c.c_float
 
 _SIGNATURES = {
     "lb_embed_positions": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
+    "lb_gather_tokens": [_p, _p, _p, _i, _p],
     "lb_layernorm": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "lb_kv_append": [_i, _p, _p, _l, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
@@ -114,6 +115,12 @@ def embed_positions(tokens: torch.Tensor, positions: torch.Tensor, table: torch.
                                    _opt(pos_table, "pos_table"), _dev(out, "out", torch.float32), n, width,
                                    float(scale), stream_ptr()), "embed_positions")
     return out
+
+
+def gather_tokens(dst: torch.Tensor, src: torch.Tensor, token_map: torch.Tensor, n: int) -> None:
+    """dst[i] = src[token_map[i]] where token_map[i] >= 0 (tokens that never left the device)."""
+    check(lib().lb_gather_tokens(_dev(dst, "dst", torch.int32), _dev(src, "src", torch.int32),
+                                 _dev(token_map, "token_map", torch.int32), n, stream_ptr()), "gather_tokens")
 
 
 def layernorm(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optional[torch.Tensor], eps: float,

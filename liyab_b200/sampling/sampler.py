@@ -34,6 +34,8 @@ class DeviceSampler:
         self._dev = torch.empty(rows * 6, dtype=torch.int32, device=self.device)
         self.out_ids = torch.empty(rows, dtype=torch.int32, device=self.device)
         self._host_ids = torch.empty(rows, dtype=torch.int32).pin_memory()
+        self._tickets = [(torch.empty(rows, dtype=torch.int32).pin_memory(), torch.cuda.Event()) for _ in range(2)]
+        self._next_ticket = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], uniforms: Sequence[float],
                out_probs: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -64,3 +66,18 @@ class DeviceSampler:
         self._host_ids[:n].copy_(self.out_ids[:n], non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return self._host_ids[:n].tolist()
+
+    def fetch_async(self, n: int) -> int:
+        """Starts copying the last `n` sampled ids to the host; returns a ticket for `wait`.  Two tickets are
+        live at most: the one before last must have been waited for."""
+        ticket = self._next_ticket
+        self._next_ticket = 1 - ticket
+        host, event = self._tickets[ticket]
+        host[:n].copy_(self.out_ids[:n], non_blocking=True)
+        event.record()
+        return ticket
+
+    def wait(self, ticket: int, n: int) -> list:
+        host, event = self._tickets[ticket]
+        event.synchronize()
+        return host[:n].tolist()

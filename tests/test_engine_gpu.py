@@ -136,3 +136,37 @@ def test_command_line(folders):
     assert lines[1]["tokens"] == plain.generate_greedy(plain.load_plain_model(folder), prompt, 6)
     proc = subprocess.run(cmd[:6] + ["--tokenize"], capture_output=True, text=True, timeout=600)
     assert proc.stdout.split() == [str(t) for t in prompt]
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16")])
+def test_pipelined_and_stepwise_loops_give_the_same_tokens(name, dtype, tmp_path):
+    """The host running one step ahead (tokens stay on the device) against waiting for every step: same tokens,
+    same reasons, with sampling, an end-of-sequence token, a callback that stops and a tight cache."""
+    from liyab_b200 import Engine, EngineConfig, SamplingParams
+    folder = write_model(str(tmp_path), name, dtype)
+    V = CONFIGS[name][0]["vocab_size"]
+    prompts = [random_tokens(40 + i, n, V) for i, n in enumerate((21, 3, 34, 9, 15))]
+    params = [SamplingParams(temperature=0.9, top_k=50, top_p=0.9, seed=11 + i, max_tokens=30 + 3 * i) for i in range(5)]
+    probe = Engine(EngineConfig(model=folder, dtype=dtype, max_requests=5, max_batched_tokens=24, num_pages=40, pipeline=False))
+    first = probe.generate_batch(prompts, params)
+    eos = first[1].tokens[7]                     # make a token that really occurs the end-of-sequence token
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    cfg["eos_token_id"] = eos
+    eos_folder = tmp_path / "eos"
+    eos_folder.mkdir()
+    (eos_folder / "config.json").write_text(json.dumps(cfg))
+    os.symlink(os.path.join(folder, "model.safetensors"), eos_folder / "model.safetensors")
+    outs = []
+    for pipeline in (False, True):
+        for pages in (40, 11):
+            engine = Engine(EngineConfig(model=str(eos_folder), dtype=dtype, max_requests=5, max_batched_tokens=24,
+                                         num_pages=pages, pipeline=pipeline))
+            seen = []
+            callbacks = [None, None, (lambda t: seen.append(t) or len(seen) < 5), None, None]
+            res = engine.generate_batch(prompts, params, callbacks)
+            outs.append([(r.tokens, r.finish_reason) for r in res])
+            assert all(v == 0 for v in engine.cache.pages_in_use().values())
+            if pages == 11:
+                assert engine.scheduler.stats.preemptions >= 1
+    assert outs[0] == outs[1] == outs[2] == outs[3]
+    assert outs[0][1][1] == "eos" and outs[0][2] == (first[2].tokens[:5], "stopped")

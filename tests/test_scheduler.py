@@ -163,3 +163,55 @@ def test_draws_do_not_depend_on_batching():
     a.tokens.append(5)
     u1 = a.next_uniform()
     assert (u0, u1) == (uniform_draw(7, 0, 0), uniform_draw(7, 0, 1)) and u0 != u1
+
+
+def run_pipelined(cache, sched, token_of):
+    """The host one step ahead: plan and begin step n+1 before step n's tokens are known (finish_step)."""
+    inflight = None
+    guard = 0
+    while (sched.has_work() or inflight is not None) and guard < 500:
+        guard += 1
+        launched = None
+        if sched.has_work():
+            plan, _ = sched.plan()
+            if plan.entries:
+                for e in plan.entries:
+                    toks = e.tokens
+                    assert all(t >= 0 for t in toks[:-1]) and (toks[-1] >= 0 or e.count == 1), "only a lone token may be unknown"
+                    cache.reserve(e.request.id, e.count)
+                    cache.commit(e.request.id, e.count)
+                # the ids depend on nothing the host has not seen: index of the token in its request
+                ids = [token_of(e.request, len(e.request.tokens) - len(e.request.prompt)) for e in plan.entries if e.sample]
+                sched.begin_step(plan)
+                launched = (plan, ids)
+        if inflight is not None:
+            sched.finish_step(*inflight)
+        inflight = launched
+        cache.check()
+    assert guard < 500
+
+
+@pytest.mark.parametrize("num_pages", [64, 5])
+def test_pipelined_protocol_gives_the_same_tokens(num_pages):
+    def token_of(r, index):
+        return 9 if (r.id == "r1" and index == 3) else 100 + index      # r1 meets its end-of-sequence at its 4th token
+
+    outputs = []
+    for pipelined in (False, True):
+        cache, sched = make(eos=9, num_pages=num_pages, page_size=4, max_batched_tokens=6)
+        stops = []
+        reqs = [req(0, 7, max_tokens=6), req(1, 3, max_tokens=12), req(2, 5, max_tokens=5, ignore_eos=True),
+                Request(id="r3", prompt=[2, 3], params=SamplingParams(temperature=0.0, max_tokens=20),
+                        callback=lambda t: stops.append(t) or len(stops) < 4)]
+        for r in reqs:
+            sched.add(r)
+        if pipelined:
+            run_pipelined(cache, sched, token_of)
+        else:
+            while sched.has_work():
+                run_step(cache, sched, next_token=lambda r: token_of(r, len(r.generated)))
+        outputs.append([(r.generated, r.finish_reason) for r in reqs])
+        assert all(v == 0 for v in cache.pages_in_use().values()) and not cache.lengths
+        assert all(t >= 0 for r in reqs for t in r.tokens)
+    assert outputs[0] == outputs[1]
+    assert outputs[0][1] == ([100, 101, 102, 9], "eos") and outputs[0][3][1] == "stopped" and len(outputs[0][3][0]) == 4
