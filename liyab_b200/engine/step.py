@@ -188,7 +188,7 @@ class Stepper:
 
     @staticmethod
     def _layout_size(S: int, T: int, R: int, widths: Sequence[int]) -> int:
-        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths] + [S]
+        sizes = [T, T, T, S + 1, S, S, R] + [S * w for w in widths] + [T for _ in widths] + [T]
         return sum((n + 3) // 4 * 4 for n in sizes)
 
     def _layout(self, entries: Sequence[StepEntry], rows: np.ndarray, q_len: np.ndarray, tokens: np.ndarray,
@@ -225,11 +225,14 @@ class Stepper:
         rows_out = out_rows
         dt = self._device_tokens
         if dt is not None:          # where each token comes from on the device (-1: from the host array)
-            if T != S or len(dt.index) != S:
-                raise invalid_argument("tokens can stay on the device only for steps of one token per request")
-            pieces.append(np.asarray(dt.index, dtype=np.int32))
+            index = np.asarray(dt.index, dtype=np.int32)
+            if len(index) != S or (q_len[index >= 0] != 1).any():
+                raise invalid_argument("a token can stay on the device only as the single token of its request")
+            token_map = np.full(T, -1, dtype=np.int32)
+            token_map[q_start[:-1]] = index
+            pieces.append(token_map)
         elif static is not None:
-            pieces.append(np.full(S, -1, dtype=np.int32))      # a captured step keeps room for the map
+            pieces.append(np.full(T, -1, dtype=np.int32))      # a captured step keeps room for the map
         # One staging buffer, one copy to the device; views are carved out of it.
         offsets, total = [], 0
         for p in pieces:
@@ -258,7 +261,7 @@ class Stepper:
             return dev[offsets[i]:offsets[i] + pieces[i].size]
 
         if dt is not None:
-            ops.gather_tokens(view(0), dt.source, view(len(pieces) - 1), S)
+            ops.gather_tokens(view(0), dt.source, view(len(pieces) - 1), T)
         groups = [GroupView(group=cache.groups[g], block_table=view(7 + g).view(S, tables[g].shape[1]),
                             slot_mapping=view(7 + G + g)) for g in range(G)]
         ctx = StepContext(
