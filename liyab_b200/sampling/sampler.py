@@ -30,7 +30,11 @@ class DeviceSampler:
         self._last_key = None
         # [temperature f32 | top_p f32 | top_k i32 | pad | uniform f64] per row, as 5 x 4-byte words... kept
         # as separate arrays inside one allocation so that one copy moves them all.
-        self._host = torch.empty(rows * 6, dtype=torch.int32).pin_memory()
+        # Two pinned staging buffers used in turn: one is rewritten only after the copy that last read it has
+        # run on the device (the host may be a step ahead of the GPU).
+        self._hosts = [torch.empty(rows * 6, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self._copied = [torch.cuda.Event(), torch.cuda.Event()]
+        self._turn = 0
         self._dev = torch.empty(rows * 6, dtype=torch.int32, device=self.device)
         self.out_ids = torch.empty(rows, dtype=torch.int32, device=self.device)
         self._host_ids = torch.empty(rows, dtype=torch.int32).pin_memory()
@@ -47,15 +51,19 @@ class DeviceSampler:
         same = key == self._last_key
         greedy = same and self._last_greedy
         if not greedy:
-            h = self._host.numpy()
+            turn = self._turn = 1 - self._turn
+            self._copied[turn].synchronize()
+            host = self._hosts[turn]
+            h = host.numpy()
+            h[0:n].view(np.float32)[:] = [p.temperature for p in params]
+            h[cap:cap + n].view(np.float32)[:] = [p.top_p for p in params]
+            h[2 * cap:2 * cap + n] = [min(p.top_k, 2 ** 31 - 1) for p in params]
             if not same:
-                h[0:n].view(np.float32)[:] = [p.temperature for p in params]
-                h[cap:cap + n].view(np.float32)[:] = [p.top_p for p in params]
-                h[2 * cap:2 * cap + n] = [min(p.top_k, 2 ** 31 - 1) for p in params]
                 self._last_key, self._last_params = key, list(params)      # the list keeps the ids from being reused
                 self._last_greedy = all(p.temperature <= 0 for p in params)
             h[4 * cap:4 * cap + 2 * n].view(np.float64)[:] = uniforms
-            self._dev.copy_(self._host, non_blocking=True)
+            self._dev.copy_(host, non_blocking=True)
+            self._copied[turn].record()
         d = self._dev
         ops.sample(logits, n, d[0:cap].view(torch.float32), d[2 * cap:3 * cap], d[cap:2 * cap].view(torch.float32),
                    d[4 * cap:6 * cap].view(torch.float64), self.out_ids, out_probs)
