@@ -157,11 +157,11 @@ class Engine:
         idle = 0
         while True:
             watching = watch is not None and all(r.state == RequestState.FINISHED for r in watch)
-            launched = None
+            launched, progressed = None, inflight is not None
             if sched.has_work() and not watching:
                 plan, _ = sched.plan()
                 if plan.entries:
-                    launched = self._launch(plan)
+                    launched, progressed = self._launch(plan), True
                     sched.begin_step(plan)
                     if not self.config.pipeline:
                         self._resolve(launched)
@@ -169,14 +169,12 @@ class Engine:
             if inflight is not None:
                 self._resolve(inflight)
             inflight = launched
-            if inflight is None:
-                if not sched.has_work() or (watch is not None and all(r.state == RequestState.FINISHED for r in watch)):
-                    break
-                idle += 1
-                if idle > 3:
-                    raise LiyabError(ErrorCode.INTERNAL, "the scheduler has work but plans no step")
-            else:
-                idle = 0
+            if inflight is None and (not sched.has_work() or
+                                     (watch is not None and all(r.state == RequestState.FINISHED for r in watch))):
+                break
+            idle = 0 if progressed else idle + 1
+            if idle > 3:
+                raise LiyabError(ErrorCode.INTERNAL, "the scheduler has work but plans no step")
 
     def _launch(self, plan):
         """Lays the plan out, launches its kernels and its sampling, and starts the copy of the ids to the host."""
