@@ -179,6 +179,8 @@ def prefill_run(model_dir, dtype, repeats=5):
     from liyab_b200.engine import StepEntry
     from liyab_b200.engine.replay import build_replayer
     model, cache, stepper = build_replayer(model_dir, dtype, max_tokens=4096, page_size=16)
+    stepper.cuda_graphs = True              # as the engine runs it: a step of a shape seen before replays its graph
+    stepper.workspace.reserve_rows(PREFILL_TOKENS)
     V = model.spec.vocab_size
     rng = np.random.default_rng(1)
     n_seq = PREFILL_TOKENS // 1024

@@ -499,17 +499,17 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
                                        act, vec_ok, s)
     if (out_dtype == LB_BF16) {
         switch (tile) {
-            case 16: LB_GO(16, 8, false, __nv_bfloat16);
-            case 32: LB_GO(32, 8, false, __nv_bfloat16);
-            case 64: LB_GO(64, 6, false, __nv_bfloat16);
+            case 16: LB_GO(16, 4, false, __nv_bfloat16);
+            case 32: LB_GO(32, 4, false, __nv_bfloat16);
+            case 64: LB_GO(64, 4, false, __nv_bfloat16);
             case 128: LB_GO(128, 3, true, __nv_bfloat16);
             default: LB_GO(256, 4, true, __nv_bfloat16);
         }
     }
     switch (tile) {
-        case 16: LB_GO(16, 8, false, float);
-        case 32: LB_GO(32, 8, false, float);
-        case 64: LB_GO(64, 6, false, float);
+        case 16: LB_GO(16, 4, false, float);
+        case 32: LB_GO(32, 4, false, float);
+        case 64: LB_GO(64, 4, false, float);
         case 128: LB_GO(128, 3, true, float);
         default: LB_GO(256, 4, true, float);
     }

@@ -52,7 +52,7 @@ class StepOutput:
 
 
 class _DecodeGraph:
-    """A captured decode step for a fixed number of requests: its layout buffer, graph and logits view."""
+    """A captured step of one shape: its layout buffer, graph and logits view."""
 
     def __init__(self, dev: torch.Tensor, generation: int):
         self.dev = dev
@@ -91,6 +91,7 @@ class Stepper:
         self.fused = FusedDecodeStack.try_build(model, cache) if fused_decode else None
         self.fused_steps = 0
         self._graphs: dict = {}
+        self._seen: dict = {}                # how often a shape without a graph has come up
         self.graph_launches: dict = {}       # kernels in the captured step, by number of requests
         self._device_tokens: Optional[DeviceTokens] = None
         self.steps = 0
@@ -148,7 +149,7 @@ class Stepper:
             ctx, out_rows = self._layout(entries, rows, q_len, tokens)
             logits = self.fused.run(ctx)
             self.fused_steps += 1
-        elif decode and self.cuda_graphs:
+        elif self.cuda_graphs and (decode or self._worth_capturing(entries, q_len)):
             logits, out_rows = self._graph_step(entries, rows, q_len, tokens)
         else:
             ctx, out_rows = self._layout(entries, rows, q_len, tokens)
@@ -158,16 +159,37 @@ class Stepper:
         self.tokens_run += int(q_len.sum())
         return StepOutput(logits=logits, rows=out_rows)
 
+    def _shape_key(self, entries: Sequence[StepEntry], q_len: np.ndarray):
+        S, T = len(entries), int(q_len.sum())
+        return S, T, sum(len(e.want) for e in entries), ((int(q_len.max()) + 63) // 64 * 64 if T != S else 1)
+
+    def _worth_capturing(self, entries: Sequence[StepEntry], q_len: np.ndarray) -> bool:
+        """A step with prompt portions is captured when its shape comes up for the third time (capturing costs
+        several eager steps) and the scratch buffers are sized so that they will not move."""
+        if int(q_len.sum()) > self.workspace.min_rows:
+            return False
+        key = self._shape_key(entries, q_len)
+        if key in self._graphs:
+            return True
+        self._seen[key] = self._seen.get(key, 0) + 1
+        if len(self._seen) > 4096:
+            self._seen.clear()
+        return self._seen[key] >= 3
+
     def _graph_step(self, entries: Sequence[StepEntry], rows, q_len, tokens):
-        S = len(entries)
-        g = self._graphs.get(S)
+        """Runs the step through a captured graph.  A graph fits every step with the same number of requests,
+        tokens and wanted rows whose longest portion falls into the same bucket of 64 tokens; everything else
+        about the step (tokens, positions, where portions start, block tables, slots) is data the graph reads."""
+        key = self._shape_key(entries, q_len)
+        S, T, R, bucket = key
+        g = self._graphs.get(key)
         if g is None or g.generation != self.workspace.generation:
-            # First decode step of this size (or buffers moved since): run it eagerly on a
-            # buffer of its own so every scratch buffer exists, then capture the same launches.
+            # First step of this shape (or buffers moved since): run it eagerly on a buffer of its own so
+            # every scratch buffer exists, then capture the same launches.
             widths = [(self.max_positions + grp.page_size - 1) // grp.page_size for grp in self.cache.groups]
-            total = self._layout_size(S, S, S, widths)
+            total = self._layout_size(S, T, R, widths)
             g = _DecodeGraph(torch.empty(total, dtype=torch.int32, device=self.device), -1)
-            ctx, out_rows = self._layout(entries, rows, q_len, tokens, static=g)
+            ctx, out_rows = self._layout(entries, rows, q_len, tokens, static=g, max_q_len=bucket)
             self.model.forward(ctx)
             torch.cuda.current_stream().synchronize()
             g.generation = self.workspace.generation
@@ -175,13 +197,17 @@ class Stepper:
             before = ops.LAUNCHES
             with torch.cuda.graph(graph):
                 g.logits = self.model.forward(ctx)
-            self.graph_launches[S] = ops.LAUNCHES - before
+            self.graph_launches[key] = ops.LAUNCHES - before
+            if S == T:
+                self.graph_launches[S] = self.graph_launches[key]
             if g.generation != self.workspace.generation:
-                raise RuntimeError("a scratch buffer was created while a decode step was being captured")
+                raise RuntimeError("a scratch buffer was created while a step was being captured")
             g.graph = graph
-            self._graphs[S] = g
+            if len(self._graphs) >= 48:                   # keep the most recent shapes
+                self._graphs.pop(next(iter(self._graphs)))
+            self._graphs[key] = g
         else:
-            _, out_rows = self._layout(entries, rows, q_len, tokens, static=g)
+            _, out_rows = self._layout(entries, rows, q_len, tokens, static=g, max_q_len=bucket)
         g.graph.replay()
         self.graph_steps += 1
         return g.logits, out_rows
@@ -192,7 +218,8 @@ class Stepper:
         return sum((n + 3) // 4 * 4 for n in sizes)
 
     def _layout(self, entries: Sequence[StepEntry], rows: np.ndarray, q_len: np.ndarray, tokens: np.ndarray,
-                static: Optional[_DecodeGraph] = None) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
+                static: Optional[_DecodeGraph] = None, max_q_len: int = 0
+                ) -> Tuple[StepContext, List[Tuple[Hashable, int]]]:
         cache = self.cache
         S = len(entries)
         n_past = cache.length_arr[rows]
@@ -268,6 +295,6 @@ class Stepper:
             runtime=self.model.runtime, workspace=self.workspace, cache=cache, n_tokens=T, n_seq=S,
             tokens=view(0), positions=view(1), tok_seq=view(2), q_start=view(3), n_past=view(4), state_slots=view(5),
             logit_rows=view(6), n_logit_rows=len(logit_rows), groups=groups, requests=requests,
-            host_q_start=q_start.tolist(), host_n_past=n_past.tolist(), max_q_len=int(q_len.max()),
-            max_kv_len=int((n_past + q_len).max()), decode_only=T == S)
+            host_q_start=q_start.tolist(), host_n_past=n_past.tolist(), max_q_len=max_q_len or int(q_len.max()),
+            max_kv_len=int((n_past + q_len).max()), decode_only=T == S, max_positions=self.max_positions)
         return ctx, rows_out

@@ -61,7 +61,7 @@ def case_decode_attention(args) -> None:
     q = torch.randn(B, H * hd, device=dev).to(torch.bfloat16)
     out = torch.empty_like(q)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
-    splits = ops.decode_splits(B, H)
+    splits = ops.decode_splits(B, H, ctx)
     partial = torch.empty(B * H * splits * (hd + 2), device=dev)
     counters = torch.zeros(B * H, dtype=torch.int32, device=dev)
     ms = _timed(lambda: ops.decode_attention(q, cache, positions, table, out, partial, counters, B, H, H, hd, ps,

@@ -227,10 +227,12 @@ def decode_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_s
     return bool(lib().lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
 
 
-def decode_splits(n_seq: int, n_kv_head: int) -> int:
-    """How many ways each request's keys are split: enough blocks to fill the GPU about four times over,
-    a function of the batch's shape only (so a captured step and an eager one split alike)."""
-    return max(1, min(32, -(-592 // max(1, n_seq * n_kv_head))))
+def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0) -> int:
+    """How many ways each request's keys are split: enough blocks for about four full waves of the GPU (a
+    single wave and a bit leaves most SMs idle for the bit), but no ranges shorter than 128 keys at the
+    longest context.  A function of the batch's shape only, so a captured step and an eager one split alike."""
+    cap = max(1, max_context // 128) if max_context else 32
+    return max(1, min(32, cap, -(-2960 // max(1, n_seq * n_kv_head))))
 
 
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,

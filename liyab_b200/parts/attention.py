@@ -60,7 +60,7 @@ class CausalSelfAttention:
         s, T = self.spec, ctx.n_tokens
         if (ctx.decode_only and self.runtime.dtype == torch.bfloat16
                 and ops.decode_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):
-            splits = ops.decode_splits(T, s.n_kv_head)
+            splits = ops.decode_splits(T, s.n_kv_head, ctx.max_positions)
             partial = counters = None
             if splits > 1:
                 partial = ctx.workspace.flat("attn.decode.partial", T * s.n_head * splits * (s.head_dim + 2), torch.float32)

@@ -112,6 +112,7 @@ class StepContext:
     max_q_len: int = 0
     max_kv_len: int = 0
     decode_only: bool = False
+    max_positions: int = 0           # the longest sequence the engine serves (fixes split counts and table widths)
     extras: Dict[str, object] = field(default_factory=dict)
 
     def kv(self, unit: int) -> Tuple[torch.Tensor, GroupView]:
