@@ -402,15 +402,11 @@ __device__ void gemm_phase(const __nv_bfloat16* __restrict__ W, int N, int K, co
     }
 }
 
-struct alignas(16) Vec8 {
-    __nv_bfloat162 h[4];
-};
-
 __device__ __forceinline__ void unpack8(const uint4& raw, float (&f)[8]) {
-    const Vec8& v = reinterpret_cast<const Vec8&>(raw);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const float2 t = __bfloat1622float2(v.h[i]);
+        const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
         f[2 * i] = t.x;
         f[2 * i + 1] = t.y;
     }
