@@ -50,10 +50,14 @@ int lb_gemm_ffma(int in_dtype, int out_dtype, const void* A, int64_t lda, const 
  * 16-byte aligned bases, else LB_ERR_UNSUPPORTED (4).  token_tile 0 picks the tile
  * (lb_gemm_tcgen05_token_tile): 16, 32, 64 put the weights on the accumulator's
  * lanes and that many tokens on its columns; 128 and 256 put 128 tokens on the
- * lanes and that many features on the columns.  out is LB_BF16 or LB_F32. */
+ * lanes and that many features on the columns.  out is LB_BF16 or LB_F32.
+ * n_splits > 1 (at most 64 tokens only) splits K over that many blocks per tile, so
+ * that a product with few output tiles still uses the whole GPU; it needs `partial`
+ * (n_splits * M * N floats) and `counters` (one int per tile, zero before the first
+ * call; the kernel leaves them zero).  The splits are summed in order. */
 int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
-                    int token_tile, void* stream);
+                    int token_tile, float* partial, int* counters, int n_splits, void* stream);
 int lb_gemm_tcgen05_token_tile(int M, int N);
 /* Reads and clears the status word that a bounded wait sets when it runs out
  * (0: none did).  Synchronises the device. */

@@ -204,7 +204,7 @@ template <int BN, int STAGES, bool TOKENS_ON_LANES, typename TO>
 __global__ void __launch_bounds__(kThreads)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_constant__ CUtensorMap map_col,
                     const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M,
-                    int N, int K, int act, int vec_ok) {
+                    int N, int K, int act, int vec_ok, float* partial, int* counters, int n_splits) {
     extern __shared__ uint8_t smem_raw[];
     using Storage = SharedStorage<BN, STAGES>;
     Storage& s = *reinterpret_cast<Storage*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -215,7 +215,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
     const int n0 = blockIdx.x * (TOKENS_ON_LANES ? BN : kLaneTile);     // first output feature of the tile
     const int m0 = blockIdx.y * (TOKENS_ON_LANES ? kLaneTile : BN);     // first token of the tile
     const int lane_row0 = TOKENS_ON_LANES ? m0 : n0, col_row0 = TOKENS_ON_LANES ? n0 : m0;
-    const int n_kb = (K + kBlockK - 1) / kBlockK;
+    // With n_splits > 1 (few tokens, weights on the lanes) block z of a tile takes a range of the k-blocks.
+    const int all_kb = (K + kBlockK - 1) / kBlockK;
+    const int per_split = (all_kb + n_splits - 1) / n_splits;
+    const int kb_first = (int)blockIdx.z * per_split;
+    const int n_kb = min(all_kb, kb_first + per_split) - kb_first;
     volatile int* abort_flag = &s.abort_flag;
 
     if (threadIdx.x == 0) {
@@ -250,8 +254,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                     break;
                 }
                 mbar_expect_tx(&s.full[st], kStageBytes);
-                tma_load_2d(s.lane_tile[st], &map_lane, &s.full[st], kb * kBlockK, lane_row0);
-                tma_load_2d(s.col_tile[st], &map_col, &s.full[st], kb * kBlockK, col_row0);
+                tma_load_2d(s.lane_tile[st], &map_lane, &s.full[st], (kb_first + kb) * kBlockK, lane_row0);
+                tma_load_2d(s.col_tile[st], &map_col, &s.full[st], (kb_first + kb) * kBlockK, col_row0);
                 issued = kb + 1;
             }
             if (s.abort_flag != 0 && issued > 0) {
@@ -336,7 +340,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                     }
                 }
             }
-        } else {
+        } else if (n_splits == 1) {
             tc_fence_after();
             const int f = n0 + quarter * 32 + lane;
             const float b = (bias != nullptr && f < N) ? bias[f] : 0.0f;
@@ -359,6 +363,54 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                     for (int j = 0; j < 16; ++j) {
                         const int t = m0 + c + j;
                         if (t < M) out[(size_t)t * ldo + f] = lb_from_float<TO>(lb_activate(__uint_as_float(v[j]) + b, act) + r[j]);
+                    }
+                }
+            }
+        } else {
+            // Split K: this block's partial sums go to scratch [split][token][feature]; the block that arrives
+            // last for the tile adds the splits in order (so the sum does not depend on which block that is)
+            // and finishes the elements.
+            tc_fence_after();
+            const int f = n0 + quarter * 32 + lane;
+            float* mine = partial + ((size_t)blockIdx.z * M) * N;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                if (m0 + c >= M) break;
+                uint32_t v[16];
+                tmem_ld16(tmem_row + (uint32_t)c, v);
+                tmem_ld_wait();
+                if (f < N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = m0 + c + j;
+                        if (t < M) mine[(size_t)t * N + f] = __uint_as_float(v[j]);
+                    }
+                }
+            }
+            // Each of the four epilogue warps reports on its own (no barrier among them that a warp which gave
+            // up could leave hanging); the warp that reports last for the tile, over all its blocks, finishes it.
+            __threadfence();
+            __syncwarp();
+            int last = 0;
+            if (lane == 0) {
+                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+                const int done = atomicAdd(&counters[tile], 1);
+                last = done == 4 * n_splits - 1;
+                if (last) counters[tile] = 0;
+            }
+            last = __shfl_sync(0xffffffffu, last, 0);
+            if (last) {
+                __threadfence();
+                for (int q = 0; q < 4; ++q) {
+                    const int ff = n0 + q * 32 + lane;
+                    if (ff >= N) continue;
+                    const float b = bias != nullptr ? bias[ff] : 0.0f;
+                    for (int t = m0; t < min(M, m0 + BN); ++t) {
+                        float acc = 0.0f;
+                        for (int sp = 0; sp < n_splits; ++sp) acc += __ldcg(partial + ((size_t)sp * M + t) * N + ff);
+                        float y = lb_activate(acc + b, act);
+                        if (residual != nullptr) y += residual[(size_t)t * ldr + ff];
+                        out[(size_t)t * ldo + ff] = lb_from_float<TO>(y);
                     }
                 }
             }
@@ -438,7 +490,8 @@ int cached_map(CUtensorMap* out, const void* base, int rows, int cols, int64_t l
 
 template <int BN, int STAGES, bool TOKENS_ON_LANES, typename TO>
 int launch(const CUtensorMap& map_lane, const CUtensorMap& map_col, const float* bias, const float* residual, int64_t ldr,
-           void* out, int64_t ldo, int M, int N, int K, int act, int vec_ok, cudaStream_t stream) {
+           void* out, int64_t ldo, int M, int N, int K, int act, int vec_ok, float* partial, int* counters, int n_splits,
+           cudaStream_t stream) {
     constexpr size_t smem = sizeof(SharedStorage<BN, STAGES>) + 1024;
     static bool configured = false;
     if (!configured) {
@@ -447,9 +500,9 @@ int launch(const CUtensorMap& map_lane, const CUtensorMap& map_col, const float*
         configured = true;
     }
     dim3 grid(TOKENS_ON_LANES ? (N + BN - 1) / BN : (N + kLaneTile - 1) / kLaneTile,
-              TOKENS_ON_LANES ? (M + kLaneTile - 1) / kLaneTile : (M + BN - 1) / BN);
+              TOKENS_ON_LANES ? (M + kLaneTile - 1) / kLaneTile : (M + BN - 1) / BN, n_splits);
     gemm_tcgen05_kernel<BN, STAGES, TOKENS_ON_LANES, TO><<<grid, kThreads, smem, stream>>>(
-        map_lane, map_col, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, vec_ok);
+        map_lane, map_col, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, vec_ok, partial, counters, n_splits);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -469,8 +522,9 @@ extern "C" int lb_gemm_tcgen05_token_tile(int M, int N) {
 
 extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                                const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
-                               int token_tile, void* stream) {
+                               int token_tile, float* partial, int* counters, int n_splits, void* stream) {
     LB_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
+    if (n_splits < 1) n_splits = 1;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0)
         return lb_fail(LB_ERR_UNSUPPORTED,
                        "gemm_tcgen05: TMA needs K and both row strides to be multiples of 8 elements and 16-byte aligned "
@@ -481,6 +535,14 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
     const int tile = token_tile > 0 ? token_tile : lb_gemm_tcgen05_token_tile(M, N);
     LB_CHECK_ARG(tile == 16 || tile == 32 || tile == 64 || tile == 128 || tile == 256, "gemm_tcgen05: token tile %d", tile);
     const bool tokens_on_lanes = tile >= 128;
+    if (n_splits > 1) {
+        const int all_kb = (K + kBlockK - 1) / kBlockK;
+        LB_CHECK_ARG(!tokens_on_lanes && partial != nullptr && counters != nullptr,
+                     "gemm_tcgen05: K is split only with at most 64 tokens, and needs scratch and counters");
+        n_splits = n_splits > all_kb ? all_kb : n_splits;
+        const int per = (all_kb + n_splits - 1) / n_splits;
+        n_splits = (all_kb + per - 1) / per;                  // no block without a k-block
+    }
     const int token_box = tokens_on_lanes ? kLaneTile : tile;
     const int feature_box = tokens_on_lanes ? tile : kLaneTile;       // tile 128/256 names the feature columns there
     LB_CHECK_ARG((M + token_box - 1) / token_box <= 65535, "gemm_tcgen05: M=%d is too large for one launch", M);
@@ -496,7 +558,7 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
                        (residual == nullptr || (((uintptr_t)residual & 15) == 0 && (ldr * 4) % 16 == 0));
 #define LB_GO(BN, STAGES, TOL, TO)                                                                                \
     return launch<BN, STAGES, TOL, TO>(TOL ? map_a : map_w, TOL ? map_w : map_a, bias, residual, ldr, out, ldo, M, N, K, \
-                                       act, vec_ok, s)
+                                       act, vec_ok, partial, counters, n_splits, s)
     if (out_dtype == LB_BF16) {
         switch (tile) {
             case 16: LB_GO(16, 4, false, __nv_bfloat16);

@@ -136,5 +136,5 @@ class DecoderModel:
         y = ctx.workspace.get("head.normed", R, width, self.runtime.dtype)
         self.final_norm.forward(ctx, x, y, R, rows=ctx.logit_rows)
         logits = ctx.workspace.get("logits", R, self.spec.vocab_size, torch.float32)
-        ops.linear(y, self.head_weight, self.head_bias, logits, R)
+        ops.linear(y, self.head_weight, self.head_bias, logits, R, workspace=ctx.workspace)
         return logits[:R]

@@ -29,7 +29,7 @@ _SIGNATURES = {
     "lb_layernorm": [_i, _p, _p, _p, _p, _p, _i, _i, _f, _p],
     "lb_kv_append": [_i, _p, _p, _l, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
-    "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
+    "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
@@ -171,9 +171,21 @@ def tcgen05_accepts(a: torch.Tensor, w: torch.Tensor) -> bool:
             and a.stride(1) == 1 and w.stride(1) == 1)
 
 
+def gemm_splits(m: int, n: int, k: int) -> int:
+    """How many ways K is split for a product of few tokens: enough blocks for most of the GPU's SMs."""
+    if m > 64 or m <= 0:
+        return 1
+    tiles, k_blocks = -(-n // 128), -(-k // 64)
+    return max(1, min(k_blocks, 16, -(-96 // tiles)))
+
+
 def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
-                 activation: str = "none", residual: Optional[torch.Tensor] = None, token_tile: int = 0) -> torch.Tensor:
-    """out[:m] = act(a[:m] @ w.T + bias) + residual on the tcgen05 tensor cores (bfloat16 operands)."""
+                 activation: str = "none", residual: Optional[torch.Tensor] = None, token_tile: int = 0,
+                 partial: Optional[torch.Tensor] = None, counters: Optional[torch.Tensor] = None, n_splits: int = 1
+                 ) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual on the tcgen05 tensor cores (bfloat16 operands).
+    n_splits > 1 (m <= 64) splits K over blocks; `partial` holds n_splits * m * n floats and `counters`
+    one zeroed int per 128 features."""
     n, k = w.shape
     if a.shape[1] != k or out.stride(1) != 1 or out.shape[1] != n:
         raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
@@ -184,7 +196,8 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     check(lib().lb_gemm_tcgen05(_code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
                                 _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
                                 residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n,
-                                k, ACTIVATIONS[activation], token_tile, stream_ptr()), "gemm_tcgen05")
+                                k, ACTIVATIONS[activation], token_tile, _opt(partial, "partial", torch.float32),
+                                _opt(counters, "counters", torch.int32), n_splits, stream_ptr()), "gemm_tcgen05")
     return out
 
 
@@ -197,9 +210,15 @@ def device_status() -> int:
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
-           activation: str = "none", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[:m] = act(a[:m] @ w.T + bias) + residual: the kernel is chosen by type and size."""
+           activation: str = "none", residual: Optional[torch.Tensor] = None, workspace=None) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual: the kernel is chosen by type and size.  With a workspace
+    (scratch buffers) a product of few tokens splits K over blocks."""
     if tcgen05_accepts(a, w):
+        splits = gemm_splits(m, w.shape[0], w.shape[1]) if workspace is not None else 1
+        if splits > 1:
+            partial = workspace.flat("gemm.partial", splits * m * w.shape[0], torch.float32)
+            counters = workspace.flat("gemm.counters", -(-w.shape[0] // 128), torch.int32, zero=True)
+            return gemm_tcgen05(a, w, bias, out, m, activation, residual, 0, partial, counters, splits)
         return gemm_tcgen05(a, w, bias, out, m, activation, residual)
     return gemm_ffma(a, w, bias, out, m, activation, residual)
 

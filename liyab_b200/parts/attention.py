@@ -80,7 +80,7 @@ class CausalSelfAttention:
         s, T, dt = self.spec, ctx.n_tokens, self.runtime.dtype
         ws = ctx.workspace
         qkv = ws.get("attn.qkv", T, self.q_dim + 2 * self.kv_dim, dt)
-        self.qkv.forward(h, qkv, T)
+        self.qkv.forward(h, qkv, T, workspace=ws)
         q = qkv[:, :self.q_dim]
         cache, view = ctx.kv(unit.read)
         page_size = view.group.page_size
@@ -90,4 +90,4 @@ class CausalSelfAttention:
             ops.kv_append(k, v, view.slot_mapping, cache, T, s.n_kv_head, s.head_dim, page_size)
         att = ws.get("attn.out", T, self.q_dim, dt)
         self._attend(ctx, q, cache, view, att, page_size)
-        self.out.forward(att, x, T, residual=x)
+        self.out.forward(att, x, T, residual=x, workspace=ws)

@@ -42,5 +42,5 @@ class DenseFeedForward:
     def forward(self, ctx: StepContext, h: torch.Tensor, x: torch.Tensor) -> None:
         T = ctx.n_tokens
         inner = ctx.workspace.get("ff.inner", T, self.spec.inner, self.runtime.dtype)
-        self.up.forward(h, inner, T, activation=self.spec.activation)
-        self.down.forward(inner, x, T, residual=x)
+        self.up.forward(h, inner, T, activation=self.spec.activation, workspace=ctx.workspace)
+        self.down.forward(inner, x, T, residual=x, workspace=ctx.workspace)

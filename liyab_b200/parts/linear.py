@@ -35,6 +35,6 @@ class Linear:
         return p
 
     def forward(self, a: torch.Tensor, out: torch.Tensor, m: int, activation: str = "none",
-                residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """out[:m] = act(a[:m] @ W^T + b) + residual[:m]."""
-        return ops.linear(a, self.weight, self.bias, out, m, activation, residual)
+                residual: Optional[torch.Tensor] = None, workspace=None) -> torch.Tensor:
+        """out[:m] = act(a[:m] @ W^T + b) + residual[:m]; `workspace` lends scratch for products of few tokens."""
+        return ops.linear(a, self.weight, self.bias, out, m, activation, residual, workspace)

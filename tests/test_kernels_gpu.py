@@ -361,3 +361,32 @@ def test_prefill_attention_finds_a_far_key_and_the_diagonal(dev):
                               1.0 / math.sqrt(head_dim), 0)
         ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
         assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M,N,K,splits", [(64, 768, 3072, 16), (17, 768, 768, 12), (33, 2304, 768, 6), (5, 1000, 200, 4),
+                                          (64, 130, 4096, 7), (20, 256, 64, 5)])
+def test_gemm_tcgen05_split_k(dev, out_dtype, M, N, K, splits):
+    """K split over blocks (few tokens): same result as unsplit to rounding, the same bits on a second call
+    (the splits are summed in order), counters left at zero, residual in place."""
+    from liyab_b200 import ops
+    a, w = _rand((M, K), 26, dev, torch.bfloat16), _rand((N, K), 27, dev, torch.bfloat16, 0.2)
+    bias, res = _rand((N,), 28, dev), _rand((M, N), 29, dev)
+    partial = torch.full((splits * M * N,), float("nan"), device=dev)
+    counters = torch.zeros(-(-N // 128), dtype=torch.int32, device=dev)
+    ref = torch.from_numpy(plain.gelu_tanh((a.double() @ w.double().t() + bias.double()).cpu().numpy())).to(dev)
+    scale = max(1.0, ref.abs().max().item())
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    outs = []
+    for _ in range(2):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
+        ops.gemm_tcgen05(a, w, bias, out, M, "gelu_tanh", partial=partial, counters=counters, n_splits=splits)
+        assert (out.double() - ref).abs().max().item() <= tol * scale
+        assert int(counters.abs().sum()) == 0 and ops.device_status() == 0
+        outs.append(out)
+    assert torch.equal(outs[0], outs[1])
+    if out_dtype == torch.float32:
+        x = res.clone()
+        ops.gemm_tcgen05(a, w, bias, x, M, "none", residual=x, partial=partial, counters=counters, n_splits=splits)
+        want = a.double() @ w.double().t() + bias.double() + res.double()
+        assert (x.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
