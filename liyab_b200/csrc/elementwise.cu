@@ -94,78 +94,12 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int32_t* __r
     }
 }
 
-// The same for rows of at most 1024 values (a multiple of 4): one warp per row, the row, gains and offsets
-// fetched as 16-byte loads that are all in flight together and kept in registers, so the kernel costs one
-// memory round trip instead of three.  The order of every sum is fixed by the width alone.
-template <typename T>
-__global__ void __launch_bounds__(256)
-layernorm_rows_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w,
-                      const float* __restrict__ b, T* __restrict__ y, int n_rows, int width, float eps) {
-    constexpr int kVecs = 8;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x * 8 + warp;
-    if (r >= n_rows) return;
-    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows != nullptr ? rows[r] : r) * width);
-    const int n_vec = width / 4;
-    float4 v[kVecs], g[kVecs], o[kVecs];
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) {
-        const int i = lane + 32 * j;
-        const bool in_row = i < n_vec;
-        v[j] = in_row ? in[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        g[j] = (in_row && w != nullptr) ? reinterpret_cast<const float4*>(w)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-        o[j] = (in_row && b != nullptr) ? reinterpret_cast<const float4*>(b)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    float sum = 0.0f;
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
-    const float mean = lb_warp_sum(sum) / (float)width;
-    float ss = 0.0f;
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) {
-        if (lane + 32 * j < n_vec) {
-            const float d0 = v[j].x - mean, d1 = v[j].y - mean, d2 = v[j].z - mean, d3 = v[j].w - mean;
-            ss = fmaf(d0, d0, ss);
-            ss = fmaf(d1, d1, ss);
-            ss = fmaf(d2, d2, ss);
-            ss = fmaf(d3, d3, ss);
-        }
-    }
-    const float inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)width + eps);
-    T* out = y + (size_t)r * width;
-#pragma unroll
-    for (int j = 0; j < kVecs; ++j) {
-        const int i = lane + 32 * j;
-        if (i < n_vec) {
-            out[4 * i] = lb_from_float<T>((v[j].x - mean) * inv * g[j].x + o[j].x);
-            out[4 * i + 1] = lb_from_float<T>((v[j].y - mean) * inv * g[j].y + o[j].y);
-            out[4 * i + 2] = lb_from_float<T>((v[j].z - mean) * inv * g[j].z + o[j].z);
-            out[4 * i + 3] = lb_from_float<T>((v[j].w - mean) * inv * g[j].w + o[j].w);
-        }
-    }
-}
-
 extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight,
                             const float* bias, void* y, int n_rows, int width, float eps, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0, "layernorm: bad sizes n_rows=%d width=%d", n_rows, width);
     if (n_rows == 0) return LB_OK;
+    const int threads = width >= 2048 ? 256 : 128;   // fixed by the width alone: a row's sums never depend on the batch
     auto s = static_cast<cudaStream_t>(stream);
-    // Which kernel runs is decided by the width (and alignment) alone: a row's sums never depend on the batch.
-    const bool in_registers = width % 4 == 0 && width <= 1024 && ((uintptr_t)x & 15) == 0 &&
-                              (weight == nullptr || ((uintptr_t)weight & 15) == 0) && (bias == nullptr || ((uintptr_t)bias & 15) == 0);
-    if (in_registers) {
-        const int blocks = (n_rows + 7) / 8;
-        if (out_dtype == LB_F32) {
-            layernorm_rows_kernel<float><<<blocks, 256, 0, s>>>(x, rows, weight, bias, (float*)y, n_rows, width, eps);
-        } else if (out_dtype == LB_BF16) {
-            layernorm_rows_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(x, rows, weight, bias, (__nv_bfloat16*)y, n_rows, width, eps);
-        } else {
-            return lb_fail(LB_ERR_INVALID_ARGUMENT, "layernorm: unknown dtype %d", out_dtype);
-        }
-        LB_CHECK_LAUNCH();
-        return LB_OK;
-    }
-    const int threads = width >= 2048 ? 256 : 128;
     if (out_dtype == LB_F32) {
         layernorm_kernel<float><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (float*)y, width, eps);
     } else if (out_dtype == LB_BF16) {
