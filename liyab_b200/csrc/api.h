@@ -85,8 +85,6 @@ int lb_decode_attention(const void* q, int64_t q_stride, const void* cache, cons
                         int* counters, int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
                         int window, int n_splits, void* stream);
 int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
-/* Reads and clears the status word of the decode kernel's bounded waits (0: none ran out).  Synchronises. */
-int lb_decode_attention_status(int* status);
 int64_t lb_decode_attention_scratch_floats(int n_seq, int n_head, int head_dim, int n_splits);
 
 /* Prefill attention, bfloat16, products on the tensor cores: request i brings the

@@ -4,12 +4,10 @@
 // The keys of a request are split into n_splits equal ranges (a function of the
 // token's position and n_splits only), one thread block per (range, key/value
 // head, request), so that even a single request keeps the whole GPU streaming its
-// cache.  A page's keys (and its values) of one head are one contiguous run in
-// the cache, so they come in by the TMA unit (cp.async.bulk, one request per run)
-// into a ring of shared-memory stages guarded by mbarriers; many runs are in
-// flight per SM without holding registers.  Inside a block HD/8 threads share a
-// key, 16 bytes each; every byte of the cache is read once, whatever the number
-// of query heads that share the key/value head (G of them are served together).  Scores, the running
+// cache.  Inside a block HD/8 threads share a key: each loads 16 bytes of the
+// key row and of the value row, so a warp reads 512 contiguous bytes per load and
+// every byte of the cache is read once, whatever the number of query heads that
+// share the key/value head (G of them are served together).  Scores, the running
 // maximum, the sum and the weighted values are 32-bit (exp2 of scores pre-scaled
 // by log2 e).  Partial results (maximum, sum, unnormalised values) of the ranges
 // go to scratch memory; the block that finishes last for a (request, head) merges
@@ -26,6 +24,7 @@ namespace {
 
 constexpr int kWarps = 4;
 constexpr int kThreads = kWarps * 32;
+constexpr int kUnroll = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // Eight bfloat16 values travel as one 16-byte load (a uint4: the compiler splits a struct of four bfloat162
@@ -54,52 +53,12 @@ __device__ __forceinline__ void merge_state(float& m, float& l, float (&acc)[N],
     m = m_new;
 }
 
-constexpr int kMaxStages = 8;
-constexpr int kMaxPagesCached = 256;
-constexpr long long kWaitLimitCycles = 4000000000ll;       // about two seconds
-
-__device__ int g_decode_status = 0;      // 0, or where a bounded wait ran out
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-
-// Bounded wait on an mbarrier phase; false when the limit ran out or another thread already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag != 0 || clock64() - t0 > kWaitLimitCycles) return false;
-    }
-}
-
-// One contiguous run of bytes (a page's keys or values of one head) from global to shared memory by the TMA
-// unit, signalling the mbarrier with the bytes that landed.  Both addresses and the size are multiples of 16.
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-
 template <int HD, int G>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache,
                         const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                         __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
-                        int* __restrict__ counters, int n_kv_head, int page_shift, float scale, int window, int n_splits,
-                        int n_stages) {
+                        int* __restrict__ counters, int n_kv_head, int page_shift, float scale, int window, int n_splits) {
     constexpr int TPK = HD / 8;                 // threads that share a key
     constexpr int KPW = 32 / TPK;               // keys a warp covers with one load
     constexpr int STATE = HD + 2;               // m, l, values
@@ -136,102 +95,51 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
         for (int i = 0; i < 8; ++i) acc[g][i] = 0.0f;
     }
 
-    // The pages of this block's key range stream through a ring of shared-memory stages: one thread asks the
-    // TMA unit for a page's keys and values of this head (two contiguous runs), the warps compute on the stage
-    // whose bytes have landed (full barrier) and hand it back (empty barrier, one arrival per warp).
-    extern __shared__ __align__(128) uint8_t stage_bytes[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages];
-    __shared__ int pages_s[kMaxPagesCached];
-    __shared__ int abort_s;
-    const int page_elems = page_size * HD;
-    const uint32_t run_bytes = (uint32_t)page_elems * sizeof(__nv_bfloat16);
-    __nv_bfloat16* stages = reinterpret_cast<__nv_bfloat16*>(stage_bytes);      // [n_stages][K|V][page_size][HD]
-    const int p_lo = begin >> page_shift;
-    const int n_pages = end > begin ? ((end - 1) >> page_shift) + 1 - p_lo : 0;
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < n_stages; ++i) {
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&full_bar[i])), "r"(1));
-            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(&empty_bar[i])), "r"(kWarps));
+    // The loop bound is the same for every lane of a warp (the shuffles below need all of them).
+    for (int jb = begin + warp * KPW; jb < end; jb += kWarps * KPW * kUnroll) {
+        const int j0 = jb + kgroup;
+        Vec8 kv[kUnroll], vv[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int j = j0 + u * kWarps * KPW;
+            if (j < end) {
+                const int page = table[j >> page_shift];
+                const __nv_bfloat16* row = cache + (size_t)page * 2 * plane +
+                                           ((size_t)kvh * page_size + (j & (page_size - 1))) * HD + sub * 8;
+                kv[u] = __ldg(reinterpret_cast<const Vec8*>(row));
+                vv[u] = __ldg(reinterpret_cast<const Vec8*>(row + plane));
+            }
         }
-        abort_s = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    for (int i = threadIdx.x; i < min(n_pages, kMaxPagesCached); i += kThreads) pages_s[i] = table[p_lo + i];
-    __syncthreads();
-    auto issue = [&](int i) {
-        const int st = i % n_stages;
-        const int page = i < kMaxPagesCached ? pages_s[i] : table[p_lo + i];
-        const __nv_bfloat16* src = cache + (size_t)page * 2 * plane + (size_t)kvh * page_elems;
-        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(&full_bar[st])), "r"(2 * run_bytes)
-                     : "memory");
-        bulk_load(stages + (size_t)st * 2 * page_elems, src, run_bytes, &full_bar[st]);
-        bulk_load(stages + (size_t)(st * 2 + 1) * page_elems, src + plane, run_bytes, &full_bar[st]);
-    };
-    if (threadIdx.x == 0)
-        for (int i = 0; i < min(n_stages, n_pages); ++i) issue(i);
-    int issued_to = min(n_stages, n_pages);          // meaningful in thread 0 only
-    for (int i = 0; i < n_pages; ++i) {
-        const int st = i % n_stages;
-        const uint32_t ph = (uint32_t)(i / n_stages) & 1u;
-        if (!mbar_wait(&full_bar[st], ph, &abort_s)) {
-            atomicCAS(&g_decode_status, 0, (1 << 8) | st);
-            abort_s = 1;
-            break;
-        }
-        const __nv_bfloat16* ks = stages + (size_t)st * 2 * page_elems;
-        const __nv_bfloat16* vs = ks + page_elems;
-        const int page_first = (p_lo + i) << page_shift;
-        for (int kb = 0; kb < page_size; kb += kWarps * KPW) {      // same trip count for every lane (shuffles below)
-            const int kk = kb + warp * KPW + kgroup;
-            const int j = page_first + kk;
-            const bool live = kk < page_size && j >= begin && j < end;
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+            const int j = j0 + u * kWarps * KPW;
+            const bool live = j < end;          // uniform within the TPK threads of a key
             float kf[8], vf[8];
             if (live) {
-                unpack8(*reinterpret_cast<const Vec8*>(ks + kk * HD + sub * 8), kf);
-                unpack8(*reinterpret_cast<const Vec8*>(vs + kk * HD + sub * 8), vf);
+                unpack8(kv[u], kf);
+                unpack8(vv[u], vf);
             } else {
 #pragma unroll
-                for (int t = 0; t < 8; ++t) kf[t] = vf[t] = 0.0f;
+                for (int i = 0; i < 8; ++i) kf[i] = vf[i] = 0.0f;
             }
 #pragma unroll
             for (int g = 0; g < G; ++g) {
-                float sc = 0.0f;
+                float s = 0.0f;
 #pragma unroll
-                for (int t = 0; t < 8; ++t) sc = fmaf(qf[g][t], kf[t], sc);
+                for (int i = 0; i < 8; ++i) s = fmaf(qf[g][i], kf[i], s);
 #pragma unroll
-                for (int o = TPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
+                for (int o = TPK / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
                 if (live) {
-                    const float m_new = fmaxf(m[g], sc);
+                    const float m_new = fmaxf(m[g], s);
                     const float corr = exp2f(m[g] - m_new);
-                    const float pj = exp2f(sc - m_new);
-                    l[g] = l[g] * corr + pj;
+                    const float p = exp2f(s - m_new);
+                    l[g] = l[g] * corr + p;
 #pragma unroll
-                    for (int t = 0; t < 8; ++t) acc[g][t] = fmaf(pj, vf[t], acc[g][t] * corr);
+                    for (int i = 0; i < 8; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i] * corr);
                     m[g] = m_new;
                 }
             }
         }
-        __syncwarp();
-        if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&empty_bar[st])) : "memory");
-        if (threadIdx.x == 0 && i + n_stages < n_pages) {
-            if (!mbar_wait(&empty_bar[st], ph, &abort_s)) {
-                atomicCAS(&g_decode_status, 0, (2 << 8) | st);
-                abort_s = 1;
-            } else {
-                issue(i + n_stages);
-                issued_to = i + n_stages + 1;
-            }
-        }
-    }
-    __syncthreads();          // every thread is out of the loop before anyone looks at the verdict
-    if (abort_s != 0) {
-        // Gave up: leave no copy in flight (the last stage asked for signals its barrier when its bytes landed),
-        // write nothing that could be taken for a result, and return.
-        if (threadIdx.x == 0 && issued_to > 0) {
-            volatile int never = 0;
-            mbar_wait(&full_bar[(issued_to - 1) % n_stages], (uint32_t)((issued_to - 1) / n_stages) & 1u, &never);
-        }
-        return;
     }
     // Merge the key groups of a warp, then the warps, in a fixed order.
 #pragma unroll
@@ -319,21 +227,9 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* po
            int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_kv_head,
            int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
     dim3 grid(n_splits, n_kv_head, n_seq);
-    // As many stages as fit 32 KB (at least two, at most eight): several blocks per SM keep their rings in flight.
-    const size_t stage_bytes = (size_t)2 * ((size_t)1 << page_shift) * HD * sizeof(__nv_bfloat16);
-    int n_stages = (int)(32768 / stage_bytes);
-    n_stages = n_stages < 2 ? 2 : n_stages > kMaxStages ? kMaxStages : n_stages;
-    const size_t smem = stage_bytes * n_stages;
-    LB_CHECK_ARG(smem <= 160 * 1024, "decode attention: pages of %d positions with head_dim %d do not fit shared memory",
-                 1 << page_shift, HD);
-    static size_t configured = 0;
-    if (smem > 48 * 1024 && smem > configured) {
-        LB_CHECK_CUDA(cudaFuncSetAttribute(decode_attention_kernel<HD, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = smem;
-    }
-    decode_attention_kernel<HD, G><<<grid, kThreads, smem, s>>>(
+    decode_attention_kernel<HD, G><<<grid, kThreads, 0, s>>>(
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits, n_stages);
+        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
@@ -356,14 +252,6 @@ int by_group(int group, const void* q, int64_t q_stride, const void* cache, cons
 }
 
 }  // namespace
-
-// Reads and clears the status word of the kernel's bounded waits (0: none ran out).  Synchronises the device.
-extern "C" int lb_decode_attention_status(int* status) {
-    int zero = 0;
-    LB_CHECK_CUDA(cudaMemcpyFromSymbol(status, g_decode_status, sizeof(int)));
-    LB_CHECK_CUDA(cudaMemcpyToSymbol(g_decode_status, &zero, sizeof(int)));
-    return LB_OK;
-}
 
 // Whether the decode kernel takes this shape (else the caller uses the generic kernel).
 extern "C" int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size) {

@@ -31,7 +31,6 @@ _SIGNATURES = {
     "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
     "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
-    "lb_decode_attention_status": [_p],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
@@ -205,10 +204,9 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
 def device_status() -> int:
     """0 unless a bounded wait inside a kernel ran out since the last call (then where it gave up).
     Synchronises the device."""
-    status, other = ctypes.c_int(0), ctypes.c_int(0)
+    status = ctypes.c_int(0)
     check(lib().lb_gemm_tcgen05_status(ctypes.byref(status)), "device_status")
-    check(lib().lb_decode_attention_status(ctypes.byref(other)), "device_status")
-    return status.value or other.value
+    return status.value
 
 
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,

@@ -301,7 +301,7 @@ def test_decode_attention(dev, n_head, n_kv_head, head_dim, page_size, window, s
         ops.decode_attention(q, cache, positions, table, out, partial, counters, S, n_head, n_kv_head, head_dim,
                              page_size, scale, window, splits)
         assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2
-        assert int(counters.abs().sum()) == 0 and ops.device_status() == 0
+        assert int(counters.abs().sum()) == 0
     generic = torch.empty_like(q)
     ops.paged_attention_generic(q, cache, tok_seq, positions, table, generic, S, n_head, n_kv_head, head_dim, page_size,
                                 scale, window)
