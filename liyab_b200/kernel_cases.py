@@ -61,13 +61,27 @@ def case_decode_attention(args) -> None:
     q = torch.randn(B, H * hd, device=dev).to(torch.bfloat16)
     out = torch.empty_like(q)
     positions = torch.full((B,), ctx - 1, dtype=torch.int32, device=dev)
-    splits = ops.decode_splits(B, H, ctx)
+    tensor = ops.decode_attention_kernels(H, H, hd, ps)[1] and not args.scalar
+    splits = args.splits or ops.decode_splits(B, H, ctx, tensor_cores=tensor)
     partial = torch.empty(B * H * splits * (hd + 2), device=dev)
     counters = torch.zeros(B * H, dtype=torch.int32, device=dev)
-    ms = _timed(lambda: ops.decode_attention(q, cache, positions, table, out, partial, counters, B, H, H, hd, ps,
-                                             hd ** -0.5, 0, splits), args.reps)
+    def launch():
+        ops.decode_attention(q, cache, positions, table, out, partial, counters, B, H, H, hd, ps, hd ** -0.5, 0, splits,
+                             tensor_cores=tensor)
+
+    if args.graph:                      # 20 launches in one CUDA graph: the kernel's time without the host's launch cost
+        launch()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(20):
+                launch()
+        ms = _timed(graph.replay, max(1, args.reps // 20)) / 20
+    else:
+        ms = _timed(launch, args.reps)
     nbytes = B * ctx * 2 * H * hd * 2
-    print(f"decode-attention batch={B} heads={H} head_dim={hd} context={ctx} splits={splits}: {ms * 1e3:.1f} us, "
+    kind = "tensor-core" if tensor else "scalar"
+    print(f"decode-attention ({kind}) batch={B} heads={H} head_dim={hd} context={ctx} splits={splits}: {ms * 1e3:.1f} us, "
           f"{nbytes / ms / 1e6:.1f} GB/s of cache ({nbytes / 1e6:.1f} MB)")
 
 
@@ -142,6 +156,9 @@ def main(argv=None) -> int:
     d.add_argument("--head-dim", type=int, default=64)
     d.add_argument("--context", type=int, default=768)
     d.add_argument("--reps", type=int, default=20)
+    d.add_argument("--splits", type=int, default=0, help="key ranges per request and head (0: the engine's choice)")
+    d.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
+    d.add_argument("--scalar", action="store_true", help="the scalar kernel even where the tensor-core one takes the shape")
     for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
+    "lb_decode_attention_mma": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "lb_decode_attention_mma_supports": [_i, _i, _i, _i],
     "lb_prefill_attention": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_prefill_attention_supports": [_i, _i, _i, _i],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
@@ -242,23 +244,35 @@ def paged_attention_generic(q: torch.Tensor, cache: torch.Tensor, tok_seq: torch
     return out
 
 
+def decode_attention_kernels(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> tuple:
+    """(scalar kernel takes the shape, tensor-core kernel takes it)."""
+    return (bool(lib().lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size)),
+            bool(lib().lb_decode_attention_mma_supports(n_head, n_kv_head, head_dim, page_size)))
+
+
 def decode_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> bool:
-    return bool(lib().lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
+    return any(decode_attention_kernels(n_head, n_kv_head, head_dim, page_size))
 
 
-def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0) -> int:
-    """How many ways each request's keys are split: enough blocks for about four full waves of the GPU (a
-    single wave and a bit leaves most SMs idle for the bit), but no ranges shorter than 128 keys at the
-    longest context.  A function of the batch's shape only, so a captured step and an eager one split alike."""
+def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0, tensor_cores: bool = False) -> int:
+    """How many ways each request's keys are split.  Scalar kernel: enough blocks for about four full waves of
+    the GPU, but no ranges shorter than 128 keys at the longest context.  Tensor-core kernel: a block gets through
+    its keys far faster, so fewer and longer ranges (about 450 blocks, 192 keys or more each); from 32 requests of
+    12 heads on, none.  A function of the batch's shape only, so a captured step and an eager one split alike."""
+    work = max(1, n_seq * n_kv_head)
+    if tensor_cores:
+        cap = max(1, max_context // 192) if max_context else 32
+        return max(1, min(32, cap, 444 // work))
     cap = max(1, max_context // 128) if max_context else 32
-    return max(1, min(32, cap, -(-2960 // max(1, n_seq * n_kv_head))))
+    return max(1, min(32, cap, -(-2960 // work)))
 
 
 def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
                      out: torch.Tensor, partial: Optional[torch.Tensor], counters: Optional[torch.Tensor], n_seq: int,
                      n_head: int, n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int,
-                     n_splits: int) -> torch.Tensor:
-    """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways."""
+                     n_splits: int, tensor_cores: Optional[bool] = None) -> torch.Tensor:
+    """Attention of one new token per request over its pages (bfloat16), keys split `n_splits` ways.
+    `tensor_cores`: None picks the tensor-core kernel where it takes the shape, else the scalar one."""
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise invalid_argument("decode attention takes bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1 or q.stride(0) % 8 != 0 or q.data_ptr() % 16 != 0:
@@ -267,7 +281,10 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
         need = n_seq * n_head * n_splits * (head_dim + 2)
         if partial is None or counters is None or partial.numel() < need or counters.numel() < n_seq * n_kv_head:
             raise invalid_argument("decode attention: scratch buffers are missing or too small")
-    check(lib().lb_decode_attention(
+    if tensor_cores is None:
+        tensor_cores = decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
+    fn = lib().lb_decode_attention_mma if tensor_cores else lib().lb_decode_attention
+    check(fn(
         _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,

@@ -53,20 +53,22 @@ class CausalSelfAttention:
         return None
 
     def _attend(self, ctx: StepContext, q, cache, view, att, page_size: int) -> None:
-        """Chooses the attention kernel.  bfloat16: the split-key decode kernel for steps of single tokens,
-        the tensor-core kernel for steps with prompt portions, where they take the shape.  Else the generic
+        """Chooses the attention kernel.  bfloat16: a split-key decode kernel for steps of single tokens (on the
+        tensor cores where that one takes the shape, else scalar), the tensor-core prefill kernel for steps with
+        prompt portions, where they take the shape.  Else the generic
         kernel; all of the 32-bit engine runs on it, so that there a position's result has the same bits
         however the work was cut."""
         s, T = self.spec, ctx.n_tokens
-        if (ctx.decode_only and self.runtime.dtype == torch.bfloat16
-                and ops.decode_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):
-            splits = ops.decode_splits(T, s.n_kv_head, ctx.max_positions)
+        scalar, tensor = (ops.decode_attention_kernels(s.n_head, s.n_kv_head, s.head_dim, page_size)
+                          if ctx.decode_only and self.runtime.dtype == torch.bfloat16 else (False, False))
+        if scalar or tensor:
+            splits = ops.decode_splits(T, s.n_kv_head, ctx.max_positions, tensor_cores=tensor)
             partial = counters = None
             if splits > 1:
                 partial = ctx.workspace.flat("attn.decode.partial", T * s.n_head * splits * (s.head_dim + 2), torch.float32)
                 counters = ctx.workspace.flat("attn.decode.counters", T * s.n_kv_head, torch.int32, zero=True)
             ops.decode_attention(q, cache, ctx.positions, view.block_table, att, partial, counters, T, s.n_head,
-                                 s.n_kv_head, s.head_dim, page_size, s.scale, s.window, splits)
+                                 s.n_kv_head, s.head_dim, page_size, s.scale, s.window, splits, tensor_cores=tensor)
             return
         if (self.runtime.dtype == torch.bfloat16
                 and ops.prefill_attention_supports(s.n_head, s.n_kv_head, s.head_dim, page_size)):

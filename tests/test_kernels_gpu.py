@@ -91,7 +91,8 @@ def _paged_case(dev, dtype, n_head, n_kv_head, head_dim, page_size, lens, q_lens
     S = len(lens)
     n_pages = sum(-(-l // page_size) for l in lens) + 3
     perm = rng.permutation(n_pages)
-    cache = torch.zeros((n_pages, 2, n_kv_head, page_size, head_dim), dtype=dtype)
+    # What no request has written holds NaN: a kernel that lets such a place reach its output, even with weight 0, shows.
+    cache = torch.full((n_pages, 2, n_kv_head, page_size, head_dim), float("nan"), dtype=dtype)
     width = max(-(-l // page_size) for l in lens)
     table = np.full((S, width), -1, dtype=np.int32)
     qs, refs, tok_seq, positions = [], [], [], []
@@ -282,12 +283,14 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_fetch(dev):
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window,splits", [
     (12, 12, 64, 16, 0, 1), (12, 12, 64, 16, 0, 5), (4, 4, 16, 16, 0, 3), (3, 3, 32, 32, 0, 32), (8, 2, 128, 16, 0, 4),
-    (16, 2, 64, 64, 0, 7), (2, 1, 256, 16, 0, 2), (6, 3, 64, 16, 33, 4), (4, 4, 32, 16, 5, 16)])
+    (16, 2, 64, 64, 0, 7), (2, 1, 256, 16, 0, 2), (6, 3, 64, 16, 33, 4), (4, 4, 32, 16, 5, 16), (32, 2, 64, 16, 0, 3),
+    (5, 5, 128, 32, 70, 2), (16, 1, 128, 16, 0, 1)])
 def test_decode_attention(dev, n_head, n_kv_head, head_dim, page_size, window, splits):
     """One new token per request over its pages, keys split several ways, against float64; the same
     scratch is used by two launches in a row (the kernel must leave its counters at zero)."""
     from liyab_b200 import ops
-    assert ops.decode_attention_supports(n_head, n_kv_head, head_dim, page_size)
+    scalar, tensor = ops.decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)
+    assert scalar or tensor
     lens = [1, 2, 17, 64, 65, 300, 1024, 33]
     scale = 0.5 / math.sqrt(head_dim)
     q, cache, tok_seq, positions, table, refs = _paged_case(dev, torch.bfloat16, n_head, n_kv_head, head_dim, page_size,
@@ -296,11 +299,12 @@ def test_decode_attention(dev, n_head, n_kv_head, head_dim, page_size, window, s
     partial = torch.full((S * n_head * splits * (head_dim + 2),), float("nan"), device=dev)
     counters = torch.zeros(S * n_kv_head, dtype=torch.int32, device=dev)
     ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
-    for _ in range(2):
+    kinds = ([False] if scalar else []) + ([True] if tensor else [])
+    for tensor_cores in kinds + kinds:          # each kernel twice over the same scratch
         out = torch.full_like(q, float("nan"))
         ops.decode_attention(q, cache, positions, table, out, partial, counters, S, n_head, n_kv_head, head_dim,
-                             page_size, scale, window, splits)
-        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2
+                             page_size, scale, window, splits, tensor_cores=tensor_cores)
+        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"tensor_cores={tensor_cores}"
         assert int(counters.abs().sum()) == 0
     generic = torch.empty_like(q)
     ops.paged_attention_generic(q, cache, tok_seq, positions, table, generic, S, n_head, n_kv_head, head_dim, page_size,
@@ -316,11 +320,12 @@ def test_decode_attention_finds_a_far_key(dev):
                                                           [1024], [1], seed=key_pos, boost=(key_pos, 4.0))
         partial = torch.zeros(n_head * splits * (head_dim + 2), device=dev)
         counters = torch.zeros(n_kv_head, dtype=torch.int32, device=dev)
-        out = torch.empty_like(q)
-        ops.decode_attention(q, cache, positions, table, out, partial, counters, 1, n_head, n_kv_head, head_dim,
-                             page_size, 1.0 / math.sqrt(head_dim), 0, splits)
         ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
-        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
+        for tensor_cores in (False, True):
+            out = torch.empty_like(q)
+            ops.decode_attention(q, cache, positions, table, out, partial, counters, 1, n_head, n_kv_head, head_dim,
+                                 page_size, 1.0 / math.sqrt(head_dim), 0, splits, tensor_cores=tensor_cores)
+            assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}, tensor_cores={tensor_cores}"
 
 
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [

@@ -57,7 +57,7 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(n_head, n_kv_head, head_d
         partial = torch.empty(n_seq * n_head * splits * (head_dim + 2), device=dev)
         counters = torch.zeros(n_seq * n_kv_head, dtype=torch.int32, device=dev)
         ops.decode_attention(q, cache, positions, table, want, partial, counters, n_seq, n_head, n_kv_head, head_dim,
-                             page_size, scale, 0, splits)
+                             page_size, scale, 0, splits, tensor_cores=False)    # the kernel the entry point is a variant of
         got = torch.full_like(q, float("nan"))
         rc = fn(q.data_ptr(), q.stride(0), cache.data_ptr(), positions.data_ptr(), table.data_ptr(), table.stride(0),
                 got.data_ptr(), got.stride(0), n_seq, n_head, n_kv_head, head_dim, page_size, scale, 0, splits, stream)
