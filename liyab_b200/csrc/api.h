@@ -60,6 +60,19 @@ int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, in
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
                     int token_tile, float* partial, int* counters, int n_splits, void* stream);
 int lb_gemm_tcgen05_token_tile(int M, int N);
+/* The same product for more than 64 tokens as a persistent kernel: one block per SM walks tiles of 128 tokens x
+ * feature_tile features, operands, residual and result all moved by TMA, the epilogue of a tile under the products
+ * of the next.  lb_gemm_persistent_tile returns the feature tile it would choose, or 0 where the kernel does not
+ * take the product (64 tokens or fewer; a row stride or base off TMA's 16-byte rule; a residual with bfloat16
+ * output).  feature_tile 0 = that choice; else a multiple of 32 (float32 out) or 64 (bfloat16 out) up to 256. */
+int lb_gemm_persistent_tile(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* residual,
+                            int64_t ldr, const void* out, int64_t ldo, int M, int N, int K);
+/* Profiling aid: from now on every launch writes eight time stamps per block (nanoseconds) to `buffer` (device
+ * memory, 8 * number of SMs 64-bit words); null switches it off. */
+int lb_gemm_persistent_timing(unsigned long long* buffer);
+int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                       const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                       int feature_tile, void* stream);
 /* Reads and clears the status word that a bounded wait sets when it runs out
  * (0: none did).  Synchronises the device. */
 int lb_gemm_tcgen05_status(int* status);

@@ -26,8 +26,7 @@
 // (16-byte TMA rule); everything else is refused by the host function.
 #include "api.h"
 #include "common.cuh"
-
-#include <cuda.h>
+#include "tcgen05.cuh"
 
 #include <map>
 #include <mutex>
@@ -35,135 +34,11 @@
 
 namespace {
 
-constexpr int kBlockK = 64;          // one 128-byte swizzle atom of bfloat16
-constexpr int kLaneTile = 128;       // UMMA M
-constexpr int kUmmaK = 16;
+using namespace lb_tc;
+
 constexpr int kThreads = 192;
-constexpr long long kWaitLimitCycles = 4000000000ll;     // about two seconds at the SM's top clock
 
 __device__ int g_status = 0;         // 0 ok; else (site << 8) | detail of the first bounded wait that ran out
-
-// ------------------------------------------------------------------ PTX wrappers
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-// Waits for the barrier's phase; false when the limit ran out, or when another role already gave up
-// (abort_flag, where given).  The limit is counted on the SM's own cycle counter, which costs a few cycles
-// to read, and only after a few hundred polls have failed: the common wait never reads a clock.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-#pragma unroll 1
-    for (int i = 0; i < 256; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; ++i)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (abort_flag != nullptr && *abort_flag != 0) return false;
-        if (clock64() - t0 > kWaitLimitCycles) return false;
-    }
-}
-
-__device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
-    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_relinquish() {
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor of a K-major tile laid out by TMA with the
-// 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
-// Fields (PTX "matrix descriptor"): start address >> 4 in bits [0,14), leading
-// byte offset >> 4 in [16,30) (unused for swizzled K-major, set to 1), stride
-// byte offset >> 4 in [32,46) (1024 >> 4), version 1 in [46,48), swizzle mode 2
-// (128 bytes) in [61,64).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)(1024 >> 4) << 32;
-    d |= (uint64_t)1 << 46;
-    d |= (uint64_t)2 << 61;
-    return d;
-}
-
-// Instruction descriptor, kind::f16: D format F32 (1) in [4,6), A and B format
-// BF16 (1) in [7,10) and [10,13), both operands K-major (bits 15, 16 = 0),
-// N >> 3 in [17,23), M >> 4 in [24,29).
-__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
-        : "r"(taddr)
-        : "memory");
-}
-
-__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<const uint32_t*>(&v);
-}
-
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ------------------------------------------------------------------ the kernel
 
@@ -434,48 +309,35 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// A [rows, cols] bfloat16 matrix with `ld` elements between rows, fetched in boxes of [box_rows, 64].
-int make_map(CUtensorMap* map, const void* base, int rows, int cols, int64_t ld, int box_rows) {
+// A [rows, cols] matrix with `ld` elements between rows, moved in boxes of [box_rows, 128 bytes].
+int make_map(CUtensorMap* map, const void* base, int elem_bytes, int rows, int cols, int64_t ld, int box_rows) {
     EncodeTiledFn fn = encode_fn();
     if (fn == nullptr) return lb_fail(LB_ERR_BACKEND, "gemm_tcgen05: cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(__nv_bfloat16)};
-    const cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * (cuuint64_t)elem_bytes};
+    const cuuint32_t box[2] = {(cuuint32_t)(128 / elem_bytes), (cuuint32_t)box_rows};
     const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const CUresult r = fn(map, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2,
+                          const_cast<void*>(base), dims, strides, box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS)
-        return lb_fail(LB_ERR_BACKEND, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld)", (int)r,
-                       rows, cols, (long long)ld);
+        return lb_fail(LB_ERR_BACKEND, "gemm_tcgen05: cuTensorMapEncodeTiled failed with %d (rows %d cols %d ld %lld box rows %d)",
+                       (int)r, rows, cols, (long long)ld, box_rows);
     return LB_OK;
 }
 
 // Tensor maps are cached by what they describe: encoding costs microseconds on the host, a decode step has dozens.
 struct MapKey {
     const void* base;
-    int rows, cols, box_rows;
+    int elem_bytes, rows, cols, box_rows;
     int64_t ld;
     bool operator<(const MapKey& o) const {
-        return std::tie(base, rows, cols, box_rows, ld) < std::tie(o.base, o.rows, o.cols, o.box_rows, o.ld);
+        return std::tie(base, elem_bytes, rows, cols, box_rows, ld) < std::tie(o.base, o.elem_bytes, o.rows, o.cols, o.box_rows, o.ld);
     }
 };
 
 int cached_map(CUtensorMap* out, const void* base, int rows, int cols, int64_t ld, int box_rows) {
-    static std::map<MapKey, CUtensorMap> cache;
-    static std::mutex mu;
-    const MapKey key{base, rows, cols, box_rows, ld};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it == cache.end()) {
-        CUtensorMap m;
-        const int rc = make_map(&m, base, rows, cols, ld, box_rows);
-        if (rc != LB_OK) return rc;
-        if (cache.size() > 4096) cache.clear();
-        it = cache.emplace(key, m).first;
-    }
-    *out = it->second;
-    return LB_OK;
+    return lb_tensor_map_2d(out, base, 2, rows, cols, ld, box_rows);
 }
 
 template <int BN, int STAGES, bool TOKENS_ON_LANES, typename TO>
@@ -498,6 +360,30 @@ int launch(const CUtensorMap& map_lane, const CUtensorMap& map_col, const float*
 }
 
 }  // namespace
+
+int lb_tensor_map_2d(CUtensorMap* out, const void* base, int elem_bytes, int rows, int cols, int64_t ld, int box_rows) {
+    static std::map<MapKey, CUtensorMap> cache;
+    static std::mutex mu;
+    const MapKey key{base, elem_bytes, rows, cols, box_rows, ld};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it == cache.end()) {
+        CUtensorMap m;
+        const int rc = make_map(&m, base, elem_bytes, rows, cols, ld, box_rows);
+        if (rc != LB_OK) return rc;
+        if (cache.size() > 4096) cache.clear();
+        it = cache.emplace(key, m).first;
+    }
+    *out = it->second;
+    return LB_OK;
+}
+
+int lb_tc_status_word(int** out) {
+    static int* addr = nullptr;
+    if (addr == nullptr) LB_CHECK_CUDA(cudaGetSymbolAddress(reinterpret_cast<void**>(&addr), g_status));
+    *out = addr;
+    return LB_OK;
+}
 
 // The tile along the tokens for M tokens: 16, 32 or 64 tokens as accumulator columns (weights on the
 // lanes) up to 64 tokens; beyond that 128 tokens on the lanes (reported as 128, or 256 when the product is

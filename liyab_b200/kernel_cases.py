@@ -36,6 +36,17 @@ def _timed(fn, reps: int, warmup: int = 2) -> float:
     return s.elapsed_time(e) / reps
 
 
+def _graph_timed(launch, reps: int, per_graph: int = 20) -> float:
+    """Time per launch with `per_graph` launches captured in one CUDA graph: the kernel without the host's launch cost."""
+    launch()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(per_graph):
+            launch()
+    return _timed(graph.replay, max(1, reps // per_graph)) / per_graph
+
+
 def case_gemm(args) -> None:
     from . import ops
     dev = torch.device("cuda:0")
@@ -45,7 +56,13 @@ def case_gemm(args) -> None:
     bias = torch.randn(args.n, device=dev)
     out = torch.zeros(args.m, args.n, dtype=odt, device=dev)
     res = out if odt == torch.float32 else None
-    ms = _timed(lambda: ops.gemm_tcgen05(a, w, bias, out, args.m, args.act, residual=res, token_tile=args.tile), args.reps)
+    if args.one_tile:
+        launch = lambda: ops.gemm_tcgen05(a, w, bias, out, args.m, args.act, residual=res, token_tile=args.tile)
+    elif args.m > 64 and ops.gemm_persistent_tile(a, w, out, args.m, res) > 0:
+        launch = lambda: ops.gemm_persistent(a, w, bias, out, args.m, args.act, residual=res, feature_tile=args.tile)
+    else:
+        launch = lambda: ops.linear(a, w, bias, out, args.m, args.act, residual=res)
+    ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
     print(f"gemm M={args.m} N={args.n} K={args.k} out={args.out}: {ms * 1e3:.1f} us per launch (includes the host's "
           f"launch cost when the kernel is shorter), {2 * args.m * args.n * args.k / ms / 1e9:.1f} TFLOP/s, "
           f"{(args.n * args.k * 2) / ms / 1e6:.1f} GB/s of weights, status {ops.device_status()}")
@@ -69,16 +86,7 @@ def case_decode_attention(args) -> None:
         ops.decode_attention(q, cache, positions, table, out, partial, counters, B, H, H, hd, ps, hd ** -0.5, 0, splits,
                              tensor_cores=tensor)
 
-    if args.graph:                      # 20 launches in one CUDA graph: the kernel's time without the host's launch cost
-        launch()
-        torch.cuda.synchronize()
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(20):
-                launch()
-        ms = _timed(graph.replay, max(1, args.reps // 20)) / 20
-    else:
-        ms = _timed(launch, args.reps)
+    ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
     nbytes = B * ctx * 2 * H * hd * 2
     kind = "tensor-core" if tensor else "scalar"
     print(f"decode-attention ({kind}) batch={B} heads={H} head_dim={hd} context={ctx} splits={splits}: {ms * 1e3:.1f} us, "
@@ -148,7 +156,9 @@ def main(argv=None) -> int:
     g.add_argument("--k", type=int, default=3072)
     g.add_argument("--out", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--act", default="none", choices=["none", "gelu_tanh", "gelu_erf"])
-    g.add_argument("--tile", type=int, default=0)
+    g.add_argument("--tile", type=int, default=0, help="feature tile of the persistent kernel (token tile with --one-tile)")
+    g.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
+    g.add_argument("--one-tile", action="store_true", help="the one-tile-per-block kernel also for many tokens")
     g.add_argument("--reps", type=int, default=20)
     d = sub.add_parser("decode-attention")
     d.add_argument("--batch", type=int, default=64)

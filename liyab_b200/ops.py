@@ -31,6 +31,9 @@ _SIGNATURES = {
     "lb_gemm_ffma": [_i, _i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
     "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
+    "lb_gemm_persistent_tile": [_i, _p, _l, _p, _l, _p, _l, _p, _l, _i, _i, _i],
+    "lb_gemm_persistent_timing": [_p],
+    "lb_gemm_persistent": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
@@ -203,6 +206,34 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+def gemm_persistent_tile(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m: int,
+                         residual: Optional[torch.Tensor] = None) -> int:
+    """The feature tile the persistent tensor-core product would use for these operands, 0 where it does not take them."""
+    if not tcgen05_accepts(a, w) or out.stride(1) != 1 or (residual is not None and residual.stride(1) != 1):
+        return 0
+    n, k = w.shape
+    return int(lib().lb_gemm_persistent_tile(
+        _code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
+        _opt(residual, "residual", torch.float32), residual.stride(0) if residual is not None else 0, _dev(out, "out"),
+        out.stride(0), m, n, k))
+
+
+def gemm_persistent(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
+                    activation: str = "none", residual: Optional[torch.Tensor] = None, feature_tile: int = 0) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual for more than 64 tokens: persistent tcgen05 kernel, every
+    operand, the residual and the result moved by TMA."""
+    n, k = w.shape
+    if a.shape[1] != k or out.stride(1) != 1 or out.shape[1] != n:
+        raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if residual is not None and (residual.shape[1] != n or residual.stride(1) != 1):
+        raise invalid_argument("gemm: residual has the wrong shape")
+    check(lib().lb_gemm_persistent(_code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
+                                   _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
+                                   residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n,
+                                   k, ACTIVATIONS[activation], feature_tile, stream_ptr()), "gemm_persistent")
+    return out
+
+
 def device_status() -> int:
     """0 unless a bounded wait inside a kernel ran out since the last call (then where it gave up).
     Synchronises the device."""
@@ -216,6 +247,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     """out[:m] = act(a[:m] @ w.T + bias) + residual: the kernel is chosen by type and size.  With a workspace
     (scratch buffers) a product of few tokens splits K over blocks."""
     if tcgen05_accepts(a, w):
+        if m > 64 and gemm_persistent_tile(a, w, out, m, residual) > 0:
+            return gemm_persistent(a, w, bias, out, m, activation, residual)
         splits = gemm_splits(m, w.shape[0], w.shape[1]) if workspace is not None else 1
         if splits > 1:
             partial = workspace.flat("gemm.partial", splits * m * w.shape[0], torch.float32)

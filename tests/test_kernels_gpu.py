@@ -270,6 +270,59 @@ def test_gemm_tcgen05(dev, out_dtype, M, N, K, tile):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("out_dtype,M,N,K,tile", [
+    (torch.float32, 65, 96, 64, 0), (torch.float32, 130, 200, 136, 0), (torch.float32, 300, 768, 3072, 0),
+    (torch.float32, 2048, 768, 768, 96), (torch.float32, 5000, 1000, 72, 128), (torch.float32, 257, 36, 520, 32),
+    (torch.float32, 1024, 352, 264, 160), (torch.bfloat16, 100, 72, 64, 0), (torch.bfloat16, 2048, 2304, 768, 0),
+    (torch.bfloat16, 777, 3072, 768, 192), (torch.bfloat16, 6000, 520, 200, 64), (torch.bfloat16, 4100, 1280, 328, 256)])
+def test_gemm_persistent(dev, out_dtype, M, N, K, tile):
+    """The persistent tensor-core product against float64: ragged edges in M, N and K, feature tiles of every
+    kind, several tiles per block (both accumulators, the staging buffer used again), all epilogues, the
+    residual in place, and a strided input."""
+    from liyab_b200 import ops
+    a, w = _rand((M, K), 36, dev, torch.bfloat16), _rand((N, K), 37, dev, torch.bfloat16, 0.2)
+    bias, res = _rand((N,), 38, dev), _rand((M, N), 39, dev)
+    assert ops.gemm_persistent_tile(a, w, torch.empty((M, N), dtype=out_dtype, device=dev), M) > 0
+    base = a.double() @ w.double().t()
+    scale = max(1.0, base.abs().max().item())
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
+    ops.gemm_persistent(a, w, None, out, M, feature_tile=tile)
+    assert ops.device_status() == 0
+    assert (out.double() - base).abs().max().item() <= tol * scale
+    for act, fn in (("gelu_tanh", plain.gelu_tanh), ("gelu_erf", plain.gelu_erf)):
+        ops.gemm_persistent(a, w, bias, out, M, act, feature_tile=tile)
+        ref = torch.from_numpy(fn((base + bias.double()).cpu().numpy())).to(dev)
+        assert (out.double() - ref).abs().max().item() <= tol * scale, act
+    if out_dtype == torch.float32:
+        out2 = res.clone()
+        ops.gemm_persistent(a, w, bias, out2, M, "none", residual=out2, feature_tile=tile)
+        assert (out2.double() - (base + bias.double() + res.double())).abs().max().item() <= tol * scale
+        same = torch.empty_like(out2)
+        ops.gemm_tcgen05(a, w, bias, same, M, "none", residual=res)
+        assert (out2 - same).abs().max().item() <= 1e-5 * scale          # the one-tile kernel agrees
+    # a view with a row stride and fewer rows than the buffer holds: rows past M stay as they were
+    wide = torch.zeros((M + 3, K + 8), dtype=torch.bfloat16, device=dev)
+    wide[:M, :K] = a
+    out3 = torch.full((M + 3, N), 7.0, dtype=out_dtype, device=dev)
+    ops.gemm_persistent(wide[:, :K], w, None, out3, M, feature_tile=tile)
+    assert (out3[:M].double() - base).abs().max().item() <= tol * scale and (out3[M:] == 7.0).all()
+    assert ops.device_status() == 0
+
+
+def test_gemm_persistent_refuses_what_it_cannot_take(dev):
+    from liyab_b200 import ops, LiyabError
+    a, w = _rand((100, 64), 1, dev, torch.bfloat16), _rand((50, 64), 2, dev, torch.bfloat16)
+    odd = torch.empty((100, 50), dtype=torch.bfloat16, device=dev)           # rows of 100 bytes: off TMA's 16-byte rule
+    assert ops.gemm_persistent_tile(a, w, odd, 100) == 0
+    with pytest.raises(LiyabError):
+        ops.gemm_persistent(a, w, None, odd, 100)
+    ops.linear(a, w, None, odd, 100)                                         # the dispatcher takes the one-tile kernel
+    assert (odd.double() - a.double() @ w.double().t()).abs().max().item() < 0.1
+    few = torch.empty((64, 50), dtype=torch.float32, device=dev)
+    assert ops.gemm_persistent_tile(a[:64], w, few, 64) == 0                  # 64 tokens or fewer: weights on the lanes
+
+
 def test_gemm_tcgen05_refuses_what_tma_cannot_fetch(dev):
     from liyab_b200 import ops, LiyabError
     a, w = _rand((4, 100), 1, dev, torch.bfloat16), _rand((8, 100), 2, dev, torch.bfloat16)
