@@ -5,12 +5,17 @@
 // One thread block serves 64 consecutive query tokens of one request and one
 // head.  It walks the keys the tile can see in tiles of 64 (four pages of 16, or
 // fewer larger pages), fetched with cp.async through the block table into shared
-// memory, two tiles in flight.  Scores S = Q K^T and the update O += P V are
+// memory through a ring of three tile buffers.  The longest query tiles are
+// handed out first.  Scores S = Q K^T and the update O += P V are
 // mma.sync m16n8k16 products with 32-bit accumulators; the running maximum, the
 // exponentials (exp2 of scores pre-scaled by log2 e) and the sums are 32-bit
 // registers, two query rows per thread.  Keys of earlier portions and of this
 // portion alike come from the cache, which the step has already written, so a
 // token's result does not depend on how its prompt was cut.
+//
+// The products are mma.sync, which a B200 runs at about 1/16 of its tcgen05 rate
+// (measured: this kernel saturates near 150 TFLOP/s with the tensor pipe busy);
+// the kernel is bound by that, not by memory or latency.
 //
 // Reference formulas: scores, causal range, softmax and weighted values
 // (src/core/transformer.cpp:2303-2313, 497-510, 2327-2341, 2344-2358).
@@ -27,6 +32,7 @@ namespace {
 constexpr int kBM = 64;           // query rows per block (16 per warp)
 constexpr int kBN = 64;           // keys per tile
 constexpr int kThreads = 128;
+constexpr int kStages = 3;        // key/value tiles in flight or in use
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -74,10 +80,12 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     constexpr int OT = HD / 8;                  // output n-tiles
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);            // [kBM][LD]
-    __nv_bfloat16* k_s = q_s + kBM * LD;                                           // [2][kBN][LD]
-    __nv_bfloat16* v_s = k_s + 2 * kBN * LD;                                       // [2][kBN][LD]
+    __nv_bfloat16* k_s = q_s + kBM * LD;                                           // [kStages][kBN][LD]
+    __nv_bfloat16* v_s = k_s + kStages * kBN * LD;                                 // [kStages][kBN][LD]
 
-    const int seq = blockIdx.z, head = blockIdx.y, tile_q = blockIdx.x;
+    // The last query tiles of a request see the most keys: they are handed out first, so that the short
+    // ones fill the gaps at the end.
+    const int seq = blockIdx.z, head = blockIdx.y, tile_q = (int)gridDim.x - 1 - (int)blockIdx.x;
     const int row0 = q_start[seq], q_len = q_start[seq + 1] - row0;
     if (tile_q * kBM >= q_len) return;
     const int past = n_past[seq];
@@ -113,8 +121,12 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
             cp_async16(v_s + (stage * kBN + r) * LD + ch * 8, src + plane, ok);
         }
     };
-    load_kv(0, 0);
-    cp_async_commit();
+    // kStages - 1 tiles ahead; one group per tile, empty past the last.
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+        if (i < n_tiles) load_kv(i, i);
+        cp_async_commit();
+    }
 
     // Positions of this thread's two rows (rows past the end copy the last valid one; they are not stored).
     const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
@@ -130,15 +142,11 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     const float sc = scale * kLog2e;
 
     for (int tile = 0; tile < n_tiles; ++tile) {
-        const int stage = tile & 1;
-        if (tile + 1 < n_tiles) {
-            load_kv(tile + 1, stage ^ 1);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
-        __syncthreads();
+        const int stage = tile % kStages;
+        cp_async_wait<kStages - 2>();           // this tile's group (and Q's, which went out with the first)
+        __syncthreads();                        // ... from every thread; and everyone is done with the tile before
+        if (tile + kStages - 1 < n_tiles) load_kv(tile + kStages - 1, (tile + kStages - 1) % kStages);
+        cp_async_commit();
         if (tile == 0) {
 #pragma unroll
             for (int kk = 0; kk < KS; ++kk) {
@@ -223,7 +231,6 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
                 mma_bf16(o[ot + 1], pf[kk], b[2], b[3]);
             }
         }
-        __syncthreads();        // the stage may be overwritten by the load issued in the next iteration
     }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
@@ -247,7 +254,7 @@ template <int HD>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_start, const int32_t* n_past,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_seq, int max_q_len,
            int n_head, int n_kv_head, int page_shift, float scale, int window, cudaStream_t s) {
-    constexpr size_t smem = (size_t)(kBM + 4 * kBN) * (HD + 8) * sizeof(__nv_bfloat16);
+    constexpr size_t smem = (size_t)(kBM + 2 * kStages * kBN) * (HD + 8) * sizeof(__nv_bfloat16);
     static bool configured = false;
     if (!configured) {
         LB_CHECK_CUDA(cudaFuncSetAttribute(prefill_attention_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));

@@ -94,13 +94,88 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int32_t* __r
     }
 }
 
+// The same for rows of up to 4 * 32 * NV values whose width is a multiple of 4: one warp per row, the row held
+// in registers (each lane float4s lane, lane + 32, ...), the two sums by warp shuffles; the row is read once
+// and no barrier is needed.  The order of additions depends on the width alone.
+template <typename T, int NV>
+__global__ void __launch_bounds__(128)
+layernorm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w,
+                      const float* __restrict__ b, T* __restrict__ y, int n_rows, int width, float eps) {
+    const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (r >= n_rows) return;
+    const int n4 = width >> 2;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows != nullptr ? rows[r] : r) * width);
+    float4 v[NV];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        v[i] = c < n4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    }
+    const float mean = lb_warp_sum(sum) / (float)width;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < n4) {
+            const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+            ss += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)width + eps);
+    T* out = y + (size_t)r * width;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + 32 * i;
+        if (c < n4) {
+            float4 o = make_float4((v[i].x - mean) * inv, (v[i].y - mean) * inv, (v[i].z - mean) * inv, (v[i].w - mean) * inv);
+            if (w != nullptr) {
+                const float4 ww = reinterpret_cast<const float4*>(w)[c];
+                o.x *= ww.x; o.y *= ww.y; o.z *= ww.z; o.w *= ww.w;
+            }
+            if (b != nullptr) {
+                const float4 bb = reinterpret_cast<const float4*>(b)[c];
+                o.x += bb.x; o.y += bb.y; o.z += bb.z; o.w += bb.w;
+            }
+            if constexpr (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(out)[c] = o;
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out)[c] = pk;
+            }
+        }
+    }
+}
+
+template <typename T>
+static void launch_layernorm_warp(const float* x, const int32_t* rows, const float* w, const float* b, T* y, int n_rows,
+                                  int width, float eps, cudaStream_t s) {
+    const int blocks = (n_rows + 3) / 4, n4 = width / 4;
+    if (n4 <= 32 * 2) layernorm_warp_kernel<T, 2><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 4) layernorm_warp_kernel<T, 4><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 6) layernorm_warp_kernel<T, 6><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 8) layernorm_warp_kernel<T, 8><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 13) layernorm_warp_kernel<T, 13><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    else layernorm_warp_kernel<T, 16><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+}
+
 extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight,
                             const float* bias, void* y, int n_rows, int width, float eps, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && width > 0, "layernorm: bad sizes n_rows=%d width=%d", n_rows, width);
     if (n_rows == 0) return LB_OK;
     const int threads = width >= 2048 ? 256 : 128;   // fixed by the width alone: a row's sums never depend on the batch
     auto s = static_cast<cudaStream_t>(stream);
-    if (out_dtype == LB_F32) {
+    // Rows of float4s that fit a warp's registers take the warp-per-row kernel (everything 16-byte aligned).
+    const bool warp_rows = width % 4 == 0 && width <= 2048 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+                           (weight == nullptr || ((uintptr_t)weight & 15) == 0) && (bias == nullptr || ((uintptr_t)bias & 15) == 0);
+    if (warp_rows && out_dtype == LB_F32) {
+        launch_layernorm_warp<float>(x, rows, weight, bias, (float*)y, n_rows, width, eps, s);
+    } else if (warp_rows && out_dtype == LB_BF16) {
+        launch_layernorm_warp<__nv_bfloat16>(x, rows, weight, bias, (__nv_bfloat16*)y, n_rows, width, eps, s);
+    } else if (out_dtype == LB_F32) {
         layernorm_kernel<float><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (float*)y, width, eps);
     } else if (out_dtype == LB_BF16) {
         layernorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (__nv_bfloat16*)y, width, eps);
@@ -139,13 +214,52 @@ __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ 
     }
 }
 
+// The same in 16-byte pieces (head_dim * sizeof(T) a multiple of 16, everything 16-byte aligned): thread c of a
+// token's block moves piece c of the key row or of the value row; four tokens per block.
+template <typename T>
+__global__ void __launch_bounds__(256)
+kv_append_vec_kernel(const T* __restrict__ k, const T* __restrict__ v, int64_t row_stride,
+                     const int32_t* __restrict__ slot_mapping, T* __restrict__ cache, int n_tokens, int n_kv_head,
+                     int head_dim, int page_size) {
+    constexpr int kPer = 16 / (int)sizeof(T);                    // elements per piece
+    const int pieces_head = head_dim / kPer, pieces_row = n_kv_head * pieces_head;
+    const int per_token = 2 * pieces_row;
+    const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int t = (int)(idx / per_token);
+    if (t >= n_tokens) return;
+    int c = (int)(idx - (long)t * per_token);
+    const int slot = slot_mapping[t];
+    if (slot < 0) return;
+    const bool is_v = c >= pieces_row;
+    if (is_v) c -= pieces_row;
+    const int h = c / pieces_head, d = (c - h * pieces_head) * kPer;
+    const int page = slot / page_size, off = slot - page * page_size;
+    const size_t plane = (size_t)n_kv_head * page_size * head_dim;
+    const T* src = (is_v ? v : k) + (size_t)t * row_stride + (size_t)h * head_dim + d;
+    T* dst = cache + (size_t)page * 2 * plane + (is_v ? plane : 0) + ((size_t)h * page_size + off) * head_dim + d;
+    *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+}
+
 extern "C" int lb_kv_append(int dtype, const void* k, const void* v, int64_t row_stride, const int32_t* slot_mapping,
                             void* cache, int n_tokens, int n_kv_head, int head_dim, int page_size, void* stream) {
     LB_CHECK_ARG(n_tokens >= 0 && n_kv_head > 0 && head_dim > 0 && page_size > 0, "kv_append: bad sizes");
     if (n_tokens == 0) return LB_OK;
     auto s = static_cast<cudaStream_t>(stream);
     const int threads = 128;
-    if (dtype == LB_F32) {
+    const int elem = dtype == LB_F32 ? 4 : 2;
+    const bool vec = (dtype == LB_F32 || dtype == LB_BF16) && (head_dim * elem) % 16 == 0 && (row_stride * elem) % 16 == 0 &&
+                     ((uintptr_t)k & 15) == 0 && ((uintptr_t)v & 15) == 0 && ((uintptr_t)cache & 15) == 0;
+    if (vec) {
+        const long pieces = (long)n_tokens * 2 * n_kv_head * (head_dim * elem / 16);
+        const int blocks = (int)((pieces + 255) / 256);
+        if (dtype == LB_F32)
+            kv_append_vec_kernel<float><<<blocks, 256, 0, s>>>((const float*)k, (const float*)v, row_stride, slot_mapping,
+                                                              (float*)cache, n_tokens, n_kv_head, head_dim, page_size);
+        else
+            kv_append_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride,
+                                                                      slot_mapping, (__nv_bfloat16*)cache, n_tokens, n_kv_head,
+                                                                      head_dim, page_size);
+    } else if (dtype == LB_F32) {
         kv_append_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)k, (const float*)v, row_stride, slot_mapping,
                                                             (float*)cache, n_kv_head, head_dim, page_size);
     } else if (dtype == LB_BF16) {

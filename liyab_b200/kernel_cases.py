@@ -2,6 +2,7 @@
 
     python -m liyab_b200.kernel_cases gemm --m 2048 --n 768 --k 3072 --out float32 --reps 20
     python -m liyab_b200.kernel_cases decode-attention --batch 64 --context 768 --reps 20
+    python -m liyab_b200.kernel_cases prefill-attention --seqs 2 --length 1024 --reps 20
     python -m liyab_b200.kernel_cases decode-step --batch 8 --layers 12 --reps 20 [--eager]
     python -m liyab_b200.kernel_cases prefill-step --tokens 2048 --layers 12 --reps 3
 
@@ -93,6 +94,27 @@ def case_decode_attention(args) -> None:
           f"{nbytes / ms / 1e6:.1f} GB/s of cache ({nbytes / 1e6:.1f} MB)")
 
 
+def case_prefill_attention(args) -> None:
+    from . import ops
+    dev = torch.device("cuda:0")
+    S, L, H, hd, ps = args.seqs, args.length, args.heads, args.head_dim, 16
+    pages_per = -(-L // ps)
+    cache = torch.randn(S * pages_per, 2, H, ps, hd, device=dev).to(torch.bfloat16)
+    table = torch.arange(S * pages_per, dtype=torch.int32, device=dev).view(S, pages_per)
+    q = torch.randn(S * L, H * hd, device=dev).to(torch.bfloat16)
+    out = torch.empty_like(q)
+    q_start = torch.arange(0, (S + 1) * L, L, dtype=torch.int32, device=dev)
+    n_past = torch.zeros(S, dtype=torch.int32, device=dev)
+
+    def launch():
+        ops.prefill_attention(q, cache, q_start, n_past, table, out, S, L, H, H, hd, ps, hd ** -0.5, 0)
+
+    ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
+    flop = S * H * (L * L / 2) * hd * 4
+    print(f"prefill-attention seqs={S} length={L} heads={H} head_dim={hd}: {ms * 1e3:.1f} us, {flop / ms / 1e9:.1f} TFLOP/s "
+          f"(causal half of the square)")
+
+
 def _model_folder(layers: int, dtype: str) -> str:
     from .config import parse_config
     from .weights import write_random_model
@@ -169,6 +191,13 @@ def main(argv=None) -> int:
     d.add_argument("--splits", type=int, default=0, help="key ranges per request and head (0: the engine's choice)")
     d.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     d.add_argument("--scalar", action="store_true", help="the scalar kernel even where the tensor-core one takes the shape")
+    a = sub.add_parser("prefill-attention")
+    a.add_argument("--seqs", type=int, default=2)
+    a.add_argument("--length", type=int, default=1024)
+    a.add_argument("--heads", type=int, default=12)
+    a.add_argument("--head-dim", type=int, default=64)
+    a.add_argument("--reps", type=int, default=20)
+    a.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
@@ -179,7 +208,7 @@ def main(argv=None) -> int:
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true")
     args = ap.parse_args(argv)
-    {"gemm": case_gemm, "decode-attention": case_decode_attention, "decode-step": case_decode_step,
+    {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "decode-step": case_decode_step,
      "prefill-step": case_prefill_step}[args.case](args)
     return 0
 
