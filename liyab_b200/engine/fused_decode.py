@@ -34,7 +34,7 @@ _c = ctypes
 _p, _i, _f = _c.c_void_p, _c.c_int, _c.c_float
 
 ops.declare("lb_decode_stack", [_p, _i, _i, _i, _i, _p, _p, _f, _p, _p, _f, _p, _p, _p, _p, _p, _i, _p, _i, _p, _p, _p, _p,
-                                _p, _p, _p, _p, _i, _i, _i, _p, _p])
+                                _p, _p, _p, _p, _i, _i, _i, _i, _p, _p])
 ops.declare("lb_decode_stack_status", [_p])
 ops.declare("lb_decode_stack_layer_bytes", [])
 
@@ -54,7 +54,7 @@ class FusedDecodeStack:
         if type(model.position) not in (LearnedAbsolutePosition, NoPosition) or type(model.final_norm) is not LayerNorm:
             return None
         ps = cache.page_size
-        if ps & (ps - 1) or spec.hidden % 8:
+        if ps & (ps - 1) or ps < 16 or spec.hidden % 8:        # the attention phase takes its 16-key tiles from one page
             return None
         head_dim = None
         for i, entry in enumerate(spec.run_order):
@@ -68,6 +68,8 @@ class FusedDecodeStack:
             a, f = parts.mixer.spec, parts.feed_forward.spec
             if a.head_dim not in (64, 128) or (head_dim or a.head_dim) != a.head_dim or f.inner % 8:
                 return None
+            if a.n_head // a.n_kv_head > 16:       # the query heads of a key/value head are the 16 rows of a tile
+                return None
             if f.activation not in ops.ACTIVATIONS:
                 return None
             head_dim = a.head_dim
@@ -77,14 +79,15 @@ class FusedDecodeStack:
             return None
         stack = FusedDecodeStack(model, cache, head_dim)
         max_k = stack.max_k
-        smem = MAX_TOKENS * ((max_k + 63) // 64 * 64 + 32) * 2 + 8 * 8 * 128 * 4 + 8 * 130 * 4
+        smem = (max(MAX_TOKENS * ((max_k + 63) // 64 * 64 + 32) * 2 + 8 * 8 * 128 * 4, 128 * 1024) + 64 + 16
+                + stack.n_layers * struct.calcsize(_LAYER_FORMAT))
         return stack if smem <= 227 * 1024 else None
 
     def __init__(self, model, cache, head_dim: int):
         self.model, self.cache, self.head_dim = model, cache, head_dim
         spec, dev = model.spec, model.runtime.device
         records = []
-        self.max_k, self.max_qd, self.max_inner, self.max_heads = spec.hidden, 0, 0, 0
+        self.max_k, self.max_qd, self.max_inner, self.max_heads, self.max_kv_heads = spec.hidden, 0, 0, 0, 0
         for i, entry in enumerate(spec.run_order):
             parts = model.layers[entry.layer].parts
             a, f = parts.mixer.spec, parts.feed_forward.spec
@@ -92,6 +95,7 @@ class FusedDecodeStack:
             qd = a.n_head * a.head_dim
             self.max_qd, self.max_inner = max(self.max_qd, qd), max(self.max_inner, f.inner)
             self.max_heads = max(self.max_heads, a.n_head)
+            self.max_kv_heads = max(self.max_kv_heads, a.n_kv_head)
             self.max_k = max(self.max_k, qd, f.inner)
             unit = cache.groups[0].unit_storage(i)
             records.append(struct.pack(
@@ -121,9 +125,14 @@ class FusedDecodeStack:
         return 1 <= n_tokens <= MAX_TOKENS
 
     def splits(self, n_tokens: int) -> int:
-        """Key ranges per (token, head): as many as give every SM at most one work item, a function of the
-        batch's shape only."""
-        return max(1, min(32, self.n_sm // (n_tokens * self.max_heads)))
+        """(key ranges per (token, key/value head), warps per work item): a function of the batch's shape only.
+        A range merged across blocks costs a round of atomics and reloads, so from 64 pairs on a pair is one item,
+        served by a whole block (eight warps) while there are blocks enough for that, else by half a block; fewer
+        pairs are split until every half block has an item."""
+        pairs = n_tokens * self.max_kv_heads
+        if pairs >= 64:
+            return 1, (8 if pairs <= self.n_sm else 4)
+        return max(1, min(32, (2 * self.n_sm) // pairs)), 4
 
     def run(self, ctx: StepContext) -> torch.Tensor:
         m, spec = self.model, self.model.spec
@@ -136,7 +145,7 @@ class FusedDecodeStack:
             ctx.positions.data_ptr(), view.block_table.data_ptr(), view.block_table.stride(0), view.slot_mapping.data_ptr(),
             self.cache.page_size, self.x.data_ptr(), self.q.data_ptr(), self.att.data_ptr(), self.inner.data_ptr(),
             self.partial.data_ptr(), self.counters.data_ptr(), self.logits.data_ptr(), self.barrier.data_ptr(), self.max_k,
-            self.head_dim, self.splits(B), _ptr(self.timing), ops.stream_ptr()), "decode_stack")
+            self.head_dim, *self.splits(B), _ptr(self.timing), ops.stream_ptr()), "decode_stack")
         self.launches += 1
         return self.logits[:B]
 
