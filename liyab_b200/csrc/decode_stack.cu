@@ -55,7 +55,6 @@ constexpr int kWarps = 8;
 constexpr int kMaxTokens = 16;
 constexpr int kGC = 8;                           // feature groups (of 8 features) a block handles per pass
 constexpr int kWRegs = 16;                       // 16-byte weight pieces a thread holds for the next matrix phase
-constexpr int kHeadChunk = 12;                   // k-blocks (of 32) per chunk of the head's stream
 constexpr long long kSpinLimit = 4000000000ll;   // cycles
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -108,6 +107,8 @@ struct StackParams {
     int* status;
     int n_splits, act_ld;
     int unit_warps;                  // warps that share an attention work item: 4 (two items per block at a time) or 8
+    int bars_offset;                         // 8 x 4 mbarriers of the head's rings
+    int head_ring_offset, head_ring_bytes;   // the head's cp.async ring: shared memory after the activations
     int pos_offset;                  // byte offset of the positions in shared memory (after what the phases share)
     unsigned long long* timing;      // optional: block 0 stamps the global timer after every barrier
 };
@@ -573,55 +574,155 @@ __device__ __forceinline__ void gemm_run(int shape, const uint4 (&w)[kWRegs], co
     else if (shape == 3) gemm_preloaded<4, 4>(w, N, K, act_s, ld, red_s, n_tokens, early, post);
 }
 
+// ---- bulk copies (TMA, untiled) with an mbarrier, for the head's stream ----
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the barrier's phase; false when about two seconds passed without it.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+#pragma unroll 1
+    for (int i = 0; i < 1024; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (clock64() - t0 > kSpinLimit) return false;
+    }
+}
+// `bytes` (a multiple of 16) from global to shared memory, both 16-byte aligned; completion is counted on `bar`.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_addr(dst)), "l"(src), "r"(bytes), "r"(smem_addr(bar))
+                 : "memory");
+}
+
 // The head: every warp owns whole groups of eight vocabulary rows (no sum across warps, no block-wide barrier) and
-// walks K in chunks of kHeadChunk k-blocks, the next chunk's 16-byte pieces requested before the current one is
-// used.  logits[b, f] = sum_k act[b, k] W[f, k] + bias[f].
+// streams them through its own ring of buffers in shared memory with bulk copies (one per row of a step, issued
+// by the warp's first lane, completion counted on the stage's mbarrier).  A step is eight rows x `kc` columns and
+// up to four steps (some 20 KB) are in flight per warp: ordinary loads and cp.async keep only about 32 KB per SM
+// in flight (measured: 3 TB/s over the GPU, however many were issued), bulk copies are not bound by that.  Rows
+// lie 64 bytes (mod 128) apart in a buffer, so the 16-byte fragment reads of a quarter warp meet no bank twice.
+// logits[b, f] = sum_k act[b, k] W[f, k] + bias[f].  A wait that runs out records `code` in the status word and
+// ends the warp's stream (after waiting, as boundedly, for the copies it still has in flight).
 __device__ void head_phase(const __nv_bfloat16* __restrict__ W, const float* __restrict__ bias, int N, int K,
-                           const __nv_bfloat16* act_s, int ld, int n_tokens, float* logits) {
+                           const __nv_bfloat16* act_s, int ld, int n_tokens, float* logits, uint8_t* ring, int ring_bytes,
+                           uint64_t* bars, int* status, int code) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n_groups = (N + 7) / 8;
     const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
     const int g_begin = min(n_groups, (int)blockIdx.x * per_cta), g_end = min(n_groups, g_begin + per_cta);
-    const int n_kb = (K + 31) / 32, n_chunks = (n_kb + kHeadChunk - 1) / kHeadChunk;
+    const int k_pad = (K + 31) / 32 * 32;
+    // A step is eight rows x kc columns (row stride kc * 2 + 64 bytes).  K is cut into the fewest equal chunks of
+    // which at least two fit the warp's share of the ring; up to four steps are in flight.
+    const int share = ring_bytes / kWarps;
+    int n_chunks = 1, kc = k_pad;
+    while (2 * 8 * (kc * 2 + 64) > share && kc > 32) {
+        ++n_chunks;
+        kc = ((k_pad + n_chunks - 1) / n_chunks + 31) / 32 * 32;
+    }
+    const int stage_bytes = 8 * (kc * 2 + 64);
+    const int n_stages = min(4, max(2, share / stage_bytes));
+    const int stride = kc + 32;                                          // elements
     const int my_groups = g_end - g_begin > warp ? (g_end - g_begin - warp + kWarps - 1) / kWarps : 0;
     const int total = my_groups * n_chunks;
+    __nv_bfloat16* my_ring = reinterpret_cast<__nv_bfloat16*>(ring + (size_t)warp * share);
+    uint64_t* my_bars = bars + warp * 4;
+    // Columns past K in a buffer are multiplied by zero activations; what they hold must be finite, so where a
+    // step is not filled to its last column the ring starts as zeros (bulk copies never touch those columns).
+    if (n_chunks * kc != K) {
+        uint4* z = reinterpret_cast<uint4*>(my_ring);
+        for (int i = lane; i < n_stages * stage_bytes / 16; i += 32) z[i] = make_uint4(0, 0, 0, 0);
+    }
+    if (lane == 0) {
+        for (int i = 0; i < 4; ++i) mbar_init(&my_bars[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // the zeros above, before any bulk copy
+    }
+    __syncwarp();
     const __nv_bfloat16* a_lo = act_s + g * ld + t * 8;
     const __nv_bfloat16* a_hi = a_lo + 8 * ld;
-    auto fetch = [&](int step, uint4 (&buf)[kHeadChunk]) {
-        const int gp = g_begin + warp + kWarps * (step / n_chunks), kb0 = (step % n_chunks) * kHeadChunk;
-#pragma unroll
-        for (int u = 0; u < kHeadChunk; ++u)
-            buf[u] = kb0 + u < n_kb ? load_w(W, N, K, gp * 8 + g, (kb0 + u) * 32 + t * 8) : make_uint4(0, 0, 0, 0);
+    // Steps are counted as (group, chunk) and stage by running counters, with no division.
+    int f_group = 0, f_chunk = 0, f_stage = 0;                           // the next step to fetch (first lane only)
+    auto fetch = [&]() {
+        const int gp = g_begin + warp + kWarps * f_group, k0 = f_chunk * kc;
+        __nv_bfloat16* dst = my_ring + (size_t)f_stage * (stage_bytes / 2);
+        const int rows = min(8, N - gp * 8);
+        const uint32_t row_bytes = (uint32_t)(min(kc, K - k0) * 2);
+        mbar_expect_tx(&my_bars[f_stage], row_bytes * rows);
+        for (int r = 0; r < rows; ++r) bulk_load(dst + r * stride, W + (size_t)(gp * 8 + r) * K + k0, row_bytes, &my_bars[f_stage]);
+        if (++f_chunk == n_chunks) { f_chunk = 0; ++f_group; }
+        if (++f_stage == n_stages) f_stage = 0;
     };
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    auto consume = [&](int step, const uint4 (&buf)[kHeadChunk]) {
-        const int gp = g_begin + warp + kWarps * (step / n_chunks), chunk = step % n_chunks, kb0 = chunk * kHeadChunk;
-#pragma unroll
-        for (int u = 0; u < kHeadChunk; ++u) {
-            if (kb0 + u < n_kb) {
-                const uint4 lo = *reinterpret_cast<const uint4*>(a_lo + (kb0 + u) * 32);
-                const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + (kb0 + u) * 32);
-                mma_bf16(acc, lo.x, hi.x, lo.y, hi.y, buf[u].x, buf[u].y);
-                mma_bf16(acc, lo.z, hi.z, lo.w, hi.w, buf[u].z, buf[u].w);
+    float acc0[4] = {0.f, 0.f, 0.f, 0.f}, acc1[4] = {0.f, 0.f, 0.f, 0.f};
+    int fetched = 0;
+    if (lane == 0)
+        for (; fetched < n_stages && fetched < total; ++fetched) fetch();
+    int c_group = 0, c_chunk = 0, c_stage = 0;                           // the step being consumed
+    uint32_t parity = 0;                                                 // of the ring's current round
+    int step = 0;
+    for (; step < total; ++step) {
+        if (!__all_sync(0xffffffffu, mbar_wait(&my_bars[c_stage], parity))) {      // one answer for the warp
+            if (lane == 0) atomicCAS(status, 0, code);
+            break;
+        }
+        const int gp = g_begin + warp + kWarps * c_group, k0 = c_chunk * kc;
+        const __nv_bfloat16* src = my_ring + (size_t)c_stage * (stage_bytes / 2) + g * stride + t * 8;
+        const int n_kb = min(kc, k_pad - k0) / 32;
+#pragma unroll 4
+        for (int kb = 0; kb < n_kb; kb += 2) {
+            {
+                const uint4 w = *reinterpret_cast<const uint4*>(src + kb * 32);
+                const uint4 lo = *reinterpret_cast<const uint4*>(a_lo + k0 + kb * 32);
+                const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + k0 + kb * 32);
+                mma_bf16(acc0, lo.x, hi.x, lo.y, hi.y, w.x, w.y);
+                mma_bf16(acc0, lo.z, hi.z, lo.w, hi.w, w.z, w.w);
+            }
+            if (kb + 1 < n_kb) {
+                const uint4 w = *reinterpret_cast<const uint4*>(src + (kb + 1) * 32);
+                const uint4 lo = *reinterpret_cast<const uint4*>(a_lo + k0 + (kb + 1) * 32);
+                const uint4 hi = *reinterpret_cast<const uint4*>(a_hi + k0 + (kb + 1) * 32);
+                mma_bf16(acc1, lo.x, hi.x, lo.y, hi.y, w.x, w.y);
+                mma_bf16(acc1, lo.z, hi.z, lo.w, hi.w, w.z, w.w);
             }
         }
-        if (chunk == n_chunks - 1) {
+        __syncwarp();                       // every lane has read the buffer: the step n_stages further on goes into it
+        if (lane == 0 && fetched < total) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            fetch();
+            ++fetched;
+        }
+        if (c_chunk == n_chunks - 1) {
             const int f = gp * 8 + 2 * t;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int r = g + (e >> 1) * 8, ff = f + (e & 1);
-                if (r < n_tokens && ff < N) logits[(size_t)r * N + ff] = acc[e] + (bias != nullptr ? __ldg(bias + ff) : 0.0f);
-                acc[e] = 0.0f;
+                if (r < n_tokens && ff < N) logits[(size_t)r * N + ff] = acc0[e] + acc1[e] + (bias != nullptr ? __ldg(bias + ff) : 0.0f);
+                acc0[e] = acc1[e] = 0.0f;
             }
         }
-    };
-    uint4 buf_a[kHeadChunk], buf_b[kHeadChunk];
-    if (total > 0) fetch(0, buf_a);
-    for (int step = 0; step < total; step += 2) {
-        if (step + 1 < total) fetch(step + 1, buf_b);
-        consume(step, buf_a);
-        if (step + 2 < total) fetch(step + 2, buf_a);
-        if (step + 1 < total) consume(step + 1, buf_b);
+        if (++c_chunk == n_chunks) { c_chunk = 0; ++c_group; }
+        if (++c_stage == n_stages) { c_stage = 0; parity ^= 1; }
+    }
+    // After a wait that ran out: the copies still in flight land before the block may leave (bounded as well).
+    fetched = __shfl_sync(0xffffffffu, fetched, 0);
+    for (; step < fetched; ++step) {
+        mbar_wait(&my_bars[c_stage], parity);
+        if (++c_stage == n_stages) { c_stage = 0; parity ^= 1; }
     }
 }
 
@@ -1019,7 +1120,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
             if (pick_shape(next_n, d) == 0) prefetch_slice(Ln.w_qkv, next_n, d);
             if (pick_shape(d, next_qd) == 0) prefetch_slice(Ln.w_out, d, next_qd);
         } else {
-            prefetch_slice(p.head_w, p.vocab, d);
+            if (p.timing == nullptr || p.timing[2040] == 0) prefetch_slice(p.head_w, p.vocab, d);
         }
         if (!grid_wait(p, epoch, code | 3)) return;
 
@@ -1086,9 +1187,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
     }
 
     // ---- Final norm and the head.
-    layernorm_to_smem(p.x, p.lnf_w, p.lnf_b, p.lnf_eps, B, d, act_s, ld, (d + 63) / 64 * 64);
+    const int ld_head = (d + 63) / 64 * 64 + 32;          // the head's activations lie compactly: the rest is its ring
+    layernorm_to_smem(p.x, p.lnf_w, p.lnf_b, p.lnf_eps, B, d, act_s, ld_head, (d + 63) / 64 * 64);
     __syncthreads();
-    head_phase(p.head_w, p.head_b, p.vocab, d, act_s, ld, B, p.logits);
+    stamp(p, 126);
+    head_phase(p.head_w, p.head_b, p.vocab, d, act_s, ld_head, B, p.logits, smem_bytes + p.head_ring_offset, p.head_ring_bytes,
+               reinterpret_cast<uint64_t*>(smem_bytes + p.bars_offset), p.status, 0xF0);
     stamp(p, 127);
 }
 
@@ -1167,9 +1271,20 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
     // (8 warps x S stages x K and V tiles of 16 keys), whichever is larger; then the positions.
     const size_t gemm_bytes = (size_t)kMaxTokens * p.act_ld * sizeof(__nv_bfloat16) + (size_t)kWarps * kGC * 128 * sizeof(float);
     const size_t ring_bytes = (size_t)kWarps * (head_dim == 64 ? 2 : 1) * 4 * 16 * head_dim * sizeof(__nv_bfloat16);
-    const size_t shared_bytes = ((gemm_bytes > ring_bytes ? gemm_bytes : ring_bytes) + 15) / 16 * 16;
+    // The head's ring follows the head's (compactly laid out) activations and takes what is left of 200 KB.
+    const size_t head_act = ((size_t)kMaxTokens * ((width + 63) / 64 * 64 + 32) * sizeof(__nv_bfloat16) + 127) / 128 * 128;
+    size_t head_ring = 200 * 1024 - head_act;
+    head_ring = head_ring / (kWarps * 16) * (kWarps * 16);
+    const size_t act_bytes = head_act;
+    p.head_ring_offset = (int)head_act;
+    p.head_ring_bytes = (int)head_ring;
+    size_t most = gemm_bytes > ring_bytes ? gemm_bytes : ring_bytes;
+    if (act_bytes + head_ring > most) most = act_bytes + head_ring;
+    const size_t shared_bytes = (most + 15) / 16 * 16;
     p.pos_offset = (int)shared_bytes;
-    const size_t smem = shared_bytes + (size_t)kMaxTokens * sizeof(int32_t) + (size_t)n_layers * sizeof(StackLayer);
+    const size_t after_layers = shared_bytes + (size_t)kMaxTokens * sizeof(int32_t) + (size_t)n_layers * sizeof(StackLayer);
+    p.bars_offset = (int)((after_layers + 15) / 16 * 16);
+    const size_t smem = (size_t)p.bars_offset + kWarps * 4 * sizeof(uint64_t);
     LB_CHECK_ARG(smem <= 227 * 1024, "decode stack: a reduction length of %d needs %zu bytes of shared memory, the SM has 232448",
                  max_k, smem);
     static size_t configured = 0;

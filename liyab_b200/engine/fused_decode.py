@@ -79,7 +79,7 @@ class FusedDecodeStack:
             return None
         stack = FusedDecodeStack(model, cache, head_dim)
         max_k = stack.max_k
-        smem = (max(MAX_TOKENS * ((max_k + 63) // 64 * 64 + 32) * 2 + 8 * 8 * 128 * 4, 128 * 1024) + 64 + 16
+        smem = (max(MAX_TOKENS * ((max_k + 63) // 64 * 64 + 32) * 2 + 8 * 8 * 128 * 4, 200 * 1024) + 64 + 16 + 16 + 256
                 + stack.n_layers * struct.calcsize(_LAYER_FORMAT))
         return stack if smem <= 227 * 1024 else None
 
