@@ -118,6 +118,14 @@ int lb_prefill_attention(const void* q, int64_t q_stride, const void* cache, con
                          int64_t out_stride, int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim,
                          int page_size, float scale, int window, void* stream);
 int lb_prefill_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
+/* The same on the tcgen05 tensor cores (head size 64, pages of 16 positions or more): TMA-fed, scores and output
+ * accumulated in tensor memory.  n_tokens is the number of rows of q (and out), n_pages the number of pages of the
+ * layer's cache (both bound the tensor maps). */
+int lb_prefill_attention_tc(const void* q, int64_t q_stride, int n_tokens, const void* cache, int n_pages,
+                            const int32_t* q_start, const int32_t* n_past, const int32_t* block_table, int table_stride,
+                            void* out, int64_t out_stride, int n_seq, int max_q_len, int n_head, int n_kv_head, int head_dim,
+                            int page_size, float scale, int window, void* stream);
+int lb_prefill_attention_tc_supports(int n_head, int n_kv_head, int head_dim, int page_size);
 
 /* One token id per row of logits.  temperature[r] <= 0: the first maximum.
  * Otherwise top_k[r] (<= 0 or >= vocab: off), top_p[r] (>= 1: off) and the draw

@@ -107,7 +107,8 @@ def case_prefill_attention(args) -> None:
     n_past = torch.zeros(S, dtype=torch.int32, device=dev)
 
     def launch():
-        ops.prefill_attention(q, cache, q_start, n_past, table, out, S, L, H, H, hd, ps, hd ** -0.5, 0)
+        ops.prefill_attention(q, cache, q_start, n_past, table, out, S, L, H, H, hd, ps, hd ** -0.5, 0,
+                              tcgen05=False if args.mma_sync else None)
 
     ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
     flop = S * H * (L * L / 2) * hd * 4
@@ -198,6 +199,7 @@ def main(argv=None) -> int:
     a.add_argument("--head-dim", type=int, default=64)
     a.add_argument("--reps", type=int, default=20)
     a.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
+    a.add_argument("--mma-sync", action="store_true", help="the mma.sync kernel even where the tcgen05 one takes the shape")
     for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)

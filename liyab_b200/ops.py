@@ -41,6 +41,8 @@ _SIGNATURES = {
     "lb_decode_attention_mma_supports": [_i, _i, _i, _i],
     "lb_prefill_attention": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_prefill_attention_supports": [_i, _i, _i, _i],
+    "lb_prefill_attention_tc": [_p, _l, _i, _p, _i, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
+    "lb_prefill_attention_tc_supports": [_i, _i, _i, _i],
     "lb_sample": [_p, _l, _i, _i, _p, _p, _p, _p, _p, _p, _p],
 }
 
@@ -329,14 +331,45 @@ def prefill_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_
     return bool(lib().lb_prefill_attention_supports(n_head, n_kv_head, head_dim, page_size))
 
 
+_SM_COUNT = {}
+
+
+def _sm_count(device) -> int:
+    key = torch.device(device).index or 0
+    if key not in _SM_COUNT:
+        _SM_COUNT[key] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _SM_COUNT[key]
+
+
+def prefill_attention_tc_supports(n_head: int, n_kv_head: int, head_dim: int, page_size: int) -> bool:
+    return bool(lib().lb_prefill_attention_tc_supports(n_head, n_kv_head, head_dim, page_size))
+
+
 def prefill_attention(q: torch.Tensor, cache: torch.Tensor, q_start: torch.Tensor, n_past: torch.Tensor,
                       block_table: torch.Tensor, out: torch.Tensor, n_seq: int, max_q_len: int, n_head: int,
-                      n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int = 0) -> torch.Tensor:
-    """Attention of the step's prompt portions over their pages (bfloat16, tensor cores)."""
+                      n_kv_head: int, head_dim: int, page_size: int, scale: float, window: int = 0,
+                      tcgen05: Optional[bool] = None) -> torch.Tensor:
+    """Attention of the step's prompt portions over their pages (bfloat16, tensor cores).  `tcgen05`: None picks
+    the tcgen05 kernel where it takes the shape and the rows are 16-byte aligned, else the mma.sync one."""
     if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise invalid_argument("prefill attention takes bfloat16 only")
     if q.stride(1) != 1 or out.stride(1) != 1:
         raise invalid_argument("prefill attention: q and out must be dense within a row")
+    if tcgen05 is None:
+        # Measured on B200: the tcgen05 kernel walks a long tile's keys about 1.4x faster, but runs one block per SM,
+        # so it wins while the launch is bound by its longest blocks (up to four blocks per SM) and loses to the
+        # mma.sync kernel's several blocks per SM beyond that.
+        blocks = n_seq * n_head * -(-max_q_len // 128)
+        tcgen05 = (prefill_attention_tc_supports(n_head, n_kv_head, head_dim, page_size) and q.stride(0) % 8 == 0
+                   and out.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+                   and blocks <= 4 * _sm_count(q.device))
+    if tcgen05:
+        check(lib().lb_prefill_attention_tc(
+            _dev(q, "q"), q.stride(0), q.shape[0], _dev(cache, "cache"), cache.shape[0],
+            _dev(q_start, "q_start", torch.int32), _dev(n_past, "n_past", torch.int32),
+            _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0), n_seq,
+            max_q_len, n_head, n_kv_head, head_dim, page_size, float(scale), int(window), stream_ptr()), "prefill_attention_tc")
+        return out
     check(lib().lb_prefill_attention(
         _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(q_start, "q_start", torch.int32),
         _dev(n_past, "n_past", torch.int32), _dev(block_table, "block_table", torch.int32), block_table.stride(0),

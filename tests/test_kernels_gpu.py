@@ -396,12 +396,15 @@ def test_prefill_attention(dev, n_head, n_kv_head, head_dim, page_size, window):
                                                             lens, q_lens, seed=head_dim + n_head + window)
     q_start = torch.tensor(np.concatenate([[0], np.cumsum(q_lens)]), dtype=torch.int32, device=dev)
     n_past = torch.tensor([l - ql for l, ql in zip(lens, q_lens)], dtype=torch.int32, device=dev)
-    out = torch.full_like(q, float("nan"))
-    ops.prefill_attention(q, cache, q_start, n_past, table, out, len(lens), max(q_lens), n_head, n_kv_head, head_dim,
-                          page_size, scale, window)
     ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
-    err = (out.double().cpu() - ref).abs().max().item()
-    assert err < 1.5e-2, err
+    kinds = [False] + ([True] if ops.prefill_attention_tc_supports(n_head, n_kv_head, head_dim, page_size) else [])
+    for tcgen05 in kinds:
+        out = torch.full_like(q, float("nan"))
+        ops.prefill_attention(q, cache, q_start, n_past, table, out, len(lens), max(q_lens), n_head, n_kv_head, head_dim,
+                              page_size, scale, window, tcgen05=tcgen05)
+        assert ops.device_status() == 0
+        err = (out.double().cpu() - ref).abs().max().item()
+        assert err < 1.5e-2, (tcgen05, err)
 
 
 def test_prefill_attention_finds_a_far_key_and_the_diagonal(dev):
@@ -414,11 +417,12 @@ def test_prefill_attention_finds_a_far_key_and_the_diagonal(dev):
                                                   seed=key_pos, boost=(key_pos, 4.0))
         q_start = torch.tensor([0, 100], dtype=torch.int32, device=dev)
         n_past = torch.tensor([412], dtype=torch.int32, device=dev)
-        out = torch.empty_like(q)
-        ops.prefill_attention(q, cache, q_start, n_past, table, out, 1, 100, n_head, n_kv_head, head_dim, page_size,
-                              1.0 / math.sqrt(head_dim), 0)
         ref = _attention_reference(refs, n_head, n_kv_head, 1.0 / math.sqrt(head_dim), 0)
-        assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}"
+        for tcgen05 in (False, True):
+            out = torch.empty_like(q)
+            ops.prefill_attention(q, cache, q_start, n_past, table, out, 1, 100, n_head, n_kv_head, head_dim, page_size,
+                                  1.0 / math.sqrt(head_dim), 0, tcgen05=tcgen05)
+            assert (out.double().cpu() - ref).abs().max().item() < 1.5e-2, f"far key at {key_pos}, tcgen05={tcgen05}"
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
