@@ -266,11 +266,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // First pass: the maximum of this half of the row; the halves meet in shared memory.
             float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
             if (ok) {
-#pragma unroll 1
+                uint32_t v2[2][32];                       // both chunks of the half are requested before either is used
+                tmem_ld32(s_row, v2[0]);
+                tmem_ld32(s_row + 32, v2[1]);
+                tmem_ld_wait();
+#pragma unroll
                 for (int ch = 0; ch < 2; ++ch) {
-                    uint32_t v[32];
-                    tmem_ld32(s_row + ch * 32, v);
-                    tmem_ld_wait();
+                    const uint32_t (&v)[32] = v2[ch];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
                         float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
@@ -298,11 +300,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // Second pass: probabilities -> shared memory (bfloat16, swizzled), and their sum.
             float sum0 = 0.0f, sum1 = 0.0f;
             uint8_t* half_row = p_row + (size_t)(pb * 2 + half) * kTileBytes;
-#pragma unroll 1
+            uint32_t w2[2][32];
+            tmem_ld32(s_row, w2[0]);
+            tmem_ld32(s_row + 32, w2[1]);
+            tmem_ld_wait();
+#pragma unroll
             for (int ch = 0; ch < 2; ++ch) {
-                uint32_t v[32];
-                tmem_ld32(s_row + ch * 32, v);
-                tmem_ld_wait();
+                const uint32_t (&v)[32] = w2[ch];
 #pragma unroll
                 for (int q8 = 0; q8 < 4; ++q8) {
                     float p[8];
