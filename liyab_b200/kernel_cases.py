@@ -48,6 +48,19 @@ def _graph_timed(launch, reps: int, per_graph: int = 20) -> float:
     return _timed(graph.replay, max(1, reps // per_graph)) / per_graph
 
 
+class _Scratch:
+    """The scratch buffers that ops.linear asks a workspace for (split-K partial sums and counters)."""
+
+    def __init__(self, dev):
+        self.dev, self.bufs = dev, {}
+
+    def flat(self, name, n, dtype, zero=False):
+        key = (name, dtype)
+        if key not in self.bufs or self.bufs[key].numel() < n:
+            self.bufs[key] = torch.zeros(n, dtype=dtype, device=self.dev)
+        return self.bufs[key][:n]
+
+
 def case_gemm(args) -> None:
     from . import ops
     dev = torch.device("cuda:0")
@@ -62,7 +75,8 @@ def case_gemm(args) -> None:
     elif args.m > 64 and ops.gemm_persistent_tile(a, w, out, args.m, res) > 0:
         launch = lambda: ops.gemm_persistent(a, w, bias, out, args.m, args.act, residual=res, feature_tile=args.tile)
     else:
-        launch = lambda: ops.linear(a, w, bias, out, args.m, args.act, residual=res)
+        ws = _Scratch(dev)
+        launch = lambda: ops.linear(a, w, bias, out, args.m, args.act, residual=res, workspace=ws)
     ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
     print(f"gemm M={args.m} N={args.n} K={args.k} out={args.out}: {ms * 1e3:.1f} us per launch (includes the host's "
           f"launch cost when the kernel is shorter), {2 * args.m * args.n * args.k / ms / 1e9:.1f} TFLOP/s, "
