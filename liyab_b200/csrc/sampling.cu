@@ -20,6 +20,7 @@
 namespace {
 
 constexpr int kThreads = 1024;
+constexpr int kSmallK = 1024;      // up to this many top-k candidates are gathered and finished in shared memory
 
 // Monotone map from float to uint32: a larger float gives a larger key.
 __device__ __forceinline__ uint32_t order_key(float v) {
@@ -93,7 +94,7 @@ __device__ T block_exclusive_scan(T v, T* scratch /* 33 */, T* total) {
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const double* __restrict__ uniform,
-              int32_t* __restrict__ out_ids, float* __restrict__ out_probs) {
+              int32_t* __restrict__ out_ids, float* __restrict__ out_probs, int staged) {
     __shared__ ArgMax am_scratch[33];
     __shared__ int i_scratch[33];
     __shared__ double d_scratch[33];
@@ -105,7 +106,15 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     __shared__ int sh_choice;
 
     const int row = blockIdx.x, tid = threadIdx.x;
+    // The row is walked a dozen times: where it fits, it is copied to shared memory first (one pass of coalesced
+    // loads, all in flight) and every later pass reads it there.
+    extern __shared__ __align__(16) float row_s[];
     const float* x = logits + (size_t)row * row_stride;
+    if (staged) {
+        for (int i = tid; i < vocab; i += kThreads) row_s[i] = x[i];
+        __syncthreads();
+        x = row_s;
+    }
     float* probs = out_probs != nullptr ? out_probs + (size_t)row * vocab : nullptr;
     const float temp = temperature[row];
 
@@ -136,9 +145,16 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
             for (int b = tid; b < 256; b += kThreads) hist_count[b] = 0;
             __syncthreads();
             const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            for (int i = tid; i < vocab; i += kThreads) {
-                const uint32_t key = order_key(x[i]);
-                if ((key & mask) == prefix) atomicAdd(&hist_count[(key >> shift) & 255u], 1);
+            // Thousands of keys share a few buckets (sign and exponent): lanes with the same bucket add once, together.
+            for (int i0 = 0; i0 < vocab; i0 += kThreads) {
+                const int i = i0 + tid;
+                int bucket = -1;
+                if (i < vocab) {
+                    const uint32_t key = order_key(x[i]);
+                    if ((key & mask) == prefix) bucket = (int)((key >> shift) & 255u);
+                }
+                const unsigned peers = __match_any_sync(0xffffffffu, bucket);
+                if (bucket >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist_count[bucket], __popc(peers));
             }
             __syncthreads();
             if (tid == 0) {
@@ -168,6 +184,98 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
         tie_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
     }
     // member(i): key > kth_key, or key == kth_key and its rank among such ties < kth_need.
+
+    // ---- few candidates (the usual top-k of some dozens): gather them, in index order, and finish among them.
+    // Same distribution and the same order of every sum as the general path below, which walks the whole
+    // vocabulary four more times with a histogram of probability mass per pass.
+    if (k > 0 && k < vocab && k <= kSmallK) {
+        __shared__ int cand_idx[kSmallK];
+        __shared__ float cand_e[kSmallK];          // exp((logit - max) / T), in index order
+        __shared__ uint32_t cand_key[kSmallK];
+        __shared__ float sorted_e[kSmallK];        // the same by (logit descending, index ascending)
+        __shared__ int cand_rank[kSmallK];
+        __shared__ int sh_n, sh_cut;
+        int mine = 0, rank = tie_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            mine += member ? 1 : 0;
+        }
+        int n;
+        int at = block_exclusive_scan<int>(mine, i_scratch, &n);
+        rank = tie_rank_base;
+        for (int i = lo; i < hi; ++i) {
+            const uint32_t key = order_key(x[i]);
+            bool member = key > kth_key;
+            if (key == kth_key) member = rank++ < kth_need;
+            if (member && at < kSmallK) {
+                cand_idx[at] = i;
+                cand_key[at] = key;
+                cand_e[at] = expf((x[i] - max_logit) * inv_t);
+                ++at;
+            }
+        }
+        n = min(n, kSmallK);
+        __syncthreads();
+        // Rank of every candidate by counting who comes before it.
+        for (int c = tid; c < n; c += kThreads) {
+            const uint32_t key = cand_key[c];
+            int before = 0;
+            for (int j = 0; j < n; ++j) before += (cand_key[j] > key || (cand_key[j] == key && j < c)) ? 1 : 0;
+            cand_rank[c] = before;
+            sorted_e[before] = cand_e[c];
+        }
+        __syncthreads();
+        if (tid == 0) {
+            double total_mass = 0.0;
+            for (int c = 0; c < n; ++c) total_mass += (double)cand_e[c];
+            const float p_cut = top_p[row];
+            int cut = n;
+            if (p_cut < 1.0f) {
+                double acc = 0.0;
+                for (int r = 0; r < n; ++r) {
+                    acc += (double)sorted_e[r];
+                    if (acc / total_mass >= (double)p_cut) {
+                        cut = r + 1;
+                        break;
+                    }
+                }
+            }
+            double kept_mass = 0.0;
+            for (int c = 0; c < n; ++c)
+                if (cand_rank[c] < cut) kept_mass += (double)cand_e[c];
+            double total = 0.0;
+            for (int c = 0; c < n; ++c)
+                if (cand_rank[c] < cut) total += (double)(float)((double)cand_e[c] / kept_mass);
+            double left = uniform[row] * total;
+            int choice = -1, last = -1;
+            for (int c = 0; c < n && choice < 0; ++c) {
+                if (cand_rank[c] >= cut) continue;
+                if (cand_e[c] > 0.0f) last = cand_idx[c];
+                left -= (double)(float)((double)cand_e[c] / kept_mass);
+                if (left < 0.0) choice = cand_idx[c];
+            }
+            if (choice < 0) {           // rounding left the draw at or past the last kept id: the last id with mass
+                for (int c = 0; c < n; ++c)
+                    if (cand_rank[c] < cut && cand_e[c] > 0.0f) last = cand_idx[c];
+                choice = last >= 0 ? last : best.i;
+            }
+            out_ids[row] = choice;
+            sh_cut = cut;
+            sh_double = kept_mass;
+            sh_n = n;
+        }
+        if (probs != nullptr) {
+            for (int i = tid; i < vocab; i += kThreads) probs[i] = 0.0f;
+            __syncthreads();
+            const int cut = sh_cut;
+            const double kept_mass = sh_double;
+            for (int c = tid; c < sh_n; c += kThreads)
+                if (cand_rank[c] < cut) probs[cand_idx[c]] = (float)((double)cand_e[c] / kept_mass);
+        }
+        return;
+    }
 
     // ---- total mass of the members.
     double total_mass;
@@ -331,8 +439,19 @@ extern "C" int lb_sample(const float* logits, int64_t row_stride, int n_rows, in
                          float* out_probs, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
     if (n_rows == 0) return LB_OK;
-    sample_kernel<<<n_rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs);
+    // Shared memory left for the row beside the kernel's static arrays.
+    static size_t room = 0;
+    if (room == 0) {
+        cudaFuncAttributes attr;
+        LB_CHECK_CUDA(cudaFuncGetAttributes(&attr, sample_kernel));
+        const size_t limit = 227 * 1024;
+        room = limit > attr.sharedSizeBytes + 1024 ? limit - attr.sharedSizeBytes - 1024 : 1;
+        LB_CHECK_CUDA(cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room));
+    }
+    const size_t row_bytes = (size_t)vocab * sizeof(float);
+    const int staged = row_bytes <= room ? 1 : 0;
+    sample_kernel<<<n_rows, kThreads, staged ? row_bytes : 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs, staged);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -3,6 +3,7 @@
     python -m liyab_b200.kernel_cases gemm --m 2048 --n 768 --k 3072 --out float32 --reps 20
     python -m liyab_b200.kernel_cases decode-attention --batch 64 --context 768 --reps 20
     python -m liyab_b200.kernel_cases prefill-attention --seqs 2 --length 1024 --reps 20
+    python -m liyab_b200.kernel_cases sample --rows 8 --vocab 50257 --temp 0.8 --top-k 40 --top-p 0.95
     python -m liyab_b200.kernel_cases decode-step --batch 8 --layers 12 --reps 20 [--eager]
     python -m liyab_b200.kernel_cases prefill-step --tokens 2048 --layers 12 --reps 3
 
@@ -130,6 +131,21 @@ def case_prefill_attention(args) -> None:
           f"(causal half of the square)")
 
 
+def case_sample(args) -> None:
+    from . import ops
+    dev = torch.device("cuda:0")
+    R, V = args.rows, args.vocab
+    logits = torch.randn(R, V, device=dev) * 3.0
+    temp = torch.full((R,), args.temp, device=dev)
+    top_k = torch.full((R,), args.top_k, dtype=torch.int32, device=dev)
+    top_p = torch.full((R,), args.top_p, device=dev)
+    u = torch.rand(R, dtype=torch.float64, device=dev)
+    ids = torch.empty(R, dtype=torch.int32, device=dev)
+    ms = _graph_timed(lambda: ops.sample(logits, R, temp, top_k, top_p, u, ids), args.reps)
+    print(f"sample rows={R} vocab={V} temp={args.temp} top_k={args.top_k} top_p={args.top_p}: {ms * 1e3:.1f} us "
+          f"(20 launches per CUDA graph)")
+
+
 def _model_folder(layers: int, dtype: str) -> str:
     from .config import parse_config
     from .weights import write_random_model
@@ -214,6 +230,13 @@ def main(argv=None) -> int:
     a.add_argument("--reps", type=int, default=20)
     a.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     a.add_argument("--mma-sync", action="store_true", help="the mma.sync kernel even where the tcgen05 one takes the shape")
+    sm = sub.add_parser("sample")
+    sm.add_argument("--rows", type=int, default=8)
+    sm.add_argument("--vocab", type=int, default=50257)
+    sm.add_argument("--temp", type=float, default=0.8)
+    sm.add_argument("--top-k", type=int, default=40)
+    sm.add_argument("--top-p", type=float, default=0.95)
+    sm.add_argument("--reps", type=int, default=400)
     for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
@@ -224,7 +247,7 @@ def main(argv=None) -> int:
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true")
     args = ap.parse_args(argv)
-    {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "decode-step": case_decode_step,
+    {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
      "prefill-step": case_prefill_step}[args.case](args)
     return 0
 
