@@ -20,7 +20,8 @@
 namespace {
 
 constexpr int kThreads = 1024;
-constexpr int kSmallK = 1024;      // up to this many top-k candidates are gathered and finished in shared memory
+constexpr int kSmallK = 256;       // a top-k up to this takes the short way: a threshold, then a list of candidates
+constexpr int kMaxList = 1024;     // candidates (logits that reach the threshold) the short way takes
 
 // Monotone map from float to uint32: a larger float gives a larger key.
 __device__ __forceinline__ uint32_t order_key(float v) {
@@ -94,7 +95,7 @@ __device__ T block_exclusive_scan(T v, T* scratch /* 33 */, T* total) {
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const double* __restrict__ uniform,
-              int32_t* __restrict__ out_ids, float* __restrict__ out_probs, int staged) {
+              int32_t* __restrict__ out_ids, float* __restrict__ out_probs) {
     __shared__ ArgMax am_scratch[33];
     __shared__ int i_scratch[33];
     __shared__ double d_scratch[33];
@@ -106,15 +107,7 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     __shared__ int sh_choice;
 
     const int row = blockIdx.x, tid = threadIdx.x;
-    // The row is walked a dozen times: where it fits, it is copied to shared memory first (one pass of coalesced
-    // loads, all in flight) and every later pass reads it there.
-    extern __shared__ __align__(16) float row_s[];
     const float* x = logits + (size_t)row * row_stride;
-    if (staged) {
-        for (int i = tid; i < vocab; i += kThreads) row_s[i] = x[i];
-        __syncthreads();
-        x = row_s;
-    }
     float* probs = out_probs != nullptr ? out_probs + (size_t)row * vocab : nullptr;
     const float temp = temperature[row];
 
@@ -124,6 +117,7 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
 
     ArgMax best{-CUDART_INF_F, 0x7fffffff};
     for (int i = tid; i < vocab; i += kThreads) best = better(best, ArgMax{x[i], i});
+    const uint32_t my_max_key = best.i != 0x7fffffff ? order_key(best.v) : 0u;      // largest key among this thread's logits
     best = block_argmax(best, am_scratch);
     if (temp <= 0.0f) {
         if (probs != nullptr)
@@ -134,8 +128,147 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     const float max_logit = best.v;
     const float inv_t = 1.0f / temp;
 
-    // ---- top-k by count: key of the k-th largest, and how many ties at it are kept.
     int k = top_k[row];
+    // ---- the short way for the usual top-k of some dozens: two more walks over the vocabulary instead of a dozen.
+    // A threshold that at least k logits reach and few more do is found from the threads' own maxima; the logits
+    // that reach it go to a list in shared memory, and everything else (exact top-k with
+    // ties to the lower index, the softmax, the top-p cut, the draw) happens among them, with the same
+    // distribution and tie rules as the general path below.  A list that would be too long takes the general path.
+    if (k > 0 && k < vocab && k <= kSmallK) {
+        __shared__ uint32_t max_keys[kThreads];
+        __shared__ int list_idx[kMaxList];
+        __shared__ uint32_t list_key[kMaxList];
+        __shared__ int list_rank[kMaxList];
+        __shared__ int cand_idx[kSmallK];
+        __shared__ float cand_e[kSmallK];          // exp((logit - max) / T), in index order
+        __shared__ int cand_rank[kSmallK];         // place by (logit descending, index ascending)
+        __shared__ float sorted_e[kSmallK];        // cand_e in that order
+        __shared__ int sh_count, sh_list_n, sh_cut;
+        // The k-th largest of the 1,024 threads' own maxima is a lower bound of the k-th largest logit (k logits
+        // are at least that large), and few other logits are: it is the threshold of the list.  Found by sorting
+        // the maxima (bitonic, descending, in shared memory: no atomics).
+        max_keys[tid] = my_max_key;
+        if (tid == 0) sh_list_n = 0;
+        __syncthreads();
+        for (int size = 2; size <= kThreads; size <<= 1) {
+            for (int stride = size >> 1; stride > 0; stride >>= 1) {
+                const int partner = tid ^ stride;
+                if (partner > tid) {
+                    const uint32_t a = max_keys[tid], b2 = max_keys[partner];
+                    const bool descending = (tid & size) == 0;
+                    if (descending ? a < b2 : a > b2) {
+                        max_keys[tid] = b2;
+                        max_keys[partner] = a;
+                    }
+                }
+                __syncthreads();
+            }
+        }
+        const uint32_t threshold = max_keys[k - 1];
+        // How many logits reach the threshold.
+        {
+            int mine = 0;
+            for (int i = tid; i < vocab; i += kThreads) mine += order_key(x[i]) >= threshold ? 1 : 0;
+            int total;
+            block_exclusive_scan<int>(mine, i_scratch, &total);
+            if (tid == 0) sh_count = total;
+        }
+        __syncthreads();
+        const int n_list = sh_count;
+        if (n_list <= kMaxList) {
+            for (int i = tid; i < vocab; i += kThreads) {
+                const uint32_t key = order_key(x[i]);
+                if (key >= threshold) {
+                    const int at = atomicAdd(&sh_list_n, 1);
+                    list_idx[at] = i;
+                    list_key[at] = key;
+                }
+            }
+            __syncthreads();
+            // Place of every listed logit by (key descending, index ascending): the first k are the members.
+            for (int c = tid; c < n_list; c += kThreads) {
+                const uint32_t key = list_key[c];
+                const int idx = list_idx[c];
+                int before = 0;
+                for (int j = 0; j < n_list; ++j) before += (list_key[j] > key || (list_key[j] == key && list_idx[j] < idx)) ? 1 : 0;
+                list_rank[c] = before;
+            }
+            __syncthreads();
+            // Members in index order.
+            for (int c = tid; c < n_list; c += kThreads) {
+                if (list_rank[c] >= k) continue;
+                const int idx = list_idx[c];
+                int at = 0;
+                for (int j = 0; j < n_list; ++j) at += (list_rank[j] < k && list_idx[j] < idx) ? 1 : 0;
+                const float e = expf((x[idx] - max_logit) * inv_t);
+                cand_idx[at] = idx;
+                cand_e[at] = e;
+                cand_rank[at] = list_rank[c];
+                sorted_e[list_rank[c]] = e;
+            }
+            __syncthreads();
+            const int n = k;
+            // The sums run in a fixed order on one thread (they are a few dozen additions); the divisions, which
+            // are slow in double precision, run one per thread.
+            __shared__ double acc_s[kSmallK];
+            __shared__ float cand_p[kSmallK];
+            __shared__ double sh_total_mass;
+            const float p_cut = top_p[row];
+            if (tid == 0) {
+                double total_mass = 0.0;
+                for (int c = 0; c < n; ++c) total_mass += (double)cand_e[c];
+                double acc = 0.0;
+                for (int r = 0; r < n; ++r) {
+                    acc += (double)sorted_e[r];
+                    acc_s[r] = acc;
+                }
+                sh_total_mass = total_mass;
+                sh_cut = n;
+            }
+            __syncthreads();
+            if (tid < n && p_cut < 1.0f && acc_s[tid] / sh_total_mass >= (double)p_cut) atomicMin(&sh_cut, tid + 1);
+            __syncthreads();
+            const int cut = sh_cut;
+            if (tid == 0) {
+                double kept_mass = 0.0;
+                for (int c = 0; c < n; ++c)
+                    if (cand_rank[c] < cut) kept_mass += (double)cand_e[c];
+                sh_double = kept_mass;
+            }
+            __syncthreads();
+            const double kept_mass = sh_double;
+            if (tid < n) cand_p[tid] = cand_rank[tid] < cut ? (float)((double)cand_e[tid] / kept_mass) : 0.0f;
+            __syncthreads();
+            if (tid == 0) {
+                double total = 0.0;
+                for (int c = 0; c < n; ++c)
+                    if (cand_rank[c] < cut) total += (double)cand_p[c];
+                double left = uniform[row] * total;
+                int choice = -1, last = -1;
+                for (int c = 0; c < n && choice < 0; ++c) {
+                    if (cand_rank[c] >= cut) continue;
+                    left -= (double)cand_p[c];
+                    if (left < 0.0) choice = cand_idx[c];
+                }
+                if (choice < 0) {           // rounding left the draw at or past the last kept id: the last id with mass
+                    for (int c = 0; c < n; ++c)
+                        if (cand_rank[c] < cut && cand_e[c] > 0.0f) last = cand_idx[c];
+                    choice = last >= 0 ? last : best.i;
+                }
+                out_ids[row] = choice;
+            }
+            if (probs != nullptr) {
+                for (int i = tid; i < vocab; i += kThreads) probs[i] = 0.0f;
+                __syncthreads();
+                for (int c = tid; c < n; c += kThreads)
+                    if (cand_rank[c] < cut) probs[cand_idx[c]] = cand_p[c];
+            }
+            return;
+        }
+    }
+
+    // ---- top-k by count: key of the k-th largest, and how many ties at it are kept.
+
     uint32_t kth_key = 0;          // every key >= 0 is a member when top-k is off
     int kth_need = 0x7fffffff;     // ties at kth_key that are members (by index order)
     if (k > 0 && k < vocab) {
@@ -184,98 +317,6 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
         tie_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
     }
     // member(i): key > kth_key, or key == kth_key and its rank among such ties < kth_need.
-
-    // ---- few candidates (the usual top-k of some dozens): gather them, in index order, and finish among them.
-    // Same distribution and the same order of every sum as the general path below, which walks the whole
-    // vocabulary four more times with a histogram of probability mass per pass.
-    if (k > 0 && k < vocab && k <= kSmallK) {
-        __shared__ int cand_idx[kSmallK];
-        __shared__ float cand_e[kSmallK];          // exp((logit - max) / T), in index order
-        __shared__ uint32_t cand_key[kSmallK];
-        __shared__ float sorted_e[kSmallK];        // the same by (logit descending, index ascending)
-        __shared__ int cand_rank[kSmallK];
-        __shared__ int sh_n, sh_cut;
-        int mine = 0, rank = tie_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
-            bool member = key > kth_key;
-            if (key == kth_key) member = rank++ < kth_need;
-            mine += member ? 1 : 0;
-        }
-        int n;
-        int at = block_exclusive_scan<int>(mine, i_scratch, &n);
-        rank = tie_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
-            bool member = key > kth_key;
-            if (key == kth_key) member = rank++ < kth_need;
-            if (member && at < kSmallK) {
-                cand_idx[at] = i;
-                cand_key[at] = key;
-                cand_e[at] = expf((x[i] - max_logit) * inv_t);
-                ++at;
-            }
-        }
-        n = min(n, kSmallK);
-        __syncthreads();
-        // Rank of every candidate by counting who comes before it.
-        for (int c = tid; c < n; c += kThreads) {
-            const uint32_t key = cand_key[c];
-            int before = 0;
-            for (int j = 0; j < n; ++j) before += (cand_key[j] > key || (cand_key[j] == key && j < c)) ? 1 : 0;
-            cand_rank[c] = before;
-            sorted_e[before] = cand_e[c];
-        }
-        __syncthreads();
-        if (tid == 0) {
-            double total_mass = 0.0;
-            for (int c = 0; c < n; ++c) total_mass += (double)cand_e[c];
-            const float p_cut = top_p[row];
-            int cut = n;
-            if (p_cut < 1.0f) {
-                double acc = 0.0;
-                for (int r = 0; r < n; ++r) {
-                    acc += (double)sorted_e[r];
-                    if (acc / total_mass >= (double)p_cut) {
-                        cut = r + 1;
-                        break;
-                    }
-                }
-            }
-            double kept_mass = 0.0;
-            for (int c = 0; c < n; ++c)
-                if (cand_rank[c] < cut) kept_mass += (double)cand_e[c];
-            double total = 0.0;
-            for (int c = 0; c < n; ++c)
-                if (cand_rank[c] < cut) total += (double)(float)((double)cand_e[c] / kept_mass);
-            double left = uniform[row] * total;
-            int choice = -1, last = -1;
-            for (int c = 0; c < n && choice < 0; ++c) {
-                if (cand_rank[c] >= cut) continue;
-                if (cand_e[c] > 0.0f) last = cand_idx[c];
-                left -= (double)(float)((double)cand_e[c] / kept_mass);
-                if (left < 0.0) choice = cand_idx[c];
-            }
-            if (choice < 0) {           // rounding left the draw at or past the last kept id: the last id with mass
-                for (int c = 0; c < n; ++c)
-                    if (cand_rank[c] < cut && cand_e[c] > 0.0f) last = cand_idx[c];
-                choice = last >= 0 ? last : best.i;
-            }
-            out_ids[row] = choice;
-            sh_cut = cut;
-            sh_double = kept_mass;
-            sh_n = n;
-        }
-        if (probs != nullptr) {
-            for (int i = tid; i < vocab; i += kThreads) probs[i] = 0.0f;
-            __syncthreads();
-            const int cut = sh_cut;
-            const double kept_mass = sh_double;
-            for (int c = tid; c < sh_n; c += kThreads)
-                if (cand_rank[c] < cut) probs[cand_idx[c]] = (float)((double)cand_e[c] / kept_mass);
-        }
-        return;
-    }
 
     // ---- total mass of the members.
     double total_mass;
@@ -439,19 +480,8 @@ extern "C" int lb_sample(const float* logits, int64_t row_stride, int n_rows, in
                          float* out_probs, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
     if (n_rows == 0) return LB_OK;
-    // Shared memory left for the row beside the kernel's static arrays.
-    static size_t room = 0;
-    if (room == 0) {
-        cudaFuncAttributes attr;
-        LB_CHECK_CUDA(cudaFuncGetAttributes(&attr, sample_kernel));
-        const size_t limit = 227 * 1024;
-        room = limit > attr.sharedSizeBytes + 1024 ? limit - attr.sharedSizeBytes - 1024 : 1;
-        LB_CHECK_CUDA(cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)room));
-    }
-    const size_t row_bytes = (size_t)vocab * sizeof(float);
-    const int staged = row_bytes <= room ? 1 : 0;
-    sample_kernel<<<n_rows, kThreads, staged ? row_bytes : 0, static_cast<cudaStream_t>(stream)>>>(
-        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs, staged);
+    sample_kernel<<<n_rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
