@@ -8,10 +8,14 @@
 // the ids in index order subtracting p_i from r = u * total until r < 0
 // (sampling.cpp:66-79).  Greedy takes the first maximum (sampling.cpp:12-14).
 // Where the reference's order among equal logits is left to std::nth_element and
-// std::sort, ties here go to the lower index.  Nothing is sorted: the k-th
-// largest logit and the top-p cut are found by radix selection over the logits'
-// bit patterns (four passes of eight bits), by count for top-k and by probability
-// mass for top-p.
+// std::sort, ties here go to the lower index.  In general nothing is sorted: the
+// k-th largest logit and the top-p cut are found by radix selection over the
+// logits' bit patterns (four passes of eight bits), by count for top-k and by
+// probability mass for top-p.  A top-k of up to 256 (the usual case: 40) takes a
+// short way instead: a threshold that at least k logits reach comes from the
+// block's 1,024 per-thread maxima, the few logits that reach it are listed in
+// shared memory and the rest happens among them (27 us instead of 200 us per step
+// at a vocabulary of 50,257; one block per row walks the row three times).
 #include "api.h"
 #include "common.cuh"
 
