@@ -60,6 +60,11 @@ int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, in
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
                     int token_tile, float* partial, int* counters, int n_splits, void* stream);
 int lb_gemm_tcgen05_token_tile(int M, int N);
+/* The same product for 17 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
+ * no second kernel): lb_gemm_rows_supports tells whether it takes the product. */
+int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K);
+int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                 const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, void* stream);
 /* The same product for more than 64 tokens as a persistent kernel: one block per SM walks tiles of 128 tokens x
  * feature_tile features, operands, residual and result all moved by TMA, the epilogue of a tile under the products
  * of the next.  lb_gemm_persistent_tile returns the feature tile it would choose, or 0 where the kernel does not

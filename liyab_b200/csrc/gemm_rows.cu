@@ -1,0 +1,215 @@
+// out[M, N] = epilogue(A[M, K] . W[N, K]^T) for 17 to 64 tokens (bfloat16
+// operands): the products of a decode step that is too large for the one-kernel
+// fused step and too small to fill a tcgen05 tile row.
+//
+// At these sizes a product reads a few MB of weights and does next to no
+// arithmetic; what it costs is latency.  The tcgen05 kernel needs K split over
+// blocks and a second kernel to add the partial sums (two launches, 8-9 us per
+// product).  Here one launch does it: every block takes a slice of the output
+// features and the whole reduction length, as the matrix phases of the fused
+// decode step do: the activations of all tokens come into shared memory by
+// cp.async in chunks of 256 columns (two buffers: the next chunk travels while the
+// current one is used), each warp takes 32 columns of every chunk, requests all
+// its weights of the pass (up to four groups of eight features) at the start with
+// 16-byte loads that go straight into mma.sync m16n8k16 fragments (tokens are the
+// rows: up to four tiles of 16), and the eight warps' partial tiles are summed in
+// warp order through shared memory.
+// Every weight byte is read once; a row's result does not depend on the other
+// rows.  Accumulators, bias, activation and residual sum are 32-bit, in the
+// reference's order (src/core/transformer.cpp:111-118, 4903-4912, 5526-5532).
+#include "api.h"
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr int kChunk = 256;           // columns of the activations per chunk: one k-block of 32 per warp
+constexpr int kChunkLd = kChunk + 32; // row stride in a buffer: 64 bytes mod 128, conflict-free 16-byte reads
+constexpr int kMaxRows = 64;
+constexpr int kWRegs = 16;            // 16-byte weight pieces a thread holds: groups per pass x chunks
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_addr(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MT: tiles of 16 tokens (2, 3 or 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
+// of up to 1024, 2048 or 4096 (NG x chunks = the 16 weight pieces a thread holds: all of a pass's weights are
+// requested at its start, one DRAM round trip, and used as the chunks of activations come in).
+template <int MT, int NG, typename TO>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
+                 const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M, int N, int K,
+                 int act) {
+    constexpr int kRows = MT * 16, MC = kWRegs / NG;
+    extern __shared__ __align__(16) uint8_t smem_bytes[];
+    __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);                       // [2][kRows][kChunkLd]
+    float* red_s = reinterpret_cast<float*>(smem_bytes + (size_t)2 * kRows * kChunkLd * sizeof(__nv_bfloat16));   // [kWarps][NG][MT][128]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int n_groups = (N + 7) / 8;
+    const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int g_begin = min(n_groups, (int)blockIdx.x * per_cta), g_end = min(n_groups, g_begin + per_cta);
+    const int n_chunks = (K + kChunk - 1) / kChunk;            // at most MC (the host checks)
+
+    // Chunk c of the activations -> buffer c & 1 (rows past M and columns past K as zeros).
+    auto stage = [&](int c) {
+        __nv_bfloat16* dst = act_s + (size_t)(c & 1) * kRows * kChunkLd;
+        const int k0 = c * kChunk;
+        constexpr int kPieces = kChunk / 8;
+        for (int idx = threadIdx.x; idx < kRows * kPieces; idx += kThreads) {
+            const int r = idx / kPieces, p = idx - r * kPieces;
+            const bool valid = r < M && k0 + p * 8 < K;
+            cp_async16(dst + r * kChunkLd + p * 8, A + (valid ? (size_t)r * lda + k0 + p * 8 : 0), valid);
+        }
+    };
+
+    for (int gp = g_begin; gp < g_end; gp += NG) {
+        const int ng = min(NG, g_end - gp);
+        // This warp's k-block of every chunk (columns c * 256 + warp * 32 ...), for every group of the pass.
+        uint4 w[kWRegs];
+#pragma unroll
+        for (int c = 0; c < MC; ++c)
+#pragma unroll
+            for (int gi = 0; gi < NG; ++gi) {
+                const int f = (gp + gi) * 8 + g, k = c * kChunk + warp * 32 + t * 8;
+                w[c * NG + gi] = (c < n_chunks && gi < ng && f < N && k < K) ? __ldg(reinterpret_cast<const uint4*>(W + (size_t)f * ldw + k))
+                                                                           : make_uint4(0, 0, 0, 0);
+            }
+        float acc[NG][MT][4];
+#pragma unroll
+        for (int i = 0; i < NG; ++i)
+#pragma unroll
+            for (int m = 0; m < MT; ++m) acc[i][m][0] = acc[i][m][1] = acc[i][m][2] = acc[i][m][3] = 0.0f;
+        stage(0);
+        cp_async_commit();
+#pragma unroll
+        for (int c = 0; c < MC; ++c) {
+            if (c < n_chunks) {                                 // the same for every thread
+                if (c + 1 < n_chunks) stage(c + 1);
+                cp_async_commit();
+                cp_async_wait<1>();
+                __syncthreads();
+                const __nv_bfloat16* buf = act_s + (size_t)(c & 1) * kRows * kChunkLd + warp * 32 + t * 8;
+                if (c * kChunk + warp * 32 < K) {
+#pragma unroll
+                    for (int m = 0; m < MT; ++m) {
+                        const uint4 lo = *reinterpret_cast<const uint4*>(buf + (m * 16 + g) * kChunkLd);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(buf + (m * 16 + g + 8) * kChunkLd);
+#pragma unroll
+                        for (int gi = 0; gi < NG; ++gi) {
+                            if (gi < ng) {
+                                mma_bf16(acc[gi][m], lo.x, hi.x, lo.y, hi.y, w[c * NG + gi].x, w[c * NG + gi].y);
+                                mma_bf16(acc[gi][m], lo.z, hi.z, lo.w, hi.w, w[c * NG + gi].z, w[c * NG + gi].w);
+                            }
+                        }
+                    }
+                }
+                __syncthreads();        // the buffer is free: the chunk after next goes into it
+            }
+        }
+        // Partial tiles of the eight warps -> shared memory -> summed in warp order -> epilogue.
+#pragma unroll
+        for (int gi = 0; gi < NG; ++gi) {
+            if (gi < ng) {
+#pragma unroll
+                for (int m = 0; m < MT; ++m) {
+                    float* tile = red_s + ((size_t)(warp * NG + gi) * MT + m) * 128;
+                    tile[g * 8 + 2 * t] = acc[gi][m][0];
+                    tile[g * 8 + 2 * t + 1] = acc[gi][m][1];
+                    tile[(g + 8) * 8 + 2 * t] = acc[gi][m][2];
+                    tile[(g + 8) * 8 + 2 * t + 1] = acc[gi][m][3];
+                }
+            }
+        }
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < ng * kRows * 8; idx += kThreads) {
+            const int gi = idx / (kRows * 8), rest = idx - gi * kRows * 8, r = rest >> 3, cfeat = rest & 7;
+            const int f = (gp + gi) * 8 + cfeat;
+            if (r < M && f < N) {
+                const int m = r >> 4, rr = r & 15;
+                float v = 0.0f;
+#pragma unroll
+                for (int wp = 0; wp < kWarps; ++wp) v += red_s[((size_t)(wp * NG + gi) * MT + m) * 128 + rr * 8 + cfeat];
+                float y = lb_activate(v + (bias != nullptr ? __ldg(bias + f) : 0.0f), act);
+                if (residual != nullptr) y += residual[(size_t)r * ldr + f];
+                out[(size_t)r * ldo + f] = lb_from_float<TO>(y);
+            }
+        }
+        __syncthreads();
+    }
+}
+
+template <int MT, int NG, typename TO>
+int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
+           void* out, int64_t ldo, int M, int N, int K, int act, int n_sm, cudaStream_t s) {
+    constexpr size_t smem = (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16) + (size_t)kWarps * NG * MT * 128 * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = true;
+    }
+    const int n_groups = (N + 7) / 8;
+    const int grid = n_groups < n_sm ? n_groups : n_sm;
+    gemm_rows_kernel<MT, NG, TO><<<grid, kThreads, smem, s>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias,
+                                                              residual, ldr, (TO*)out, ldo, M, N, K, act);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+template <int MT, typename TO>
+int launch_by_k(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
+                void* out, int64_t ldo, int M, int N, int K, int act, int n_sm, cudaStream_t s) {
+    if (K <= 4 * kChunk) return launch<MT, 4, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
+    if (K <= 8 * kChunk) return launch<MT, 2, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
+    return launch<MT, 1, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
+}
+
+}  // namespace
+
+// Whether the kernel takes the product: 17 to 64 tokens, a reduction length of up to 4096, K and the row strides of
+// A and W multiples of 8, 16-byte aligned bases, and at most four passes over the feature groups of a block (the
+// head's vocabulary is left to the tcgen05 kernel, whose tiles suit it).
+extern "C" int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K) {
+    if (M <= 16 || M > kMaxRows || N <= 0 || K <= 0) return 0;
+    if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0) return 0;
+    if (K > kWRegs * kChunk) return 0;
+    const int ng = K <= 4 * kChunk ? 4 : K <= 8 * kChunk ? 2 : 1;
+    return (N + 7) / 8 <= 148 * 4 * ng;
+}
+
+extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                            const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                            void* stream) {
+    LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows: unknown output dtype %d", out_dtype);
+    if (!lb_gemm_rows_supports(A, lda, W, ldw, M, N, K))
+        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows: takes 17 to 64 tokens, K and row strides multiples of 8 and 16-byte aligned "
+                       "bases (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, (long long)lda, (long long)ldw);
+    LB_CHECK_ARG(lda >= K && ldw >= K && ldo >= N, "gemm_rows: a row stride is shorter than the row");
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        LB_CHECK_CUDA(cudaGetDevice(&dev));
+        LB_CHECK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    auto s = static_cast<cudaStream_t>(stream);
+    const int mt = (M + 15) / 16;
+#define LB_GO(MT)                                                                                                          \
+    return out_dtype == LB_F32 ? launch_by_k<MT, float>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s)   \
+                               : launch_by_k<MT, __nv_bfloat16>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s)
+    if (mt <= 2) LB_GO(2);
+    if (mt == 3) LB_GO(3);
+    LB_GO(4);
+#undef LB_GO
+}

@@ -310,6 +310,53 @@ def test_gemm_persistent(dev, out_dtype, M, N, K, tile):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("out_dtype,M,N,K", [
+    (torch.float32, 17, 768, 768), (torch.float32, 64, 768, 3072), (torch.float32, 33, 1000, 200), (torch.float32, 48, 36, 4096),
+    (torch.float32, 50, 130, 1032), (torch.bfloat16, 64, 2304, 768), (torch.bfloat16, 40, 3072, 768), (torch.bfloat16, 25, 4800, 1600),
+    (torch.bfloat16, 64, 72, 328), (torch.bfloat16, 18, 5000, 2048)])
+def test_gemm_rows(dev, out_dtype, M, N, K):
+    """The one-launch product for 17 to 64 tokens against float64: every number of token tiles and of groups per
+    pass, several passes per block, ragged edges in M, N and K, all epilogues, the residual in place, a strided
+    input; and a row's bits do not depend on how many rows share the launch."""
+    from liyab_b200 import ops
+    a, w = _rand((M, K), 46, dev, torch.bfloat16), _rand((N, K), 47, dev, torch.bfloat16, 0.2)
+    bias, res = _rand((N,), 48, dev), _rand((M, N), 49, dev)
+    assert ops.gemm_rows_supports(a, w, M)
+    base = a.double() @ w.double().t()
+    scale = max(1.0, base.abs().max().item())
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
+    ops.gemm_rows(a, w, None, out, M)
+    assert (out.double() - base).abs().max().item() <= tol * scale
+    for act, fn in (("gelu_tanh", plain.gelu_tanh), ("gelu_erf", plain.gelu_erf)):
+        ops.gemm_rows(a, w, bias, out, M, act)
+        ref = torch.from_numpy(fn((base + bias.double()).cpu().numpy())).to(dev)
+        assert (out.double() - ref).abs().max().item() <= tol * scale, act
+    if out_dtype == torch.float32:
+        out2 = res.clone()
+        ops.gemm_rows(a, w, bias, out2, M, "none", residual=out2)
+        assert (out2.double() - (base + bias.double() + res.double())).abs().max().item() <= tol * scale
+        fewer = torch.empty((17, N), dtype=out_dtype, device=dev)
+        ops.gemm_rows(a[:17], w, bias, fewer, 17, "none", residual=res[:17])
+        assert torch.equal(fewer, out2[:17])
+    wide = torch.zeros((M + 3, K + 8), dtype=torch.bfloat16, device=dev)
+    wide[:M, :K] = a
+    out3 = torch.full((M + 3, N), 7.0, dtype=out_dtype, device=dev)
+    ops.gemm_rows(wide[:, :K], w, None, out3, M)
+    assert (out3[:M].double() - base).abs().max().item() <= tol * scale and (out3[M:] == 7.0).all()
+
+
+def test_gemm_rows_refuses_what_it_cannot_take(dev):
+    from liyab_b200 import ops, LiyabError
+    a, w = _rand((64, 4104), 1, dev, torch.bfloat16), _rand((16, 4104), 2, dev, torch.bfloat16)
+    assert not ops.gemm_rows_supports(a, w, 64)                # a reduction length past 4096
+    assert not ops.gemm_rows_supports(a[:, :768], w[:, :768], 16) and not ops.gemm_rows_supports(a[:, :768], w[:, :768], 65)
+    big = _rand((50304, 64), 3, dev, torch.bfloat16)
+    assert not ops.gemm_rows_supports(a[:, :64].contiguous(), big, 64)          # a vocabulary: too many groups per block
+    with pytest.raises(LiyabError):
+        ops.gemm_rows(a, w, None, torch.empty((64, 16), dtype=torch.float32, device=dev), 64)
+
+
 def test_gemm_persistent_refuses_what_it_cannot_take(dev):
     from liyab_b200 import ops, LiyabError
     a, w = _rand((100, 64), 1, dev, torch.bfloat16), _rand((50, 64), 2, dev, torch.bfloat16)
