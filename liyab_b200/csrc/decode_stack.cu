@@ -958,8 +958,10 @@ __device__ void attention_phase(const StackParams& p, const StackLayer& L, uint8
                 for (int idx = gt; idx < G * HD; idx += kUnitThreads) {
                     const int r = idx / HD, d = idx - r * HD;
                     float mm = -CUDART_INF_F;
+#pragma unroll 4
                     for (int sp = 0; sp < splits; ++sp) mm = fmaxf(mm, __ldcg(all + (size_t)sp * G * STATE + r * STATE));
                     float ll = 0.0f, a = 0.0f;
+#pragma unroll 4
                     for (int sp = 0; sp < splits; ++sp) {
                         const float* st = all + (size_t)sp * G * STATE + r * STATE;
                         const float f = exp2f(__ldcg(st) - mm);        // an empty range has m = -inf: factor 0

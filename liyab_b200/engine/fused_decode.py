@@ -132,7 +132,7 @@ class FusedDecodeStack:
         pairs = n_tokens * self.max_kv_heads
         if pairs >= 64:
             return 1, (8 if pairs <= self.n_sm else 4)
-        return max(1, min(32, (2 * self.n_sm) // pairs)), 4
+        return max(1, min(8, (2 * self.n_sm) // pairs)), 4        # more ranges only lengthen the last group's merge
 
     def run(self, ctx: StepContext) -> torch.Tensor:
         m, spec = self.model, self.model.spec
