@@ -5,7 +5,7 @@
     python bench.py --impl reference        # prints why the reference cannot run here
 
 A step is one decode step of the whole batch.  The default run has the layer
-sizes of GPT-2 small (BASELINE.json configs[2]) with random weights, a batch of
+sizes of GPT-2 small (12 layers, width 768, 12 heads) with random weights, a batch of
 8 requests and the benchmark context of 1024 positions: 512-token prompts, then
 decoding (contexts 512 -> 1024; when a request reaches the model's last position
 its cache is cut back to the prompt and decoding goes on, so any K can be timed).

@@ -36,7 +36,7 @@ def plain_sampled(model, prompt, params, stream, n_new):
 
 @pytest.mark.parametrize("graphs", [False, True])
 def test_greedy_generation_config_a(folders, graphs):
-    """BASELINE workload A: two prompts of 7 and 13 ids, 16 greedy steps, 32-bit."""
+    """Workload A: two prompts of 7 and 13 ids, 16 greedy steps, 32-bit."""
     from liyab_b200 import Engine, EngineConfig, SamplingParams
     folder = folders[("A", "float32")]
     prompts = [random_tokens(1, 7, 512), random_tokens(2, 13, 512)]
@@ -52,7 +52,7 @@ def test_greedy_generation_config_a(folders, graphs):
 
 
 def test_sampled_generation_config_b(folders):
-    """BASELINE workload B: prompts of 1, 5, 33 and 70 ids, prefilled in portions of 16 beside decoding,
+    """Workload B: prompts of 1, 5, 33 and 70 ids, prefilled in portions of 16 beside decoding,
     24 steps at temperature 0.8 with sampler seed 7."""
     from liyab_b200 import Engine, EngineConfig, SamplingParams
     folder = folders[("B", "float32")]
