@@ -103,7 +103,8 @@ struct StackParams {
     float* partial;
     int* counters;
     float* logits;
-    unsigned* barrier;
+    unsigned* barrier;               // this launch's grid-barrier counter (starts at zero)
+    unsigned* other_barrier;         // the one the launch before used: block 0 zeroes it for the launch after
     int* status;
     int n_splits, act_ld;
     int unit_warps;                  // warps that share an attention work item: 4 (two items per block at a time) or 8
@@ -990,6 +991,7 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const StackPa
         p.timing[0] = now;
     }
     for (int i = threadIdx.x; i < B; i += kThreads) pos_s[i] = p.positions[i];
+    if (blockIdx.x == 0 && threadIdx.x == 0) *p.other_barrier = 0u;
     {
         const uint4* src = reinterpret_cast<const uint4*>(p.layers);
         uint4* dst = reinterpret_cast<uint4*>(pos_s + kMaxTokens);
@@ -1261,7 +1263,11 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
     p.partial = partial;
     p.counters = counters;
     p.logits = logits;
+    // `barrier` points at one of a pair of counters (8-byte aligned pair, both zero at first) and the caller
+    // alternates between the two from launch to launch: a launch zeroes the other one (its only other user, the
+    // launch before, has ended), so the step needs no memset of its own.
     p.barrier = barrier;
+    p.other_barrier = reinterpret_cast<unsigned*>(reinterpret_cast<uintptr_t>(barrier) ^ (uintptr_t)4);
     int* status = nullptr;
     LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&status, g_stack_status));
     p.status = status;
@@ -1294,7 +1300,6 @@ extern "C" int lb_decode_stack(const void* layers_dev, int n_layers, int n_token
         LB_CHECK_CUDA(cudaFuncSetAttribute(decode_stack_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
-    LB_CHECK_CUDA(cudaMemsetAsync(barrier, 0, sizeof(unsigned), s));
     void* args[] = {&p};
     LB_CHECK_CUDA(cudaLaunchCooperativeKernel((const void*)decode_stack_kernel, dim3(g_sm_count), dim3(kThreads), args, smem, s));
     return LB_OK;

@@ -115,7 +115,7 @@ class FusedDecodeStack:
         self.logits = torch.empty((T, V), dtype=torch.float32, device=dev)
         self.partial = torch.empty(T * self.max_heads * 64 * (head_dim + 2), dtype=torch.float32, device=dev)
         self.counters = torch.zeros(T * self.max_heads, dtype=torch.int32, device=dev)
-        self.barrier = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.barrier = torch.zeros(2, dtype=torch.int32, device=dev)      # two counters, used by alternate launches
         self.pos_table = getattr(model.position, "table", None)
         self.launches = 0
         self.n_sm = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -144,7 +144,7 @@ class FusedDecodeStack:
             float(m.final_norm.spec.eps), m.head_weight.data_ptr(), _ptr(m.head_bias), ctx.tokens.data_ptr(),
             ctx.positions.data_ptr(), view.block_table.data_ptr(), view.block_table.stride(0), view.slot_mapping.data_ptr(),
             self.cache.page_size, self.x.data_ptr(), self.q.data_ptr(), self.att.data_ptr(), self.inner.data_ptr(),
-            self.partial.data_ptr(), self.counters.data_ptr(), self.logits.data_ptr(), self.barrier.data_ptr(), self.max_k,
+            self.partial.data_ptr(), self.counters.data_ptr(), self.logits.data_ptr(), self.barrier.data_ptr() + 4 * (self.launches & 1), self.max_k,
             self.head_dim, *self.splits(B), _ptr(self.timing), ops.stream_ptr()), "decode_stack")
         self.launches += 1
         return self.logits[:B]
