@@ -61,10 +61,13 @@ int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, in
                     int token_tile, float* partial, int* counters, int n_splits, void* stream);
 int lb_gemm_tcgen05_token_tile(int M, int N);
 /* The same product for 17 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
- * no second kernel): lb_gemm_rows_supports tells whether it takes the product. */
+ * no second kernel): lb_gemm_rows_supports tells whether it takes the product.  With kv_cache given (bfloat16 pages
+ * of one layer), features from q_dim on are the keys and values of a fused projection and are also written to the
+ * tokens' cache slots (as lb_kv_append would). */
 int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K);
 int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
-                 const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, void* stream);
+                 const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, void* kv_cache,
+                 const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size, void* stream);
 /* The same product for more than 64 tokens as a persistent kernel: one block per SM walks tiles of 128 tokens x
  * feature_tile features, operands, residual and result all moved by TMA, the epilogue of a tile under the products
  * of the next.  lb_gemm_persistent_tile returns the feature tile it would choose, or 0 where the kernel does not

@@ -45,6 +45,15 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Optional second destination of a fused query/key/value projection: features from q_dim on are keys, then values,
+// and go (as bfloat16) to the token's slot of its cache page as well (layout [page][K|V][kv_head][slot][head_dim];
+// slot_mapping[token] = page * page_size + slot, negative: not kept).  cache == nullptr: none.
+struct KvScatter {
+    __nv_bfloat16* cache;
+    const int32_t* slot_mapping;
+    int q_dim, n_kv_head, head_dim, page_size;
+};
+
 // MT: tiles of 16 tokens (2, 3 or 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
 // of up to 1024, 2048 or 4096 (NG x chunks = the 16 weight pieces a thread holds: all of a pass's weights are
 // requested at its start, one DRAM round trip, and used as the chunks of activations come in).
@@ -52,7 +61,7 @@ template <int MT, int NG, typename TO>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
                  const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M, int N, int K,
-                 int act) {
+                 int act, KvScatter kv) {
     constexpr int kRows = MT * 16, MC = kWRegs / NG;
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);                       // [2][kRows][kChunkLd]
@@ -145,6 +154,19 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
                 float y = lb_activate(v + (bias != nullptr ? __ldg(bias + f) : 0.0f), act);
                 if (residual != nullptr) y += residual[(size_t)r * ldr + f];
                 out[(size_t)r * ldo + f] = lb_from_float<TO>(y);
+                if (kv.cache != nullptr && f >= kv.q_dim) {
+                    // A key or value feature of a fused projection: also into the token's slot of its cache page.
+                    const int kvf = f - kv.q_dim, kv_dim = kv.n_kv_head * kv.head_dim;
+                    const int which = kvf >= kv_dim ? 1 : 0, within = kvf - which * kv_dim;
+                    const int head = within / kv.head_dim, dd = within - head * kv.head_dim;
+                    const int slot = __ldg(kv.slot_mapping + r);
+                    if (slot >= 0) {
+                        const int page = slot / kv.page_size, off = slot - page * kv.page_size;
+                        const size_t plane = (size_t)kv.n_kv_head * kv.page_size * kv.head_dim;
+                        kv.cache[(size_t)page * 2 * plane + (size_t)which * plane + ((size_t)head * kv.page_size + off) * kv.head_dim + dd] =
+                            __float2bfloat16_rn(y);
+                    }
+                }
             }
         }
         __syncthreads();
@@ -153,7 +175,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
 
 template <int MT, int NG, typename TO>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
-           void* out, int64_t ldo, int M, int N, int K, int act, int n_sm, cudaStream_t s) {
+           void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s) {
     constexpr size_t smem = (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16) + (size_t)kWarps * NG * MT * 128 * sizeof(float);
     static bool configured = false;
     if (!configured) {
@@ -163,17 +185,17 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
     const int n_groups = (N + 7) / 8;
     const int grid = n_groups < n_sm ? n_groups : n_sm;
     gemm_rows_kernel<MT, NG, TO><<<grid, kThreads, smem, s>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias,
-                                                              residual, ldr, (TO*)out, ldo, M, N, K, act);
+                                                              residual, ldr, (TO*)out, ldo, M, N, K, act, kv);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
 
 template <int MT, typename TO>
 int launch_by_k(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
-                void* out, int64_t ldo, int M, int N, int K, int act, int n_sm, cudaStream_t s) {
-    if (K <= 4 * kChunk) return launch<MT, 4, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
-    if (K <= 8 * kChunk) return launch<MT, 2, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
-    return launch<MT, 1, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s);
+                void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s) {
+    if (K <= 4 * kChunk) return launch<MT, 4, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
+    if (K <= 8 * kChunk) return launch<MT, 2, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
+    return launch<MT, 1, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
 }
 
 }  // namespace
@@ -191,6 +213,7 @@ extern "C" int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, 
 
 extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                             const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                            void* kv_cache, const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size,
                             void* stream) {
     LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows: unknown output dtype %d", out_dtype);
     if (!lb_gemm_rows_supports(A, lda, W, ldw, M, N, K))
@@ -203,11 +226,17 @@ extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const voi
         LB_CHECK_CUDA(cudaGetDevice(&dev));
         LB_CHECK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
     }
+    KvScatter kv{static_cast<__nv_bfloat16*>(kv_cache), slot_mapping, q_dim, n_kv_head, head_dim, page_size};
+    if (kv_cache != nullptr)
+        LB_CHECK_ARG(slot_mapping != nullptr && q_dim >= 0 && n_kv_head > 0 && head_dim > 0 && page_size > 0 &&
+                         q_dim + 2 * n_kv_head * head_dim == N,
+                     "gemm_rows: the cache destination needs N = q_dim + 2 * n_kv_head * head_dim (N=%d q_dim=%d heads %d x %d)", N,
+                     q_dim, n_kv_head, head_dim);
     auto s = static_cast<cudaStream_t>(stream);
     const int mt = (M + 15) / 16;
 #define LB_GO(MT)                                                                                                          \
-    return out_dtype == LB_F32 ? launch_by_k<MT, float>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s)   \
-                               : launch_by_k<MT, __nv_bfloat16>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, n_sm, s)
+    return out_dtype == LB_F32 ? launch_by_k<MT, float>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)   \
+                               : launch_by_k<MT, __nv_bfloat16>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)
     if (mt <= 2) LB_GO(2);
     if (mt == 3) LB_GO(3);
     LB_GO(4);

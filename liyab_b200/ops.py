@@ -32,7 +32,7 @@ _SIGNATURES = {
     "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
     "lb_gemm_rows_supports": [_p, _l, _p, _l, _i, _i, _i],
-    "lb_gemm_rows": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p],
+    "lb_gemm_rows": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_persistent_tile": [_i, _p, _l, _p, _l, _p, _l, _p, _l, _i, _i, _i],
     "lb_gemm_persistent_timing": [_p],
     "lb_gemm_persistent": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
@@ -210,6 +210,15 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor],
     return out
 
 
+def _kv_args(kv: Optional[tuple]) -> tuple:
+    if kv is None:
+        return None, None, 0, 0, 0, 0
+    cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size = kv
+    if cache.dtype != torch.bfloat16:
+        raise invalid_argument("gemm_rows: the cache destination must be bfloat16")
+    return _dev(cache, "cache"), _dev(slot_mapping, "slot_mapping", torch.int32), q_dim, n_kv_head, head_dim, page_size
+
+
 def gemm_rows_supports(a: torch.Tensor, w: torch.Tensor, m: int) -> bool:
     """Whether the one-launch product for 17 to 64 tokens takes these operands."""
     if not tcgen05_accepts(a, w):
@@ -218,8 +227,10 @@ def gemm_rows_supports(a: torch.Tensor, w: torch.Tensor, m: int) -> bool:
 
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
-              activation: str = "none", residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[:m] = act(a[:m] @ w.T + bias) + residual for 17 to 64 tokens: one launch, weights streamed once."""
+              activation: str = "none", residual: Optional[torch.Tensor] = None, kv: Optional[tuple] = None) -> torch.Tensor:
+    """out[:m] = act(a[:m] @ w.T + bias) + residual for 17 to 64 tokens: one launch, weights streamed once.
+    `kv` = (cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size): the features from q_dim on are keys and
+    values of a fused projection and also go to the tokens' cache slots."""
     n, k = w.shape
     if a.shape[1] != k or out.stride(1) != 1 or out.shape[1] != n:
         raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
@@ -228,7 +239,7 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
     check(lib().lb_gemm_rows(_code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
                              _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
                              residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n, k,
-                             ACTIVATIONS[activation], stream_ptr()), "gemm_rows")
+                             ACTIVATIONS[activation], *_kv_args(kv), stream_ptr()), "gemm_rows")
     return out
 
 

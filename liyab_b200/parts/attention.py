@@ -82,14 +82,20 @@ class CausalSelfAttention:
         s, T, dt = self.spec, ctx.n_tokens, self.runtime.dtype
         ws = ctx.workspace
         qkv = ws.get("attn.qkv", T, self.q_dim + 2 * self.kv_dim, dt)
-        self.qkv.forward(h, qkv, T, workspace=ws)
-        q = qkv[:, :self.q_dim]
         cache, view = ctx.kv(unit.read)
         page_size = view.group.page_size
-        if unit.write:
-            k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
-            v = qkv[:, self.q_dim + self.kv_dim:]
-            ops.kv_append(k, v, view.slot_mapping, cache, T, s.n_kv_head, s.head_dim, page_size)
+        w = self.qkv.weight
+        if (unit.write and dt == torch.bfloat16 and 16 < T <= 64 and w.shape[1] <= 1024 and ops.gemm_rows_supports(h, w, T)):
+            # A step of a few dozen tokens: the projection's epilogue also puts the new keys and values into their pages.
+            ops.gemm_rows(h, w, self.qkv.bias, qkv, T,
+                          kv=(cache, view.slot_mapping, self.q_dim, s.n_kv_head, s.head_dim, page_size))
+        else:
+            self.qkv.forward(h, qkv, T, workspace=ws)
+            if unit.write:
+                k = qkv[:, self.q_dim:self.q_dim + self.kv_dim]
+                v = qkv[:, self.q_dim + self.kv_dim:]
+                ops.kv_append(k, v, view.slot_mapping, cache, T, s.n_kv_head, s.head_dim, page_size)
+        q = qkv[:, :self.q_dim]
         att = ws.get("attn.out", T, self.q_dim, dt)
         self._attend(ctx, q, cache, view, att, page_size)
         self.out.forward(att, x, T, residual=x, workspace=ws)

@@ -346,6 +346,29 @@ def test_gemm_rows(dev, out_dtype, M, N, K):
     assert (out3[:M].double() - base).abs().max().item() <= tol * scale and (out3[M:] == 7.0).all()
 
 
+def test_gemm_rows_writes_keys_and_values_into_their_pages(dev):
+    """A fused query/key/value projection whose epilogue also fills the cache, against the product followed by
+    lb_kv_append: the same bits in the cache, tokens with a negative slot left out, other pages untouched."""
+    from liyab_b200 import ops
+    M, n_head, n_kv_head, head_dim, page_size, n_pages, K = 37, 6, 2, 64, 16, 9, 520
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    a, w = _rand((M, K), 56, dev, torch.bfloat16), _rand((q_dim + 2 * kv_dim, K), 57, dev, torch.bfloat16, 0.2)
+    bias = _rand((q_dim + 2 * kv_dim,), 58, dev)
+    rng = np.random.default_rng(5)
+    slots = rng.permutation(n_pages * page_size)[:M].astype(np.int32)
+    slots[[3, 20]] = -1
+    slot_mapping = torch.from_numpy(slots).to(dev)
+    want_cache = torch.full((n_pages, 2, n_kv_head, page_size, head_dim), 3.0, dtype=torch.bfloat16, device=dev)
+    got_cache = want_cache.clone()
+    want = torch.empty((M, q_dim + 2 * kv_dim), dtype=torch.bfloat16, device=dev)
+    ops.gemm_rows(a, w, bias, want, M)
+    ops.kv_append(want[:, q_dim:q_dim + kv_dim], want[:, q_dim + kv_dim:], slot_mapping, want_cache, M, n_kv_head, head_dim, page_size)
+    got = torch.empty_like(want)
+    ops.gemm_rows(a, w, bias, got, M, kv=(got_cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size))
+    assert torch.equal(got, want) and torch.equal(got_cache, want_cache)
+    assert (got_cache != 3.0).any()
+
+
 def test_gemm_rows_refuses_what_it_cannot_take(dev):
     from liyab_b200 import ops, LiyabError
     a, w = _rand((64, 4104), 1, dev, torch.bfloat16), _rand((16, 4104), 2, dev, torch.bfloat16)
