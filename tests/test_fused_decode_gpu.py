@@ -82,6 +82,42 @@ def test_fused_decode_up_to_sixteen_requests_and_long_contexts(folders):
     assert np.abs(got2[:16] - got).max() <= REL_TOL * np.abs(got).max()
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+@pytest.mark.parametrize("graphs", [False, True])
+def test_decode_steps_of_dozens_of_requests(name, graphs, folders):
+    """Forty requests decode side by side for several steps (too many for the one-kernel step: the products of 17
+    to 64 tokens, the projection that fills the cache from its epilogue and the tensor-core decode attention), with
+    prompts added in groups while others are live; every logit against the plain implementation."""
+    from liyab_b200.engine import StepEntry
+    from liyab_b200.engine.replay import build_replayer
+    raw, seed = CONFIGS[name]
+    V = raw["vocab_size"]
+    _, cache, stepper = build_replayer(folders[name], "bfloat16", max_tokens=42 * 128, max_requests=42)
+    stepper.cuda_graphs = graphs
+    oracle = plain.load_plain_model(folders[name])
+    n_new = 4
+    toks = {f"q{i}": random_tokens(700 + 40 * seed + i, 3 + (i * 7) % 90 + n_new, V) for i in range(40)}
+    names = list(toks)
+    got = {r: [] for r in names}
+    for lo in range(0, 40, 13):                        # prompts in groups of 13, beside nothing else
+        group = names[lo:lo + 13]
+        for r in group:
+            cache.open(r)
+        out = stepper.step([StepEntry(r, toks[r][:-n_new], [len(toks[r]) - n_new - 1]) for r in group])
+        for r, row in zip(group, out.logits.float().cpu().numpy()):
+            got[r].append(row)
+    for k in range(n_new - 1):
+        out = stepper.step([StepEntry(r, [toks[r][len(toks[r]) - n_new + k]], [0]) for r in names])
+        for r, row in zip(names, out.logits.float().cpu().numpy()):
+            got[r].append(row)
+    assert stepper.fused_steps == 0
+    for r in names:
+        ref = plain.forward_logits(oracle, toks[r][:-1])
+        first = len(toks[r]) - n_new - 1
+        for k, row in enumerate(got[r]):
+            assert np.abs(row - ref[first + k]).max() <= REL_TOL * np.abs(ref).max(), (r, k)
+
+
 def test_models_of_other_parts_do_not_take_the_fused_path(tmp_path):
     from liyab_b200.engine.replay import build_replayer
     _, _, stepper = build_replayer(write_model(str(tmp_path), "B", "bfloat16"), "bfloat16", max_tokens=256)
