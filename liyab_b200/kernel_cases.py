@@ -135,7 +135,7 @@ def case_sample(args) -> None:
     from . import ops
     dev = torch.device("cuda:0")
     R, V = args.rows, args.vocab
-    logits = torch.randn(R, V, device=dev) * 3.0
+    logits = torch.randn(R, V, device=dev) * args.spread
     temp = torch.full((R,), args.temp, device=dev)
     top_k = torch.full((R,), args.top_k, dtype=torch.int32, device=dev)
     top_p = torch.full((R,), args.top_p, device=dev)
@@ -236,6 +236,7 @@ def main(argv=None) -> int:
     sm.add_argument("--temp", type=float, default=0.8)
     sm.add_argument("--top-k", type=int, default=40)
     sm.add_argument("--top-p", type=float, default=0.95)
+    sm.add_argument("--spread", type=float, default=3.0, help="standard deviation of the random logits (8: peaked like a model's)")
     sm.add_argument("--reps", type=int, default=400)
     for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)

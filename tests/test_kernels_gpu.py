@@ -224,6 +224,33 @@ def test_sampling_matches_plain(dev, vocab):
             assert got_ids[r] == plain.sampler_draw(got_probs[r], float(u[r])), f"case {r}"
 
 
+@pytest.mark.parametrize("vocab", [300, 50257])
+def test_sampling_top_p_alone_on_peaked_rows(dev, vocab):
+    """Top-p without top-k on rows peaked enough that the few largest logits hold the asked share (the short way)
+    and on one that is not (the general way), with ties at the cut: kept sets, probabilities and draws as the plain
+    sampler's."""
+    from liyab_b200 import ops
+    rng = np.random.default_rng(vocab + 1)
+    cases = [(1.0, 0, 0.9), (0.7, 0, 0.3), (1.0, 0, 0.999), (1.5, 0, 0.95), (1.0, 0, 0.6)]
+    R = len(cases)
+    logits = rng.standard_normal((R, vocab)).astype(np.float32) * 8.0
+    logits[3] *= 0.05                                   # flat: the nucleus holds thousands of ids
+    logits[4, :] = np.round(logits[4, :] / 4.0) * 4.0   # many exact ties, also at the cut
+    u = rng.random(R)
+    out_ids = torch.empty(R, dtype=torch.int32, device=dev)
+    probs = torch.empty((R, vocab), dtype=torch.float32, device=dev)
+    ops.sample(torch.from_numpy(logits).to(dev), R, torch.tensor([c[0] for c in cases], dtype=torch.float32, device=dev),
+               torch.tensor([c[1] for c in cases], dtype=torch.int32, device=dev),
+               torch.tensor([c[2] for c in cases], dtype=torch.float32, device=dev),
+               torch.from_numpy(u).to(dev), out_ids, probs)
+    got_ids, got_probs = out_ids.cpu().numpy(), probs.cpu().numpy()
+    for r, (t, k, p) in enumerate(cases):
+        ref = plain.sampler_probabilities(logits[r], t, k, p)
+        assert np.array_equal(ref > 0, got_probs[r] > 0), f"case {r}: kept sets differ ({(ref > 0).sum()} vs {(got_probs[r] > 0).sum()})"
+        assert np.abs(ref - got_probs[r]).max() < 2e-6, f"case {r}"
+        assert got_ids[r] == plain.sampler_draw(got_probs[r], float(u[r])), f"case {r}"
+
+
 def test_greedy_takes_the_first_maximum(dev):
     from liyab_b200 import ops
     logits = torch.zeros((2, 3000), dtype=torch.float32, device=dev)
