@@ -108,7 +108,7 @@ int lb_decode_attention(const void* q, int64_t q_stride, const void* cache, cons
 int lb_decode_attention_supports(int n_head, int n_kv_head, int head_dim, int page_size);
 /* The same with scores and weighted values on the tensor cores (head_dim 64 or 128, up to 16 query heads per
  * key/value head, pages of 16 positions or more); same arguments, scratch and split semantics. */
-int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
+int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
                             const int32_t* block_table, int table_stride, void* out, int64_t out_stride, float* partial,
                             int* counters, int n_seq, int n_head, int n_kv_head, int head_dim, int page_size, float scale,
                             int window, int n_splits, void* stream);

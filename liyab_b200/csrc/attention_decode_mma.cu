@@ -25,6 +25,7 @@
 // Reference formulas: src/core/transformer.cpp:2303-2313, 2327-2341, 2344-2358, 2367-2385.
 #include "api.h"
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 #include <math_constants.h>
 
@@ -62,9 +63,12 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int HD, int kWarps, int kStages>
+// TMA: the tiles come as tensor-map boxes of 16 keys (head size 64: a row is the 128 bytes of the swizzle) instead
+// of 16-byte cp.async pieces: two instructions per tile from one lane, completion on a per-warp mbarrier.
+template <int HD, int kWarps, int kStages, bool TMA>
 __global__ void __launch_bounds__(kWarps * 32)
-decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache,
+decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_rows, int* status,
+                            const __nv_bfloat16* __restrict__ q, int64_t q_stride, const __nv_bfloat16* __restrict__ cache,
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                             __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
                             int* __restrict__ counters, int n_head, int n_kv_head, int page_shift, float scale, int window,
@@ -77,10 +81,13 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
     constexpr int STATE = HD + 2;               // m, l, values of one query head
     // Dynamic shared memory: the warps' tile buffers [warp][stage][K|V][16 x LD]; once the key loop is over the
     // same bytes hold the warps' states per query row, red[warp][row][STATE].
-    extern __shared__ __align__(16) uint8_t smem_bytes[];
+    extern __shared__ __align__(16) uint8_t smem_raw[];
+    // TMA's swizzle counts rows from 1024-byte boundaries.
+    uint8_t* smem_bytes = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023) : smem_raw;
     __nv_bfloat16* tiles = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
     float* red = reinterpret_cast<float*>(smem_bytes);
     __shared__ int is_last;
+    __shared__ uint64_t bars[kWarps][kStages];
 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
@@ -126,6 +133,18 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
         const __nv_bfloat16* src = cache + (size_t)page * 2 * plane + ((size_t)kvh * page_size + (j0 & (page_size - 1))) * HD;
         __nv_bfloat16* kd = tiles + (size_t)((warp * kStages + stage) * 2) * kTile * LD;
         __nv_bfloat16* vd = kd + kTile * LD;
+        if constexpr (TMA) {
+            // Rows of the cache as the tensor map counts them: ((page * 2 + K|V) * kv_heads + head) * page_size + slot.
+            if (lane == 0) {
+                const int row_k = ((page * 2) * n_kv_head + kvh) * page_size + (j0 & (page_size - 1));
+                const int row_v = row_k + n_kv_head * page_size;
+                lb_tc::fence_async_shared();              // the lanes' reads of the stage (ordered before by __syncwarp)
+                lb_tc::mbar_expect_tx(&bars[warp][stage], 2 * kTile * HD * sizeof(__nv_bfloat16));
+                lb_tc::tma_load_2d(kd, &map_kv, &bars[warp][stage], 0, row_k);
+                lb_tc::tma_load_2d(vd, &map_kv, &bars[warp][stage], 0, row_v);
+            }
+            return;
+        }
 #pragma unroll
         for (int c = lane; c < kTile * CH; c += 32) {
             const int r = c / CH, ch = c - r * CH;
@@ -142,6 +161,14 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
     float m_lo = -CUDART_INF_F, m_hi = -CUDART_INF_F, l_lo = 0.0f, l_hi = 0.0f;
     const float sc = scale * kLog2e;
 
+    if constexpr (TMA) {
+        if (lane == 0) {
+            for (int i = 0; i < kStages; ++i) lb_tc::mbar_init(&bars[warp][i], 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        __syncwarp();
+    }
+    int gave_up_at = -1;
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {          // kStages - 1 tiles ahead; a group per tile, empty past the end
         if (i < my_tiles) load_tile(i, i);
@@ -150,8 +177,28 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
     for (int i = 0; i < my_tiles; ++i) {
         const int stage = i % kStages;
         if (i + kStages - 1 < my_tiles) load_tile(i + kStages - 1, (i + kStages - 1) % kStages);
-        cp_async_commit();
-        cp_async_wait<kStages - 1>();
+        if constexpr (TMA) {
+            // Bounded; one answer for the warp.  A wait that ran out ends the warp's walk (its result is then wrong
+            // and the status word says so).
+            if (!__all_sync(0xffffffffu, lb_tc::mbar_wait(&bars[warp][stage], (uint32_t)(i / kStages) & 1u, nullptr))) {
+                if (lane == 0) atomicCAS(status, 0, (0xD << 12) | 1);
+                gave_up_at = i;
+                break;
+            }
+            // Rows outside the range came with the box: values there (whatever the page holds, also NaN) would
+            // meet a zero weight.  Zeroed here, in the tiles of the range's two ends only.
+            const int j0z = (tile0 + warp + kWarps * i) * kTile;
+            if (j0z < begin || j0z + kTile > end) {
+                __nv_bfloat16* vz = tiles + (size_t)((warp * kStages + stage) * 2) * kTile * LD + kTile * LD;
+                for (int c = lane; c < kTile * CH; c += 32) {
+                    const int r = c / CH;
+                    if (j0z + r < begin || j0z + r >= end) *reinterpret_cast<uint4*>(vz + r * LD + (c - r * CH) * 8) = make_uint4(0, 0, 0, 0);
+                }
+            }
+        } else {
+            cp_async_commit();
+            cp_async_wait<kStages - 1>();
+        }
         __syncwarp();
         const __nv_bfloat16* kt = tiles + (size_t)((warp * kStages + stage) * 2) * kTile * LD;
         const __nv_bfloat16* vt = kt + kTile * LD;
@@ -211,6 +258,12 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
         __syncwarp();        // the stage is overwritten by the load issued in the next trip
     }
     cp_async_wait<0>();
+    if constexpr (TMA) {
+        // After a wait that ran out the copies still in flight land before the block may leave (bounded as well).
+        if (gave_up_at >= 0)
+            for (int t2 = gave_up_at; t2 < my_tiles && t2 < gave_up_at + kStages; ++t2)
+                lb_tc::mbar_wait(&bars[warp][t2 % kStages], (uint32_t)(t2 / kStages) & 1u, nullptr);
+    }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
@@ -282,19 +335,19 @@ decode_attention_mma_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_strid
 }
 
 // Shared memory of one block and how many blocks of an instantiation one SM holds (asked once).
-template <int HD, int kWarps, int kStages>
+template <int HD, int kWarps, int kStages, bool TMA>
 struct Variant {
     static constexpr size_t tile_bytes = (size_t)kWarps * kStages * 2 * kTile * HD * sizeof(__nv_bfloat16);
     static constexpr size_t red_bytes = (size_t)kWarps * 16 * (HD + 2) * sizeof(float);
-    static constexpr size_t smem = tile_bytes > red_bytes ? tile_bytes : red_bytes;
+    static constexpr size_t smem = (tile_bytes > red_bytes ? tile_bytes : red_bytes) + (TMA ? 1024 : 0);
 
     static int blocks_per_sm(int* out) {
         static int cached = 0;
         if (cached == 0) {
-            LB_CHECK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel<HD, kWarps, kStages>,
+            LB_CHECK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel<HD, kWarps, kStages, TMA>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             int n = 0;
-            LB_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_mma_kernel<HD, kWarps, kStages>,
+            LB_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_mma_kernel<HD, kWarps, kStages, TMA>,
                                                                         kWarps * 32, smem));
             cached = n > 0 ? n : 1;
         }
@@ -302,12 +355,12 @@ struct Variant {
         return LB_OK;
     }
 
-    static int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+    static int launch(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                       int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
                       int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
         dim3 grid(n_splits, n_kv_head, n_seq);
-        decode_attention_mma_kernel<HD, kWarps, kStages><<<grid, kWarps * 32, smem, s>>>(
-            (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
+        decode_attention_mma_kernel<HD, kWarps, kStages, TMA><<<grid, kWarps * 32, smem, s>>>(
+            map_kv, kv_rows, status, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
             (__nv_bfloat16*)out, out_stride, partial, counters, n_head, n_kv_head, page_shift, scale, window, n_splits);
         LB_CHECK_LAUNCH();
         return LB_OK;
@@ -318,12 +371,12 @@ struct Variant {
 // fewer blocks, so a count a little above one wave of them leaves a second wave nearly empty; two-warp blocks
 // then fit in one).  A choice by the launch's shape only; it changes the order in which tiles are merged, which
 // is rounding.
-template <int HD>
-int launch_for(const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
+template <int HD, bool TMA>
+int launch_for(const CUtensorMap& map_kv, int kv_rows, int* status, const void* q, int64_t q_stride, const void* cache, const int32_t* positions, const int32_t* block_table,
                int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
                int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
-    using Wide = Variant<HD, 4, 2>;
-    using Narrow = Variant<HD, 2, 2>;
+    using Wide = Variant<HD, 4, 2, TMA>;
+    using Narrow = Variant<HD, 2, 2, TMA>;
     static int n_sm = 0;
     if (n_sm == 0) {
         int dev = 0;
@@ -339,9 +392,9 @@ int launch_for(const void* q, int64_t q_stride, const void* cache, const int32_t
     // fill = blocks / (waves * slots); compared without division
     const bool narrow = blocks > slots_wide && waves_wide * slots_wide >= waves_narrow * slots_narrow;
     if (narrow)
-        return Narrow::launch(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
+        return Narrow::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
                               n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
-    return Wide::launch(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq,
+    return Wide::launch(map_kv, kv_rows, status, q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters, n_seq,
                         n_head, n_kv_head, page_shift, scale, window, n_splits, s);
 }
 
@@ -355,7 +408,9 @@ extern "C" int lb_decode_attention_mma_supports(int n_head, int n_kv_head, int h
     return (head_dim == 64 || head_dim == 128) && g >= 1 && g <= 16 && page_size >= 16 && (page_size & (page_size - 1)) == 0;
 }
 
-extern "C" int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, const int32_t* positions,
+// n_pages: the pages of the cache (its first extent).  With head size 64 and a cache that a tensor map can
+// describe, the tiles come through TMA; with n_pages 0, or otherwise, through cp.async.
+extern "C" int lb_decode_attention_mma(const void* q, int64_t q_stride, const void* cache, int n_pages, const int32_t* positions,
                                        const int32_t* block_table, int table_stride, void* out, int64_t out_stride,
                                        float* partial, int* counters, int n_seq, int n_head, int n_kv_head, int head_dim,
                                        int page_size, float scale, int window, int n_splits, void* stream) {
@@ -370,9 +425,23 @@ extern "C" int lb_decode_attention_mma(const void* q, int64_t q_stride, const vo
     int page_shift = 0;
     while ((1 << page_shift) < page_size) ++page_shift;
     auto s = static_cast<cudaStream_t>(stream);
-if (head_dim == 64)
-        return launch_for<64>(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
-                              n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
-    return launch_for<128>(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, partial, counters,
-                           n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+    CUtensorMap none;
+    memset(&none, 0, sizeof(none));
+    if (head_dim == 64) {
+        const int64_t kv_rows = (int64_t)n_pages * 2 * n_kv_head * page_size;
+        if (n_pages > 0 && kv_rows < (int64_t)1 << 31 && ((uintptr_t)cache & 15) == 0) {
+            CUtensorMap map_kv;
+            int* status = nullptr;
+            int rc = lb_tensor_map_2d(&map_kv, cache, 2, (int)kv_rows, 64, 64, kTile);
+            if (rc == LB_OK) rc = lb_tc_status_word(&status);
+            if (rc != LB_OK) return rc;
+            return launch_for<64, true>(map_kv, (int)kv_rows, status, q, q_stride, cache, positions, block_table, table_stride,
+                                        out, out_stride, partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window,
+                                        n_splits, s);
+        }
+        return launch_for<64, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
+                                     partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
+    }
+    return launch_for<128, false>(none, 0, nullptr, q, q_stride, cache, positions, block_table, table_stride, out, out_stride,
+                                  partial, counters, n_seq, n_head, n_kv_head, page_shift, scale, window, n_splits, s);
 }

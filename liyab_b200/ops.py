@@ -39,7 +39,7 @@ _SIGNATURES = {
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
-    "lb_decode_attention_mma": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
+    "lb_decode_attention_mma": [_p, _l, _p, _i, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_mma_supports": [_i, _i, _i, _i],
     "lb_prefill_attention": [_p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_prefill_attention_supports": [_i, _i, _i, _i],
@@ -358,9 +358,10 @@ def decode_attention(q: torch.Tensor, cache: torch.Tensor, positions: torch.Tens
             raise invalid_argument("decode attention: scratch buffers are missing or too small")
     if tensor_cores is None:
         tensor_cores = decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)[1]
+    cache_args = (_dev(cache, "cache"), cache.shape[0]) if tensor_cores else (_dev(cache, "cache"),)
     fn = lib().lb_decode_attention_mma if tensor_cores else lib().lb_decode_attention
     check(fn(
-        _dev(q, "q"), q.stride(0), _dev(cache, "cache"), _dev(positions, "positions", torch.int32),
+        _dev(q, "q"), q.stride(0), *cache_args, _dev(positions, "positions", torch.int32),
         _dev(block_table, "block_table", torch.int32), block_table.stride(0), _dev(out, "out"), out.stride(0),
         _opt(partial, "partial", torch.float32), _opt(counters, "counters", torch.int32), n_seq, n_head, n_kv_head,
         head_dim, page_size, float(scale), int(window), int(n_splits), stream_ptr()), "decode_attention")
