@@ -1,6 +1,7 @@
 """Each part alone against the plain functions, and the framework's generality: a toy mixer with
 state of its own, defined here, is registered, built into a model beside attention layers (one layer
-run twice, one run reading another run's cache) and stepped, without a change to the framework."""
+run twice, one run reading another run's cache) and stepped, without a change to the framework; and so are
+a feed-forward with routing, a position encoding without a table, a norm and an arrangement of a block."""
 from __future__ import annotations
 
 import math
@@ -234,3 +235,148 @@ def test_windowed_layers_get_pages_of_their_own_and_give_them_back():
     # 200 positions need 13 pages of 16; the windowed group never held more than a window and a portion's worth
     gw = cache.groups[cache.group_of_unit[1]]
     assert gw.need.window == 20 and gw.pool.num_pages == 14
+
+
+def register_toy_parts():
+    """A feed-forward with routing, a position encoding without a table, a norm without a mean and a
+    block that runs its two parts side by side: each defined here, in plain torch, on the parts' interfaces."""
+    from liyab_b200 import ops
+    from liyab_b200.parts import ARRANGEMENTS, FEED_FORWARDS, NORMS, POSITIONS
+
+    @FEED_FORWARDS.register("toy_routed")
+    class RoutedFeedForward:
+        """Every token goes to its best `top` experts of `experts` small ungated ones; router in 32-bit."""
+        def __init__(self, spec, params, runtime):
+            self.spec, self.p = spec, params
+
+        @classmethod
+        def parameters(cls, spec):
+            E, I, H = spec.options["experts"], spec.options["inner"], spec.hidden
+            return {"router": ((E, H), "matrix"), "up": ((E * I, H), "matrix"), "down": ((E * H, I), "matrix")}
+
+        def forward(self, ctx, h, x):
+            E, I, H, top = self.spec.options["experts"], self.spec.options["inner"], self.spec.hidden, self.spec.options["top"]
+            hf = h[:ctx.n_tokens].float()
+            gate = torch.softmax(hf @ self.p["router"].float().t(), dim=-1)
+            weight, chosen = torch.topk(gate, top, dim=-1)
+            weight = weight / weight.sum(-1, keepdim=True)
+            up, down = self.p["up"].float().view(E, I, H), self.p["down"].float().view(E, H, I)
+            for e in range(E):
+                share = (weight * (chosen == e)).sum(-1)
+                rows = torch.nonzero(share > 0).flatten()
+                if rows.numel():
+                    y = torch.relu(hf[rows] @ up[e].t()) @ down[e].t()
+                    x[rows] += share[rows, None] * y
+
+    @POSITIONS.register("toy_sinusoid")
+    class SinusoidPosition:
+        """sin / cos of the position at geometric frequencies, added to the embedding; nothing learned."""
+        def __init__(self, spec, params, runtime):
+            self.spec = spec
+
+        @classmethod
+        def parameters(cls, spec):
+            return {}
+
+        @property
+        def max_positions(self):
+            return 1 << 20
+
+        def embed(self, ctx, table, scale, x):
+            ops.embed_positions(ctx.tokens, ctx.positions, table, None, x, scale)
+            H = self.spec.hidden
+            freq = self.spec.options["base"] ** (-torch.arange(0, H, 2, device=x.device, dtype=torch.float32) / H)
+            angle = ctx.positions[:ctx.n_tokens].float()[:, None] * freq
+            x[:ctx.n_tokens, 0::2] += torch.sin(angle)
+            x[:ctx.n_tokens, 1::2] += torch.cos(angle)
+            return x
+
+    @NORMS.register("toy_rms")
+    class RmsNorm:
+        def __init__(self, spec, params, runtime):
+            self.spec, self.weight = spec, params["weight"]
+
+        @classmethod
+        def parameters(cls, spec):
+            return {"weight": ((spec.hidden,), "vector")}
+
+        def forward(self, ctx, x, out, n_rows, rows=None):
+            v = x[:n_rows] if rows is None else x[rows[:n_rows].long()]
+            v = v.float()
+            y = v * torch.rsqrt((v * v).mean(-1, keepdim=True) + self.spec.options["eps"]) * self.weight.float()
+            out[:n_rows] = y.to(out.dtype)
+            return out
+
+    @ARRANGEMENTS.register("toy_side_by_side")
+    class SideBySideBlock:
+        """x += mixer(norm(x)) + feed_forward(norm(x)): both parts read the same normalised input."""
+        def __init__(self, spec, parts, runtime):
+            self.spec, self.parts, self.runtime = spec, parts, runtime
+
+        def forward(self, ctx, x, unit):
+            h = ctx.workspace.get("block.normed", ctx.n_tokens, x.shape[1], self.runtime.dtype)
+            self.parts.mixer_norm.forward(ctx, x, h, ctx.n_tokens)
+            self.parts.mixer.forward(ctx, h, x, unit)
+            self.parts.feed_forward.forward(ctx, h, x)
+
+
+def toy_parts_spec():
+    from liyab_b200.config import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, GenericSpec, HeadSpec, LayerSpec,
+                                   ModelSpec, NormSpec, RunEntry)
+    H, V = 40, 33
+    ln = NormSpec(kind="layernorm", size=H, eps=1e-5)
+    rms = GenericSpec(kind="toy_rms", hidden=H, options={"eps": 1e-3})
+    attn = AttentionSpec(kind="attention", hidden=H, n_head=5, n_kv_head=5, head_dim=8, scale=0.3)
+    routed = GenericSpec(kind="toy_routed", hidden=H, options={"experts": 3, "inner": 24, "top": 2})
+    first = LayerSpec("pre_norm", rms, attn, ln, routed)
+    second = LayerSpec("toy_side_by_side", rms, attn, rms,
+                       DenseFeedForwardSpec(kind="dense", hidden=H, inner=56, activation="gelu_tanh"))
+    return ModelSpec("toy", EmbeddingSpec(V, H), GenericSpec(kind="toy_sinusoid", hidden=H, options={"base": 50.0}),
+                     (first, second), (RunEntry(0, 0), RunEntry(1, 1)), rms, HeadSpec(V, H, tied=False), 128)
+
+
+def plain_toy_parts_logits(p, tokens):
+    H = 40
+    x = plain.embed(tokens, _np(p["embedding.weight"]))
+    freq = 50.0 ** (-np.arange(0, H, 2) / H)
+    angle = np.arange(len(tokens))[:, None] * freq
+    x[:, 0::2] += np.sin(angle)
+    x[:, 1::2] += np.cos(angle)
+
+    def rms(v, name):
+        return v / np.sqrt((v * v).mean(-1, keepdims=True) + 1e-3) * _np(p[name + ".weight"])
+
+    x = x + plain_attention_part(rms(x, "layers.0.mixer_norm"), p, "layers.0.mixer.", 5, 5, 0.3)
+    h = plain.layernorm(x, _np(p["layers.0.ff_norm.weight"]), _np(p["layers.0.ff_norm.bias"]), 1e-5)
+    logits = h @ _np(p["layers.0.feed_forward.router"]).T
+    gate = np.exp(logits - logits.max(-1, keepdims=True))
+    gate /= gate.sum(-1, keepdims=True)
+    up = _np(p["layers.0.feed_forward.up"]).reshape(3, 24, H)
+    down = _np(p["layers.0.feed_forward.down"]).reshape(3, H, 24)
+    y = np.zeros_like(x)
+    for t in range(len(tokens)):
+        best = np.argsort(-gate[t], kind="stable")[:2]
+        for e in best:
+            y[t] += gate[t, e] / gate[t, best].sum() * (np.maximum(h[t] @ up[e].T, 0.0) @ down[e].T)
+    x = x + y
+    h = rms(x, "layers.1.mixer_norm")
+    x = x + plain_attention_part(h, p, "layers.1.mixer.", 5, 5, 0.3) + plain_ff_part(h, p, "layers.1.feed_forward.", "gelu_tanh")
+    return rms(x, "final_norm") @ _np(p["head.weight"]).T
+
+
+def test_toy_feed_forward_with_routing_position_norm_and_arrangement():
+    """Parts of every other role, defined in this file, are registered, built beside the framework's own
+    (attention over pages, the dense feed-forward, LayerNorm) and stepped in every cutting."""
+    import trace_tools as tt
+    register_toy_parts()
+    model, p, cache, stepper = build(toy_parts_spec(), seed=9, num_pages=24)
+    assert sorted(model.kv_needs()) == [0, 1] and not model.state_needs()
+    rng = np.random.default_rng(4)
+    reqs = {f"t{i}": rng.integers(0, 33, size=n).tolist() for i, n in enumerate((41, 6, 90, 17))}
+    want = {r: plain_toy_parts_logits(p, toks) for r, toks in reqs.items()}
+    for steps in (tt.whole(reqs), tt.changing_portions(reqs), tt.mixed(reqs, max_live=3, seed=3)):
+        got = tt.collect(stepper, cache, steps)
+        assert len(got) == sum(len(t) for t in reqs.values())
+        for (r, pos), row in got.items():
+            assert np.abs(row - want[r][pos]).max() < 5e-5 * max(1.0, np.abs(want[r]).max()), (r, pos)
+    assert all(v == 0 for v in cache.pages_in_use().values())
