@@ -23,6 +23,9 @@ import torch
 
 GPT2_SMALL = dict(model_type="gpt2", n_layer=12, n_embd=768, n_head=12, n_inner=3072, vocab_size=50257,
                   n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+GPT2_SIZES = {"small": GPT2_SMALL,
+              "medium": dict(GPT2_SMALL, n_layer=24, n_embd=1024, n_head=16, n_inner=4096),
+              "xl": dict(GPT2_SMALL, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)}
 
 
 def _timed(fn, reps: int, warmup: int = 2) -> float:
@@ -146,18 +149,18 @@ def case_sample(args) -> None:
           f"(20 launches per CUDA graph)")
 
 
-def _model_folder(layers: int, dtype: str) -> str:
+def _model_folder(layers: int, dtype: str, size: str = "small") -> str:
     from .config import parse_config
     from .weights import write_random_model
     tmp = tempfile.mkdtemp(prefix="liyab_b200_case_")
-    return write_random_model(os.path.join(tmp, "m"), parse_config(dict(GPT2_SMALL, n_layer=layers)), 0, dtype)
+    return write_random_model(os.path.join(tmp, "m"), parse_config(dict(GPT2_SIZES[size], n_layer=layers or GPT2_SIZES[size]["n_layer"])), 0, dtype)
 
 
 def case_decode_step(args) -> None:
     from .engine import StepEntry
     from .engine.replay import build_replayer
     B = args.batch
-    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype), args.dtype, max_tokens=B * 1024,
+    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=B * 1024,
                                            max_requests=B)
     stepper.cuda_graphs = not args.eager
     stepper.workspace.reserve_rows(max(1024, B))
@@ -176,28 +179,30 @@ def case_decode_step(args) -> None:
         stepper.step([StepEntry(r, [1], [0]) for r in ids])
 
     ms = _timed(one, args.reps, warmup=3)
-    print(f"decode-step batch={B} layers={args.layers} context~{args.context} graphs={not args.eager}: "
+    print(f"decode-step size={args.size} batch={B} layers={len(model.spec.layers)} context~{args.context} graphs={not args.eager}: "
           f"{ms * 1e3:.1f} us per step, {B / ms * 1e3:.0f} tokens/s")
 
 
 def case_prefill_step(args) -> None:
     from .engine import StepEntry
     from .engine.replay import build_replayer
-    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype), args.dtype, max_tokens=2 * args.tokens)
+    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=2 * args.tokens)
     V = model.spec.vocab_size
     rng = np.random.default_rng(0)
     n_seq = max(1, args.tokens // 1024)
     per = args.tokens // n_seq
 
+    prompts = [rng.integers(0, V, size=per).tolist() for _ in range(n_seq)]
+
     def one():
         for i in range(n_seq):
             cache.open(f"p{i}")
-        stepper.step([StepEntry(f"p{i}", rng.integers(0, V, size=per).tolist(), [per - 1]) for i in range(n_seq)])
+        stepper.step([StepEntry(f"p{i}", prompts[i], [per - 1]) for i in range(n_seq)])
         for i in range(n_seq):
             cache.close(f"p{i}")
 
     ms = _timed(one, args.reps, warmup=2)
-    print(f"prefill-step tokens={n_seq}x{per} layers={args.layers}: {ms:.3f} ms per step, {n_seq * per / ms * 1e3:.0f} tokens/s")
+    print(f"prefill-step size={args.size} tokens={n_seq}x{per} layers={len(model.spec.layers)}: {ms:.3f} ms per step, {n_seq * per / ms * 1e3:.0f} tokens/s")
 
 
 def main(argv=None) -> int:
@@ -243,7 +248,8 @@ def main(argv=None) -> int:
         p.add_argument("--batch", type=int, default=8)
         p.add_argument("--tokens", type=int, default=2048)
         p.add_argument("--context", type=int, default=512)
-        p.add_argument("--layers", type=int, default=12)
+        p.add_argument("--layers", type=int, default=0, help="fewer layers than the size has (0: all)")
+        p.add_argument("--size", default="small", choices=sorted(GPT2_SIZES))
         p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true")
