@@ -78,9 +78,15 @@ int lb_gemm_persistent_tile(int out_dtype, const void* A, int64_t lda, const voi
 /* Profiling aid: from now on every launch writes eight time stamps per block (nanoseconds) to `buffer` (device
  * memory, 8 * number of SMs 64-bit words); null switches it off. */
 int lb_gemm_persistent_timing(unsigned long long* buffer);
+/* With kv_cache (else null and zeros): the product is a fused query/key/value projection whose features from
+ * q_dim on go to the pages of the cache (token i at slot_mapping[i]; negative: nowhere) instead of `out`;
+ * lb_gemm_persistent_kv_supports says for which shapes. */
 int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                        const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
-                       int feature_tile, void* stream);
+                       int feature_tile, void* kv_cache, const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim,
+                       int page_size, void* stream);
+int lb_gemm_persistent_kv_supports(int out_dtype, int N, int act, int has_residual, int q_dim, int n_kv_head, int head_dim,
+                                   int page_size);
 /* Reads and clears the status word that a bounded wait sets when it runs out
  * (0: none did).  Synchronises the device. */
 int lb_gemm_tcgen05_status(int* status);

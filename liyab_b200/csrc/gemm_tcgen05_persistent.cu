@@ -162,12 +162,21 @@ __device__ __forceinline__ float activate(float x) {
     }
 }
 
-template <typename TO, int ACT, bool HAS_RES>
+// Where the features from q_dim on go instead of `out` when the product is a fused query/key/value projection:
+// the pages of the cache ([page][K|V][kv_head][slot][head_dim]), row (token) i at slot_mapping[i] (negative: nowhere).
+// A 64-feature strip lies inside one head (head_dim and q_dim are multiples of 64): 128 contiguous bytes per token.
+struct KvTarget {
+    __nv_bfloat16* cache;
+    const int32_t* slot_mapping;
+    int q_dim, n_kv_head, head_dim, page_shift;
+};
+
+template <typename TO, int ACT, bool HAS_RES, bool KV>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_res, const __grid_constant__ CUtensorMap map_out,
                        const float* __restrict__ bias, int M, int N, int K, int BN, int n_stages, int* status,
-                       unsigned long long* timing) {
+                       unsigned long long* timing, const KvTarget kv) {
     if (threadIdx.x == 0) stamp(timing, 0);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -335,9 +344,26 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             tc_fence_after();
             if (et == 0 && it == 0) stamp(timing, 4);
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride;
+            int slot = -1;                                             // where this thread's token lies in the cache
+            if constexpr (KV) slot = m0 + row < M ? __ldg(kv.slot_mapping + m0 + row) : -1;
             for (int sp = group; sp < n_strips; sp += 2) {
                 const uint32_t strip = row_u32 + (uint32_t)sp * kStripBytes;
                 const uint32_t b = bias_u32 + (uint32_t)(sp * kStripCols) * 4u;
+                // A strip of keys or values goes straight from the registers to its page, a strip of queries to `out`.
+                bool to_cache = false;
+                uint4* cache_row = nullptr;
+                if constexpr (KV) {
+                    const int col0 = n0 + sp * kStripCols;
+                    to_cache = col0 >= kv.q_dim;
+                    if (to_cache && slot >= 0 && col0 < N) {
+                        const int kvd = kv.n_kv_head * kv.head_dim, rel = col0 - kv.q_dim;
+                        const int which = rel >= kvd ? 1 : 0, within = rel - which * kvd;
+                        const int head = within / kv.head_dim, dd = within - head * kv.head_dim;
+                        const int page = slot >> kv.page_shift, off = slot & ((1 << kv.page_shift) - 1);
+                        const size_t at = ((((size_t)page * 2 + which) * kv.n_kv_head + head) << kv.page_shift) + off;
+                        cache_row = reinterpret_cast<uint4*>(kv.cache + at * kv.head_dim + dd);
+                    }
+                }
                 if constexpr (sizeof(TO) == 4) {
                     uint32_t v[32];
                     tmem_ld32(t_row + (uint32_t)(sp * 32), v);
@@ -372,7 +398,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                             y.y = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 2]) + b0.z), activate<ACT, true>(__uint_as_float(v[8 * q + 3]) + b0.w));
                             y.z = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 4]) + b1.x), activate<ACT, true>(__uint_as_float(v[8 * q + 5]) + b1.y));
                             y.w = pack2(activate<ACT, true>(__uint_as_float(v[8 * q + 6]) + b1.z), activate<ACT, true>(__uint_as_float(v[8 * q + 7]) + b1.w));
-                            sts4(strip + (((uint32_t)ch ^ swz) << 4), y);
+                            if (KV && to_cache) {
+                                if (cache_row != nullptr) cache_row[ch] = y;
+                            } else {
+                                sts4(strip + (((uint32_t)ch ^ swz) << 4), y);
+                            }
                         }
                     }
                 }
@@ -380,7 +410,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 fence_async_shared();
                 named_barrier(2 + group, 128);
                 if (elected) {
-                    if (n0 + sp * kStripCols < N) tma_store_2d(&map_out, staging + (size_t)sp * kStripBytes, n0 + sp * kStripCols, m0);
+                    if (!to_cache && n0 + sp * kStripCols < N)
+                        tma_store_2d(&map_out, staging + (size_t)sp * kStripBytes, n0 + sp * kStripCols, m0);
                     bulk_commit();
                 }
             }
@@ -460,6 +491,14 @@ extern "C" int lb_gemm_persistent_tile(int out_dtype, const void* A, int64_t lda
     return best;
 }
 
+// Whether lb_gemm_persistent can send the features from q_dim on to the pages of a cache instead of `out`.
+extern "C" int lb_gemm_persistent_kv_supports(int out_dtype, int N, int act, int has_residual, int q_dim, int n_kv_head,
+                                              int head_dim, int page_size) {
+    return out_dtype == LB_BF16 && act == LB_ACT_NONE && !has_residual && q_dim > 0 && q_dim % 64 == 0 && head_dim > 0 &&
+           head_dim % 64 == 0 && n_kv_head > 0 && N == q_dim + 2 * n_kv_head * head_dim && page_size > 0 &&
+           (page_size & (page_size - 1)) == 0;
+}
+
 // Profiling aid: eight time stamps per block go to `buffer` (device memory, 8 * 148 64-bit words) on every launch
 // from now on; null switches them off again.
 extern "C" int lb_gemm_persistent_timing(unsigned long long* buffer) {
@@ -469,8 +508,19 @@ extern "C" int lb_gemm_persistent_timing(unsigned long long* buffer) {
 
 extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                                   const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
-                                  int feature_tile, void* stream) {
+                                  int feature_tile, void* kv_cache, const int32_t* slot_mapping, int q_dim, int n_kv_head,
+                                  int head_dim, int page_size, void* stream) {
     LB_CHECK_ARG(M > 0 && N > 0 && K > 0, "gemm_persistent: bad sizes M=%d N=%d K=%d", M, N, K);
+    KvTarget kv{static_cast<__nv_bfloat16*>(kv_cache), slot_mapping, q_dim, n_kv_head, head_dim, 0};
+    if (kv_cache != nullptr) {
+        if (!lb_gemm_persistent_kv_supports(out_dtype, N, act, residual != nullptr, q_dim, n_kv_head, head_dim, page_size))
+            return lb_fail(LB_ERR_UNSUPPORTED,
+                           "gemm_persistent: keys and values go to the cache only from a bfloat16 product without activation "
+                           "or residual, with q_dim and head_dim multiples of 64 and a power-of-two page (N=%d q_dim=%d "
+                           "kv_heads=%d head_dim=%d page_size=%d)", N, q_dim, n_kv_head, head_dim, page_size);
+        LB_CHECK_ARG(slot_mapping != nullptr, "gemm_persistent: the slot mapping is missing");
+        while ((1 << kv.page_shift) < page_size) ++kv.page_shift;
+    }
     LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_persistent: unknown output dtype %d", out_dtype);
     LB_CHECK_ARG(lda >= K && ldw >= K && ldo >= N, "gemm_persistent: a row stride is shorter than the row");
     const int elem = out_dtype == LB_F32 ? 4 : 2;
@@ -507,17 +557,18 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
     size_t smem = smem_bytes(bn, n_stages, elem);
     if (smem < 120 * 1024) smem = 120 * 1024;
     auto s = static_cast<cudaStream_t>(stream);
-#define LB_GO(TO, ACT, RES)                                                                                              \
+#define LB_GO_KV(TO, ACT, RES, KV)                                                                                       \
     {                                                                                                                    \
         static bool configured = false;                                                                                  \
         if (!configured) {                                                                                               \
-            LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<TO, ACT, RES>,                                     \
+            LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<TO, ACT, RES, KV>,                                 \
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));           \
             configured = true;                                                                                           \
         }                                                                                                                \
-        gemm_persistent_kernel<TO, ACT, RES><<<grid, kThreads, smem, s>>>(map_a, map_w, map_res, map_out, bias, M, N, K, bn, \
-                                                                          n_stages, status, g_timing);                   \
+        gemm_persistent_kernel<TO, ACT, RES, KV><<<grid, kThreads, smem, s>>>(map_a, map_w, map_res, map_out, bias, M, N, K, \
+                                                                              bn, n_stages, status, g_timing, kv);       \
     }
+#define LB_GO(TO, ACT, RES) LB_GO_KV(TO, ACT, RES, false)
 #define LB_GO_ACT(TO, RES)                                                  \
     switch (act) {                                                          \
         case LB_ACT_NONE: LB_GO(TO, LB_ACT_NONE, RES); break;               \
@@ -527,11 +578,14 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
     }
     if (elem == 4) {
         if (residual != nullptr) LB_GO_ACT(float, true) else LB_GO_ACT(float, false)
+    } else if (kv_cache != nullptr) {
+        LB_GO_KV(__nv_bfloat16, LB_ACT_NONE, false, true)
     } else {
         LB_GO_ACT(__nv_bfloat16, false)
     }
 #undef LB_GO_ACT
 #undef LB_GO
+#undef LB_GO_KV
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

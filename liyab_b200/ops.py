@@ -35,7 +35,8 @@ _SIGNATURES = {
     "lb_gemm_rows": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_persistent_tile": [_i, _p, _l, _p, _l, _p, _l, _p, _l, _i, _i, _i],
     "lb_gemm_persistent_timing": [_p],
-    "lb_gemm_persistent": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p],
+    "lb_gemm_persistent": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _i, _i, _i, _p],
+    "lb_gemm_persistent_kv_supports": [_i, _i, _i, _i, _i, _i, _i, _i],
     "lb_paged_attention_generic": [_i, _p, _l, _p, _p, _p, _p, _i, _p, _l, _i, _i, _i, _i, _i, _f, _i, _p],
     "lb_decode_attention": [_p, _l, _p, _p, _p, _i, _p, _l, _p, _p, _i, _i, _i, _i, _i, _f, _i, _i, _p],
     "lb_decode_attention_supports": [_i, _i, _i, _i],
@@ -215,7 +216,7 @@ def _kv_args(kv: Optional[tuple]) -> tuple:
         return None, None, 0, 0, 0, 0
     cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size = kv
     if cache.dtype != torch.bfloat16:
-        raise invalid_argument("gemm_rows: the cache destination must be bfloat16")
+        raise invalid_argument("gemm: the cache destination must be bfloat16")
     return _dev(cache, "cache"), _dev(slot_mapping, "slot_mapping", torch.int32), q_dim, n_kv_head, head_dim, page_size
 
 
@@ -255,10 +256,20 @@ def gemm_persistent_tile(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, m:
         out.stride(0), m, n, k))
 
 
+def gemm_persistent_kv_supports(w: torch.Tensor, out: torch.Tensor, q_dim: int, n_kv_head: int, head_dim: int,
+                                page_size: int) -> bool:
+    """Whether gemm_persistent can put the keys and values of a fused projection with these sizes into the cache."""
+    return bool(lib().lb_gemm_persistent_kv_supports(_code(out.dtype, "out"), w.shape[0], ACTIVATIONS["none"], 0, q_dim,
+                                                     n_kv_head, head_dim, page_size))
+
+
 def gemm_persistent(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
-                    activation: str = "none", residual: Optional[torch.Tensor] = None, feature_tile: int = 0) -> torch.Tensor:
+                    activation: str = "none", residual: Optional[torch.Tensor] = None, feature_tile: int = 0,
+                    kv: Optional[tuple] = None) -> torch.Tensor:
     """out[:m] = act(a[:m] @ w.T + bias) + residual for more than 64 tokens: persistent tcgen05 kernel, every
-    operand, the residual and the result moved by TMA."""
+    operand, the residual and the result moved by TMA.  `kv` = (cache, slot_mapping, q_dim, n_kv_head, head_dim,
+    page_size): the product is a fused query/key/value projection; the features from q_dim on go into the cache's
+    pages (row i at slot_mapping[i]) and not into `out`."""
     n, k = w.shape
     if a.shape[1] != k or out.stride(1) != 1 or out.shape[1] != n:
         raise invalid_argument(f"gemm: shapes do not fit: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
@@ -267,7 +278,7 @@ def gemm_persistent(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tenso
     check(lib().lb_gemm_persistent(_code(out.dtype, "out"), _dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0),
                                    _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
                                    residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n,
-                                   k, ACTIVATIONS[activation], feature_tile, stream_ptr()), "gemm_persistent")
+                                   k, ACTIVATIONS[activation], feature_tile, *_kv_args(kv), stream_ptr()), "gemm_persistent")
     return out
 
 

@@ -89,6 +89,11 @@ class CausalSelfAttention:
             # A step of a few dozen tokens: the projection's epilogue also puts the new keys and values into their pages.
             ops.gemm_rows(h, w, self.qkv.bias, qkv, T,
                           kv=(cache, view.slot_mapping, self.q_dim, s.n_kv_head, s.head_dim, page_size))
+        elif (unit.write and dt == torch.bfloat16 and T > 64 and ops.gemm_persistent_tile(h, w, qkv, T) > 0
+              and ops.gemm_persistent_kv_supports(w, qkv, self.q_dim, s.n_kv_head, s.head_dim, page_size)):
+            # Many tokens: the same from the tensor-core product's epilogue (only the queries go to `qkv`).
+            ops.gemm_persistent(h, w, self.qkv.bias, qkv, T,
+                                kv=(cache, view.slot_mapping, self.q_dim, s.n_kv_head, s.head_dim, page_size))
         else:
             self.qkv.forward(h, qkv, T, workspace=ws)
             if unit.write:

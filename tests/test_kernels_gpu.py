@@ -407,6 +407,36 @@ def test_gemm_rows_refuses_what_it_cannot_take(dev):
         ops.gemm_rows(a, w, None, torch.empty((64, 16), dtype=torch.float32, device=dev), 64)
 
 
+@pytest.mark.parametrize("M,n_head,n_kv_head,head_dim,page_size,tile", [
+    (300, 6, 2, 64, 16, 0), (300, 6, 2, 64, 16, 64), (1000, 3, 3, 128, 32, 192), (130, 5, 1, 64, 64, 0)])
+def test_gemm_persistent_writes_keys_and_values_into_their_pages(dev, M, n_head, n_kv_head, head_dim, page_size, tile):
+    """The fused projection of many tokens with the cache filled from the epilogue, against the product followed by
+    lb_kv_append: the same queries, the same bits in the cache, tokens with a negative slot left out, other slots
+    untouched; the key and value columns of `out` are left alone."""
+    from liyab_b200 import ops
+    K = 264
+    q_dim, kv_dim = n_head * head_dim, n_kv_head * head_dim
+    N = q_dim + 2 * kv_dim
+    n_pages = (M + page_size - 1) // page_size + 3
+    a, w = _rand((M, K), 66, dev, torch.bfloat16), _rand((N, K), 67, dev, torch.bfloat16, 0.2)
+    bias = _rand((N,), 68, dev)
+    rng = np.random.default_rng(6)
+    slots = rng.permutation(n_pages * page_size)[:M].astype(np.int32)
+    slots[[3, 20, M - 1]] = -1
+    slot_mapping = torch.from_numpy(slots).to(dev)
+    want_cache = torch.full((n_pages, 2, n_kv_head, page_size, head_dim), 3.0, dtype=torch.bfloat16, device=dev)
+    got_cache = want_cache.clone()
+    want = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    ops.gemm_persistent(a, w, bias, want, M, feature_tile=tile)
+    ops.kv_append(want[:, q_dim:q_dim + kv_dim], want[:, q_dim + kv_dim:], slot_mapping, want_cache, M, n_kv_head, head_dim, page_size)
+    assert ops.gemm_persistent_kv_supports(w, want, q_dim, n_kv_head, head_dim, page_size)
+    got = torch.full_like(want, 5.0)
+    ops.gemm_persistent(a, w, bias, got, M, feature_tile=tile, kv=(got_cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size))
+    assert ops.device_status() == 0
+    assert torch.equal(got[:, :q_dim], want[:, :q_dim]) and (got[:, q_dim:] == 5.0).all()
+    assert torch.equal(got_cache, want_cache) and (got_cache != 3.0).any()
+
+
 def test_gemm_persistent_refuses_what_it_cannot_take(dev):
     from liyab_b200 import ops, LiyabError
     a, w = _rand((100, 64), 1, dev, torch.bfloat16), _rand((50, 64), 2, dev, torch.bfloat16)
@@ -414,6 +444,12 @@ def test_gemm_persistent_refuses_what_it_cannot_take(dev):
     assert ops.gemm_persistent_tile(a, w, odd, 100) == 0
     with pytest.raises(LiyabError):
         ops.gemm_persistent(a, w, None, odd, 100)
+    # keys and values go to the cache only in strips of 64 features that lie inside one head
+    w2, out2 = _rand((3 * 96, 64), 3, dev, torch.bfloat16), torch.empty((100, 3 * 96), dtype=torch.bfloat16, device=dev)
+    assert not ops.gemm_persistent_kv_supports(w2, out2, 96, 1, 96, 16)
+    cache = torch.zeros((8, 2, 1, 16, 96), dtype=torch.bfloat16, device=dev)
+    with pytest.raises(LiyabError):
+        ops.gemm_persistent(a, w2, None, out2, 100, kv=(cache, torch.zeros(100, dtype=torch.int32, device=dev), 96, 1, 96, 16))
     ops.linear(a, w, None, odd, 100)                                         # the dispatcher takes the one-tile kernel
     assert (odd.double() - a.double() @ w.double().t()).abs().max().item() < 0.1
     few = torch.empty((64, 50), dtype=torch.float32, device=dev)
