@@ -15,9 +15,9 @@
 //               0..127 of tensor memory) and O += P V (128 x 64, columns 128..191),
 //               the scores of tile j+1 before the update of tile j.  V is used as it
 //               lies in the cache ([key][dim], the "MN-major" operand form).
-//   warps 2..9  softmax, two threads per query row (tensor-memory lane = row; warps
-//               2..5 take the first 64 keys of a tile, warps 6..9 the other 64, and
-//               the halves' maxima meet in shared memory once per tile):
+//   warps 2..17 softmax, four threads per query row (tensor-memory lane = row; warps
+//               2..5 take the first 32 keys of a tile, warps 6..9 the next 32, and so
+//               on; the parts' maxima meet in shared memory once per tile):
 //               tcgen05.ld of the scores (two accumulators: the tensor core
 //               computes the next tile's scores meanwhile), scale, causal/window
 //               mask, running maximum, exp2, the probabilities as bfloat16 into one
@@ -44,8 +44,9 @@ constexpr int kHD = 64;
 constexpr int kBM = 128;              // query rows per block
 constexpr int kBN = 128;              // keys per tile
 constexpr int kStages = 3;
-constexpr int kThreads = 320;
-constexpr int kSoftmaxThreads = 256;        // two threads per query row, one per half of a tile's keys
+constexpr int kThreads = 576;
+constexpr int kParts = 4;                   // threads per query row, each with 32 of a tile's 128 keys
+constexpr int kSoftmaxThreads = 128 * kParts;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kTileBytes = 128 * 128;          // [128 rows][128 bytes]: Q, a K tile, a V tile, half of P
 constexpr uint32_t kTmemCols = 512;    // scores twice (columns 0..127 and 128..255), output (256..319)
@@ -62,8 +63,8 @@ struct Control {
     uint64_t o_done;
     uint32_t tmem_base;
     int abort_flag;
-    float row_max[2][2][kBM];             // [tile parity][key half][row]: the halves' maxima of a tile
-    float row_sum[2][kBM];                // [key half][row]: the halves' sums at the end
+    float row_max[2][kParts][kBM];        // [tile parity][key part][row]: the parts' maxima of a tile
+    float row_sum[kParts][kBM];           // [key part][row]: the parts' sums at the end
 };
 
 __device__ __forceinline__ void give_up(Control* c, int* status, int site) {
@@ -71,14 +72,11 @@ __device__ __forceinline__ void give_up(Control* c, int* status, int site) {
     c->abort_flag = 1;
 }
 
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&v)[32]) {
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16]) {
     asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
-        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
         ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
-          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]),
-          "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]),
-          "r"(v[30]), "r"(v[31])
+          "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
         : "memory");
 }
 // 2^x for x <= 0 or so: the hardware approximation alone (results below the normal range become zero).
@@ -142,8 +140,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c->s_full[i], 1);
-            mbar_init(&c->s_free[i], kSoftmaxThreads);
-            mbar_init(&c->p_full[i], kSoftmaxThreads);
+            mbar_init(&c->s_free[i], kSoftmaxThreads / 32);      // one arrival per softmax warp
+            mbar_init(&c->p_full[i], kSoftmaxThreads / 32);
             mbar_init(&c->p_free[i], 1);
         }
         mbar_init(&c->o_done, 1);
@@ -241,9 +239,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
         }
     } else {
-        // ---- softmax: two threads per query row (warps 2..5 take the first 64 keys of every tile, warps 6..9 the
-        // other 64; both see tensor-memory lanes 32 * (warp % 4) .. + 31).
-        const int quarter = warp & 3, half = (warp - 2) >> 2;
+        // ---- softmax: four threads per query row (warps 2..5 take the first 32 keys of every tile, warps 6..9 the
+        // next 32, and so on; all see tensor-memory lanes 32 * (warp % 4) .. + 31).  Four warps per scheduler: with
+        // two, every instruction's latency showed (0.45 instructions a clock).
+        const int quarter = warp & 3, part = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;                              // row of the tile = lane of tensor memory
         const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const int pos = past + tile_q * kBM + min(r, rows_here - 1);    // rows past the end copy the last one; not stored
@@ -251,45 +250,45 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float sc = scale * kLog2e;
         const uint32_t swz = (uint32_t)(r & 7);
         uint8_t* p_row = p_s + (size_t)r * 128;
-        float m = -CUDART_INF_F, l = 0.0f;                              // l: this thread's half of the row's sum
+        float m = -CUDART_INF_F, l = 0.0f;                              // l: this thread's part of the row's sum
         bool ok = true;
         for (int tile = 0; tile < n_tiles; ++tile) {
             const int sb = tile & 1, pb = tile & 1;
             ok = __all_sync(0xffffffffu, mbar_wait(&c->s_full[sb], (tile >> 1) & 1, abort_flag));      // one answer for the warp
             if (!ok) give_up(c, status, 6);
             tc_fence_after();
-            const int j0 = kv_lo + tile * kBN + half * 64;             // this thread's first key of the tile
-            const bool need_mask = (j0 + 63 > p_min) || (window > 0 && j0 < p_max - window + 1);
-            const uint32_t s_row = t_row + (uint32_t)(sb * kBN + half * 64);
-            // The loops over the 32-column chunks stay rolled: unrolled, a tile's softmax is thousands of
-            // instructions of straight-line code, which the instruction cache does not hold (measured: 2.4x slower).
-            // First pass: the maximum of this half of the row; the halves meet in shared memory.
-            float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F;
+            const int j0 = kv_lo + tile * kBN + part * 32;             // this thread's first key of the tile
+            const bool need_mask = (j0 + 31 > p_min) || (window > 0 && j0 < p_max - window + 1);
+            const uint32_t s_row = t_row + (uint32_t)(sb * kBN + part * 32);
+            // First pass: the maximum of this part of the row; the parts meet in shared memory.
+            float mx0 = -CUDART_INF_F, mx1 = -CUDART_INF_F, mx2 = -CUDART_INF_F, mx3 = -CUDART_INF_F;
+            uint32_t v[32];
             if (ok) {
-                uint32_t v2[2][32];                       // both chunks of the half are requested before either is used
-                tmem_ld32(s_row, v2[0]);
-                tmem_ld32(s_row + 32, v2[1]);
+                tmem_ld32(s_row, v);
                 tmem_ld_wait();
+                if (need_mask) {
 #pragma unroll
-                for (int ch = 0; ch < 2; ++ch) {
-                    const uint32_t (&v)[32] = v2[ch];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-                        if (need_mask) {
-                            const int j = j0 + ch * 32 + i;
-                            if (j > pos || j < first) s0 = -CUDART_INF_F;
-                            if (j + 1 > pos || j + 1 < first) s1 = -CUDART_INF_F;
-                        }
-                        mx0 = fmaxf(mx0, s0);
-                        mx1 = fmaxf(mx1, s1);
-                    }
+                    for (int i = 0; i < 32; ++i)
+                        if (j0 + i > pos || j0 + i < first) v[i] = __float_as_uint(-CUDART_INF_F);
                 }
+#pragma unroll
+                for (int i = 0; i < 32; i += 4) {
+                    mx0 = fmaxf(mx0, __uint_as_float(v[i]));
+                    mx1 = fmaxf(mx1, __uint_as_float(v[i + 1]));
+                    mx2 = fmaxf(mx2, __uint_as_float(v[i + 2]));
+                    mx3 = fmaxf(mx3, __uint_as_float(v[i + 3]));
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = 0u;
             }
-            c->row_max[tile & 1][half][r] = fmaxf(mx0, mx1);
-            named_barrier(1, kSoftmaxThreads);              // reached by all 256 threads, also after a wait ran out
+            c->row_max[tile & 1][part][r] = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+            named_barrier(1, kSoftmaxThreads);              // reached by all softmax threads, also after a wait ran out
             if (*abort_flag != 0) break;
-            const float m_new = fmaxf(m, fmaxf(c->row_max[tile & 1][0][r], c->row_max[tile & 1][1][r]) * sc);
+            float mx = c->row_max[tile & 1][0][r];
+#pragma unroll
+            for (int q = 1; q < kParts; ++q) mx = fmaxf(mx, c->row_max[tile & 1][q][r]);
+            const float m_new = fmaxf(m, mx * sc);
             const float base_m = m_new == -CUDART_INF_F ? 0.0f : m_new;
             const float corr = exp2f(m - base_m);
             // This buffer of probabilities was last read by the update of the tile before last.
@@ -297,58 +296,46 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 ok = __all_sync(0xffffffffu, mbar_wait(&c->p_free[pb], ((tile >> 1) - 1) & 1, abort_flag));
                 if (!ok) { give_up(c, status, 7); break; }
             }
-            // Second pass: probabilities -> shared memory (bfloat16, swizzled), and their sum.
+            // Second pass, on the scores still in registers (masked ones are -inf: weight 0): probabilities -> shared
+            // memory (bfloat16, swizzled), and their sum.  One multiply-add and one MUFU per score: the SM's
+            // exponential unit (16 results a clock) and its issue slots, not the tensor core, set this kernel's pace.
             float sum0 = 0.0f, sum1 = 0.0f;
-            uint8_t* half_row = p_row + (size_t)(pb * 2 + half) * kTileBytes;
-            uint32_t w2[2][32];
-            tmem_ld32(s_row, w2[0]);
-            tmem_ld32(s_row + 32, w2[1]);
-            tmem_ld_wait();
+            uint8_t* half_row = p_row + (size_t)(pb * 2 + (part >> 1)) * kTileBytes;
 #pragma unroll
-            for (int ch = 0; ch < 2; ++ch) {
-                const uint32_t (&v)[32] = w2[ch];
+            for (int q8 = 0; q8 < 4; ++q8) {
+                float p[8];
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
-                    float p[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        // One multiply-add and one MUFU per score: the SM's exponential unit (16 results a clock) and
-                        // its issue slots, not the tensor core, set this kernel's pace.
-                        p[i] = ex2_approx(fmaf(__uint_as_float(v[q8 * 8 + i]), sc, -base_m));
-                        if (need_mask) {
-                            const int j = j0 + ch * 32 + q8 * 8 + i;
-                            if (j > pos || j < first) p[i] = 0.0f;
-                        }
-                    }
-                    sum0 += (p[0] + p[1]) + (p[2] + p[3]);
-                    sum1 += (p[4] + p[5]) + (p[6] + p[7]);
-                    uint4 pk;
-                    pk.x = pack2(p[0], p[1]);
-                    pk.y = pack2(p[2], p[3]);
-                    pk.z = pack2(p[4], p[5]);
-                    pk.w = pack2(p[6], p[7]);
-                    const uint32_t chunk = (uint32_t)(ch * 4 + q8);                   // 16-byte chunk within the 64-key half
-                    *reinterpret_cast<uint4*>(half_row + ((chunk ^ swz) << 4)) = pk;
-                }
+                for (int i = 0; i < 8; ++i) p[i] = ex2_approx(fmaf(__uint_as_float(v[q8 * 8 + i]), sc, -base_m));
+                sum0 += (p[0] + p[1]) + (p[2] + p[3]);
+                sum1 += (p[4] + p[5]) + (p[6] + p[7]);
+                uint4 pk;
+                pk.x = pack2(p[0], p[1]);
+                pk.y = pack2(p[2], p[3]);
+                pk.z = pack2(p[4], p[5]);
+                pk.w = pack2(p[6], p[7]);
+                const uint32_t chunk = (uint32_t)((part & 1) * 4 + q8);                // 16-byte chunk within the 64-key half
+                *reinterpret_cast<uint4*>(half_row + ((chunk ^ swz) << 4)) = pk;
             }
             // The scores have been read: the tile after next may overwrite them.
+            // (One lane arrives for its warp: hundreds of arrivals on one barrier word would queue up behind one another.)
             tc_fence_before();
-            mbar_arrive(&c->s_free[sb]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->s_free[sb]);
             l = l * corr + (sum0 + sum1);
             m = m_new;
             // O *= corr where some row of the warp moved its maximum (never for the first tile: O is overwritten);
-            // the update of the tile before must be complete for that.  Each half rescales 32 of the 64 columns.
+            // the update of the tile before must be complete for that.  Each part rescales 16 of the 64 columns.
             if (tile > 0) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&c->o_done, (tile - 1) & 1, abort_flag));
                 if (!ok) { give_up(c, status, 8); break; }
                 tc_fence_after();
                 if (__any_sync(0xffffffffu, corr != 1.0f)) {
-                    uint32_t o[32];
-                    tmem_ld32(t_row + kOCol + half * 32, o);
+                    uint32_t o[16];
+                    tmem_ld16(t_row + kOCol + part * 16, o);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
-                    tmem_st32(t_row + kOCol + half * 32, o);
+                    for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * corr);
+                    tmem_st16(t_row + kOCol + part * 16, o);
                     tmem_st_wait();
                 }
             }
@@ -356,7 +343,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // cache holds there (it may be anything, also NaN) would meet its zero weight in the second product.
             // Those value rows (fewer than 16, in the last tile only) are zeroed here, after the tile has landed.
             const int t0 = kv_lo + tile * kBN;
-            if (half == 0 && t0 + kBN - 1 > p_max) {
+            if (part == 0 && t0 + kBN - 1 > p_max) {
                 ok = __all_sync(0xffffffffu, mbar_wait(&c->kv_full[tile % kStages], (tile / kStages) & 1, abort_flag));
                 if (!ok) { give_up(c, status, 9); break; }
                 const int last = p_max - t0;                        // last visible row of the tile
@@ -368,10 +355,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             }
             tc_fence_before();
             fence_async_shared();                   // P (and those rows), written through the generic proxy, are read by the tensor core
-            mbar_arrive(&c->p_full[pb]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->p_full[pb]);
         }
-        // The halves' sums meet, then each half normalises and stores 32 of the row's 64 values.
-        c->row_sum[half][r] = l;
+        // The parts' sums meet, then each part normalises and stores 16 of the row's 64 values.
+        c->row_sum[part][r] = l;
         named_barrier(1, kSoftmaxThreads);
         if (*abort_flag == 0) {
             ok = __all_sync(0xffffffffu, mbar_wait(&c->o_done, (n_tiles - 1) & 1, abort_flag));
@@ -381,19 +369,22 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
         if (ok) {
             tc_fence_after();
-            const float inv = 1.0f / (c->row_sum[0][r] + c->row_sum[1][r]);
-            __nv_bfloat16* dst = out + (size_t)(row0 + tile_q * kBM + r) * out_stride + (size_t)head * kHD + half * 32;
-            uint32_t v[32];
-            tmem_ld32(t_row + kOCol + half * 32, v);
+            float total = c->row_sum[0][r];
+#pragma unroll
+            for (int q = 1; q < kParts; ++q) total += c->row_sum[q][r];
+            const float inv = 1.0f / total;
+            __nv_bfloat16* dst = out + (size_t)(row0 + tile_q * kBM + r) * out_stride + (size_t)head * kHD + part * 16;
+            uint32_t o[16];
+            tmem_ld16(t_row + kOCol + part * 16, o);
             tmem_ld_wait();
             if (r < rows_here) {
 #pragma unroll
-                for (int q8 = 0; q8 < 4; ++q8) {
+                for (int q8 = 0; q8 < 2; ++q8) {
                     uint4 pk;
-                    pk.x = pack2(__uint_as_float(v[q8 * 8]) * inv, __uint_as_float(v[q8 * 8 + 1]) * inv);
-                    pk.y = pack2(__uint_as_float(v[q8 * 8 + 2]) * inv, __uint_as_float(v[q8 * 8 + 3]) * inv);
-                    pk.z = pack2(__uint_as_float(v[q8 * 8 + 4]) * inv, __uint_as_float(v[q8 * 8 + 5]) * inv);
-                    pk.w = pack2(__uint_as_float(v[q8 * 8 + 6]) * inv, __uint_as_float(v[q8 * 8 + 7]) * inv);
+                    pk.x = pack2(__uint_as_float(o[q8 * 8]) * inv, __uint_as_float(o[q8 * 8 + 1]) * inv);
+                    pk.y = pack2(__uint_as_float(o[q8 * 8 + 2]) * inv, __uint_as_float(o[q8 * 8 + 3]) * inv);
+                    pk.z = pack2(__uint_as_float(o[q8 * 8 + 4]) * inv, __uint_as_float(o[q8 * 8 + 5]) * inv);
+                    pk.w = pack2(__uint_as_float(o[q8 * 8 + 6]) * inv, __uint_as_float(o[q8 * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(dst + q8 * 8) = pk;
                 }
             }

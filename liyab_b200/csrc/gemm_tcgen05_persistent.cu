@@ -208,7 +208,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c->acc_full[i], 1);
-            mbar_init(&c->acc_empty[i], kEpilogueThreads);
+            mbar_init(&c->acc_empty[i], kEpilogueThreads / 32);     // one arrival per epilogue warp
         }
         mbar_init(&c->res_full, 1);
         mbar_init(&c->staging_free, 2);
@@ -417,7 +417,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             }
             // The accumulator has been read: the MMAs of the tile after next may overwrite it.
             tc_fence_before();
-            mbar_arrive(&c->acc_empty[buf]);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c->acc_empty[buf]);
             if (et == 0 && it == 0) stamp(timing, 5);
             if (elected) {
                 bulk_wait_read();                   // this group's stores have read the staging buffer
