@@ -88,7 +88,14 @@ def check(status: int, what: str) -> None:
         raise LiyabError(code, f"{what}: {msg}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """The current CUDA stream of the current device as a raw pointer (asked once per launch, so by the short way
+    where torch offers it)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
