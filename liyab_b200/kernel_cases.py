@@ -6,6 +6,7 @@
     python -m liyab_b200.kernel_cases sample --rows 8 --vocab 50257 --temp 0.8 --top-k 40 --top-p 0.95
     python -m liyab_b200.kernel_cases decode-step --batch 8 --layers 12 --reps 20 [--eager]
     python -m liyab_b200.kernel_cases prefill-step --tokens 2048 --layers 12 --reps 3
+    python -m liyab_b200.kernel_cases mixed-workload --size xl --batch 64
 
 Each prints one line with the CUDA-event time per repetition and the achieved rate.  The cases are what the
 ncu summaries under profiles/ were captured on (one kernel, a few launches, inputs of a few hundred MB at most).
@@ -205,6 +206,30 @@ def case_prefill_step(args) -> None:
     print(f"prefill-step size={args.size} tokens={n_seq}x{per} layers={len(model.spec.layers)}: {ms:.3f} ms per step, {n_seq * per / ms * 1e3:.0f} tokens/s")
 
 
+def case_mixed_workload(args) -> None:
+    """Requests with prompts of 1 to the model's positions, each generated up to the last position, all submitted
+    at once: chunked prefill beside decoding through the engine's scheduler; host ids in and out."""
+    import time
+    from . import Engine, EngineConfig, SamplingParams
+    folder = _model_folder(args.layers, args.dtype, args.size)
+    n = args.batch
+    eng = Engine(EngineConfig(model=folder, dtype=args.dtype, max_requests=n, max_batched_tokens=args.tokens, page_size=16))
+    V, P = eng.model.spec.vocab_size, eng.max_positions
+    rng = np.random.default_rng(3)
+    lens = rng.integers(1, P + 1, size=n)
+    prompts = [rng.integers(0, V, size=int(k)).tolist() for k in lens]
+    params = [SamplingParams(temperature=0.0, max_tokens=int(P - k), ignore_eos=True) for k in lens]
+    eng.generate_batch([p[:8] for p in prompts[:4]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    results = eng.generate_batch(prompts, params)
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    generated = sum(r.stats.generated_tokens for r in results)
+    print(f"mixed-workload size={args.size} layers={len(eng.model.spec.layers)} requests={n}: {int(lens.sum())} prompt tokens and "
+          f"{generated} generated tokens in {seconds:.2f} s, {generated / seconds:.0f} generated tokens/s")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m liyab_b200.kernel_cases")
     sub = ap.add_subparsers(dest="case", required=True)
@@ -243,7 +268,7 @@ def main(argv=None) -> int:
     sm.add_argument("--top-p", type=float, default=0.95)
     sm.add_argument("--spread", type=float, default=3.0, help="standard deviation of the random logits (8: peaked like a model's)")
     sm.add_argument("--reps", type=int, default=400)
-    for name in ("decode-step", "prefill-step"):
+    for name in ("decode-step", "prefill-step", "mixed-workload"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
         p.add_argument("--tokens", type=int, default=2048)
@@ -255,7 +280,7 @@ def main(argv=None) -> int:
         p.add_argument("--eager", action="store_true")
     args = ap.parse_args(argv)
     {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
-     "prefill-step": case_prefill_step}[args.case](args)
+     "prefill-step": case_prefill_step, "mixed-workload": case_mixed_workload}[args.case](args)
     return 0
 
 
