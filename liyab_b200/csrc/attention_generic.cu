@@ -22,6 +22,15 @@ constexpr int kWarps = 4;
 constexpr int kTile = 32;       // keys per step, one per lane
 constexpr int kMaxHeadDim = 256;
 
+// Four consecutive elements as floats with one load (the address is aligned to the four of them).
+__device__ __forceinline__ float4 lb_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 lb_load4(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+    const float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+}
+
 // Copies the rows of up to 32 keys (lane i knows the row of key i: `base`, negative if there is none) into
 // the warp's tile as floats.  Eight loads are issued before any is used, so a lone warp (a decode step of
 // one request) still keeps several requests to memory in flight.
@@ -29,6 +38,34 @@ template <typename T>
 __device__ __forceinline__ void load_tile(const T* __restrict__ cache, long long base, long long offset, float* tile,
                                           int tile_stride, int head_dim, int lane) {
     constexpr int kBatch = 8;
+    if (head_dim % 4 == 0) {
+        // Four values per load (rows of the cache start on 16-byte, or for 2-byte types 8-byte, boundaries).
+        constexpr int kQuadBatch = 4;
+        const int quads = head_dim / 4, total4 = kTile * quads;     // a multiple of 32
+        for (int idx0 = lane; idx0 < total4; idx0 += 32 * kQuadBatch) {
+            float4 r[kQuadBatch];
+#pragma unroll
+            for (int u = 0; u < kQuadBatch; ++u) {
+                const int idx = idx0 + 32 * u;
+                r[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (idx < total4) {            // uniform across the warp
+                    const int key = idx / quads, d = (idx - key * quads) * 4;
+                    const long long b = __shfl_sync(0xffffffffu, base, key);
+                    if (b >= 0) r[u] = lb_load4(cache + b + offset + d);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < kQuadBatch; ++u) {
+                const int idx = idx0 + 32 * u;
+                if (idx < total4) {
+                    const int key = idx / quads;
+                    float* dst = tile + key * tile_stride + (idx - key * quads) * 4;
+                    dst[0] = r[u].x; dst[1] = r[u].y; dst[2] = r[u].z; dst[3] = r[u].w;
+                }
+            }
+        }
+        return;
+    }
     const int total = kTile * head_dim;        // a multiple of 32: every lane makes the same number of trips
     for (int idx0 = lane; idx0 < total; idx0 += 32 * kBatch) {
         float r[kBatch];

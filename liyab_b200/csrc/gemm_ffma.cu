@@ -32,18 +32,39 @@ gemm_ffma_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W
 #pragma unroll
         for (int j = 0; j < TN; ++j) acc[i][j] = 0.0f;
 
-    for (int k0 = 0; k0 < K; k0 += BK) {
-        for (int idx = tid; idx < BM * BK; idx += THREADS) {
-            const int r = idx / BK, k = idx % BK;
+    // A thread's pieces of the next tiles wait in registers while the current ones are multiplied: the loads of
+    // step i + 1 travel under the arithmetic of step i.
+    constexpr int LA = BM * BK / THREADS, LW = BN * BK / THREADS;
+    static_assert(LA * THREADS == BM * BK && LW * THREADS == BN * BK, "the tiles divide among the threads");
+    float ra[LA], rw[LW];
+    auto fetch = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < LA; ++i) {
+            const int idx = tid + i * THREADS, r = idx / BK, k = idx % BK;
             const int gm = m0 + r, gk = k0 + k;
-            As[k][r] = (gm < M && gk < K) ? lb_to_float(A[(size_t)gm * lda + gk]) : 0.0f;
+            ra[i] = (gm < M && gk < K) ? lb_to_float(A[(size_t)gm * lda + gk]) : 0.0f;
         }
-        for (int idx = tid; idx < BN * BK; idx += THREADS) {
-            const int r = idx / BK, k = idx % BK;
+#pragma unroll
+        for (int i = 0; i < LW; ++i) {
+            const int idx = tid + i * THREADS, r = idx / BK, k = idx % BK;
             const int gn = n0 + r, gk = k0 + k;
-            Ws[k][r] = (gn < N && gk < K) ? lb_to_float(W[(size_t)gn * ldw + gk]) : 0.0f;
+            rw[i] = (gn < N && gk < K) ? lb_to_float(W[(size_t)gn * ldw + gk]) : 0.0f;
+        }
+    };
+    fetch(0);
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < LA; ++i) {
+            const int idx = tid + i * THREADS;
+            As[idx % BK][idx / BK] = ra[i];
+        }
+#pragma unroll
+        for (int i = 0; i < LW; ++i) {
+            const int idx = tid + i * THREADS;
+            Ws[idx % BK][idx / BK] = rw[i];
         }
         __syncthreads();
+        if (k0 + BK < K) fetch(k0 + BK);
 #pragma unroll
         for (int kk = 0; kk < BK; ++kk) {
             float a[TM], b[TN];
@@ -79,8 +100,10 @@ template <typename TI, typename TO>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual,
            int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, cudaStream_t s) {
     if (M <= 16) {
-        dim3 grid((N + 63) / 64, (M + 15) / 16);
-        gemm_ffma_kernel<TI, TO, 16, 64, 16, 1, 4><<<grid, 256, 0, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias,
+        // Few tokens: one output per thread, 16 features per block (so that a narrow matrix still gives every SM a
+        // block) and 64 columns of K per step.
+        dim3 grid((N + 15) / 16, (M + 15) / 16);
+        gemm_ffma_kernel<TI, TO, 16, 16, 64, 1, 1><<<grid, 256, 0, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias,
                                                                       residual, ldr, (TO*)out, ldo, M, N, K, act);
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64);
