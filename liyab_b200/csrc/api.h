@@ -149,6 +149,35 @@ int lb_sample(const float* logits, int64_t row_stride, int n_rows, int vocab, co
               const int32_t* top_k, const float* top_p, const double* uniform, int32_t* out_ids, float* out_probs,
               void* stream);
 
+/* logits[i] = logits[i] * scale, then soft_cap * tanh(logits[i] / soft_cap) when soft_cap > 0. */
+int lb_scale_softcap(float* logits, int64_t count, float scale, float soft_cap, void* stream);
+
+/* A whole decode step of up to 16 tokens as one cooperative kernel (bfloat16, head size 64 or 128): embedding,
+ * every layer (LayerNorm, fused projection with cache write, attention over the pages, output projection,
+ * LayerNorm, feed-forward) and the head.  `layers_dev` holds n_layers records of lb_decode_stack_layer_bytes()
+ * bytes each on the device: thirteen pointers (norm 1 gain and bias, norm 2 gain and bias, projection weight and
+ * bias, output weight and bias, up weight and bias, down weight and bias, the layer's cache pages), three floats
+ * (the norms' eps, the score factor), six ints (heads, key/value heads, head size, inner width, activation,
+ * window) and four bytes of padding.  x, q, att, inner, partial, counters and logits are scratch of 16 rows;
+ * `barrier` points at one of a pair of zeroed counters that alternate launches use in turn. */
+int lb_decode_stack_layer_bytes(void);
+int64_t lb_decode_stack_scratch_floats(int n_tokens, int n_head, int head_dim, int n_splits);
+int lb_decode_stack(const void* layers_dev, int n_layers, int n_tokens, int width, int vocab, const void* embedding,
+                    const void* pos_table, float embed_scale, const float* lnf_w, const float* lnf_b, float lnf_eps,
+                    const void* head_w, const float* head_b, const int32_t* tokens, const int32_t* positions,
+                    const int32_t* block_table, int table_stride, const int32_t* slot_mapping, int page_size, float* x, void* q,
+                    void* att, void* inner, float* partial, int* counters, float* logits, unsigned* barrier, int max_k,
+                    int head_dim, int n_splits, int unit_warps, unsigned long long* timing, void* stream);
+/* Reads and clears the status word of the fused step's grid barrier.  Synchronises the device. */
+int lb_decode_stack_status(int* status);
+
+/* The two status words without a device synchronisation: an asynchronous copy into pinned host memory on
+ * `stream`, and a reset on `stream`. */
+int lb_gemm_tcgen05_status_async(int* host, void* stream);
+int lb_gemm_tcgen05_status_clear(void* stream);
+int lb_decode_stack_status_async(int* host, void* stream);
+int lb_decode_stack_status_clear(void* stream);
+
 #ifdef __cplusplus
 }
 #endif

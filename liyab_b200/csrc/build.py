@@ -1,11 +1,14 @@
-"""Builds and loads the kernel library.
+"""Builds and loads the engine's library and its two programs.
 
-Every .cu file of this folder is compiled for sm_100a with nvcc into an object,
-and the objects are linked into libliyab_b200.so under `_build/` beside the
-sources (or, where that folder cannot be written, under the system's temporary
-folder).  Nothing is built when the library on disk was made from the same
-sources and flags.  The first call in a fresh checkout therefore compiles what
-the engine needs, printing a line per file; later calls only load.
+Every .cu file of this folder (the kernels) is compiled for sm_100a with nvcc and
+every .cpp file of ../host (the C++20 host: configuration, weights, cache manager,
+step function, scheduler, engine, C interface) with the host compiler; the objects
+are linked into libliyab_b200.so under `_build/` beside the sources (or, where
+that folder cannot be written, under the system's temporary folder), and the
+programs liyab-cli and trace_run (../host/tools) are linked against it.  Nothing
+is built when what is on disk was made from the same sources and flags.  The first
+call in a fresh checkout therefore compiles what the engine needs, printing a line
+per file; later calls only load.
 
 There is no fallback: without the library (no nvcc, a compile error) the engine
 raises, it never computes on the CPU or through another library instead.
@@ -28,9 +31,13 @@ from typing import List, Optional
 from ..status import backend_error
 
 HERE = os.path.dirname(os.path.abspath(__file__))
+HOST = os.path.join(os.path.dirname(HERE), "host")
+INCLUDE = os.path.join(os.path.dirname(HERE), "include")
 LIB_NAME = "libliyab_b200.so"
+PROGRAMS = ("liyab_cli", "trace_run")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-warn-spills"]
+CXX_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter"]
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -41,11 +48,17 @@ def _say(msg: str) -> None:
 
 
 def sources() -> List[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+    """The CUDA sources (names in this folder) and the host sources (paths relative to this folder)."""
+    cu = sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
+    cpp = sorted(os.path.join("..", "host", f) for f in os.listdir(HOST) if f.endswith(".cpp"))
+    return cu + cpp
 
 
 def _headers() -> List[str]:
-    return sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+    own = sorted(f for f in os.listdir(HERE) if f.endswith((".cuh", ".h")))
+    host = sorted(os.path.join("..", "host", f) for f in os.listdir(HOST) if f.endswith(".h"))
+    public = sorted(os.path.join("..", "include", f) for f in os.listdir(INCLUDE) if f.endswith(".h"))
+    return own + host + public
 
 
 def _digest(files: List[str], extra: str = "") -> str:
@@ -54,6 +67,18 @@ def _digest(files: List[str], extra: str = "") -> str:
         with open(os.path.join(HERE, name), "rb") as f:
             h.update(name.encode() + b"\0" + f.read())
     return h.hexdigest()[:24]
+
+
+def find_cxx() -> str:
+    for cand in (os.environ.get("LIYAB_CXX"), os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++")):
+        if cand and shutil.which(cand):
+            return shutil.which(cand)
+    raise backend_error("no C++ compiler was found (looked at $LIYAB_CXX, $CXX, g++ and c++ on PATH); the engine's host "
+                        "library cannot be built")
+
+
+def cuda_include(nvcc: str) -> str:
+    return os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(nvcc))), "include")
 
 
 def find_nvcc() -> str:
@@ -85,12 +110,15 @@ def build_dir() -> str:
 
 
 def _compile_one(nvcc: str, src: str, obj: str, log: str) -> None:
-    cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+    if src.endswith(".cu"):
+        cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+    else:
+        cmd = [find_cxx(), *CXX_FLAGS, "-I", cuda_include(nvcc), "-c", os.path.join(HERE, src), "-o", obj]
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     with open(log, "w") as f:
         f.write(" ".join(cmd) + "\n" + proc.stdout)
     if proc.returncode != 0:
-        raise backend_error(f"nvcc failed on {src}:\n{proc.stdout[-4000:]}")
+        raise backend_error(f"{os.path.basename(cmd[0])} failed on {src}:\n{proc.stdout[-4000:]}")
 
 
 def ensure_built(verbose: bool = True) -> str:
@@ -105,7 +133,8 @@ def ensure_built(verbose: bool = True) -> str:
     def fresh() -> bool:
         try:
             with open(stamp) as f:
-                return f.read().strip() == whole and os.path.isfile(lib)
+                return (f.read().strip() == whole and os.path.isfile(lib)
+                        and all(os.path.isfile(os.path.join(out, p)) for p in PROGRAMS))
         except OSError:
             return False
 
@@ -121,32 +150,40 @@ def ensure_built(verbose: bool = True) -> str:
             todo, objs = [], []
             for src in srcs:
                 tag = _digest([src], hdr_digest)
-                obj = os.path.join(out, f"{os.path.splitext(src)[0]}.{tag}.o")
+                obj = os.path.join(out, f"{os.path.splitext(os.path.basename(src))[0]}.{tag}.o")
                 objs.append(obj)
                 if not os.path.isfile(obj):
                     todo.append((src, obj))
             if todo and verbose:
-                _say(f"compiling {len(todo)} CUDA source file(s) for sm_100a into {out} (first call only)")
+                _say(f"compiling {len(todo)} source file(s) (CUDA for sm_100a, C++ host) into {out} (first call only)")
             t0 = time.time()
             done = [0]
 
             def work(item):
                 src, obj = item
                 tmp = obj + f".tmp{os.getpid()}"
-                _compile_one(nvcc, src, tmp, os.path.join(out, src + ".log"))
+                _compile_one(nvcc, src, tmp, os.path.join(out, os.path.basename(src) + ".log"))
                 os.replace(tmp, obj)
                 done[0] += 1
                 if verbose:
-                    _say(f"  compiled {src} ({done[0]}/{len(todo)}, {time.time() - t0:.0f} s)")
+                    _say(f"  compiled {os.path.basename(src)} ({done[0]}/{len(todo)}, {time.time() - t0:.0f} s)")
 
             with ThreadPoolExecutor(max_workers=min(8, max(1, os.cpu_count() or 1))) as pool:
                 list(pool.map(work, todo))
             tmp_lib = lib + f".tmp{os.getpid()}"
-            link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
+            link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl", "-lpthread"]
             proc = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             if proc.returncode != 0:
                 raise backend_error(f"linking {LIB_NAME} failed:\n{proc.stdout[-4000:]}")
             os.replace(tmp_lib, lib)
+            for prog in PROGRAMS:       # the programs talk to the library through its C interface only
+                tmp_prog = os.path.join(out, f"{prog}.tmp{os.getpid()}")
+                cmd = [find_cxx(), "-std=c++17", "-O2", os.path.join(HOST, "tools", prog + ".cpp"), "-o", tmp_prog,
+                       "-L", out, "-lliyab_b200", "-Wl,-rpath,$ORIGIN"]
+                proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+                if proc.returncode != 0:
+                    raise backend_error(f"building {prog} failed:\n{proc.stdout[-4000:]}")
+                os.replace(tmp_prog, os.path.join(out, prog))
             with open(stamp, "w") as f:
                 f.write(whole)
             keep = set(objs)
@@ -161,14 +198,19 @@ def ensure_built(verbose: bool = True) -> str:
             fcntl.flock(lockf, fcntl.LOCK_UN)
 
 
+def program(name: str) -> str:
+    """The path of a built program (liyab_cli or trace_run); built first if it has to be."""
+    return os.path.join(os.path.dirname(ensure_built()), name)
+
+
 def load_library() -> ctypes.CDLL:
-    """The loaded kernel library; built first if it has to be."""
+    """The loaded library; built first if it has to be.  Its symbols are visible to plug-ins loaded later."""
     global _lib
     with _lock:
         if _lib is None:
             path = ensure_built()
             try:
-                _lib = ctypes.CDLL(path)
+                _lib = ctypes.CDLL(path, mode=ctypes.RTLD_GLOBAL)
             except OSError as e:
                 raise backend_error(f"cannot load {path}: {e}") from e
         return _lib

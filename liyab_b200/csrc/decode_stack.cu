@@ -1312,3 +1312,19 @@ extern "C" int lb_decode_stack_status(int* status) {
     LB_CHECK_CUDA(cudaMemcpyToSymbol(g_stack_status, &zero, sizeof(int)));
     return LB_OK;
 }
+
+// The same word without a device synchronisation: copies it into `host` (pinned memory) on `stream`;
+// lb_decode_stack_status_clear zeroes it on `stream`.
+extern "C" int lb_decode_stack_status_async(int* host, void* stream) {
+    int* word = nullptr;
+    LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&word, g_stack_status));
+    LB_CHECK_CUDA(cudaMemcpyAsync(host, word, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return LB_OK;
+}
+
+extern "C" int lb_decode_stack_status_clear(void* stream) {
+    int* word = nullptr;
+    LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&word, g_stack_status));
+    LB_CHECK_CUDA(cudaMemsetAsync(word, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    return LB_OK;
+}

@@ -8,7 +8,7 @@
 
 // ---------------------------------------------------------------- errors
 
-static thread_local char g_last_error[512] = "";
+static thread_local char g_last_error[4096] = "";
 
 int lb_fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -19,6 +19,11 @@ int lb_fail(int code, const char* fmt, ...) {
 }
 
 extern "C" const char* lb_last_error(void) { return g_last_error; }
+
+// The host library's failures land in the same thread-local message.
+extern "C" void lb_set_last_error(const char* message) {
+    snprintf(g_last_error, sizeof g_last_error, "%s", message != nullptr ? message : "");
+}
 
 extern "C" int lb_abi_version(void) { return LB_ABI_VERSION; }
 
@@ -287,6 +292,27 @@ extern "C" int lb_gather_tokens(int32_t* dst, const int32_t* src, const int32_t*
     LB_CHECK_ARG(n >= 0, "gather_tokens: bad size %d", n);
     if (n == 0) return LB_OK;
     gather_tokens_kernel<<<(n + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(dst, src, map, n);
+    LB_CHECK_LAUNCH();
+    return LB_OK;
+}
+
+// ---------------------------------------------------------------- logit scale and soft cap
+
+// The head's finishing touches where a model has them (the reference's finish_logits and
+// apply_final_softcap: src/core/transformer.cpp:2613-2620): x * scale, then cap * tanh(x / cap).
+__global__ void scale_softcap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.0f) v = cap * tanhf(v / cap);
+        x[i] = v;
+    }
+}
+
+extern "C" int lb_scale_softcap(float* logits, int64_t count, float scale, float soft_cap, void* stream) {
+    LB_CHECK_ARG(logits != nullptr && count >= 0, "scale_softcap: bad arguments");
+    if (count == 0) return LB_OK;
+    const int blocks = (int)((count + 255) / 256 < 1184 ? (count + 255) / 256 : 1184);
+    scale_softcap_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, count, scale, soft_cap);
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

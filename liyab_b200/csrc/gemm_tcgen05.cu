@@ -468,3 +468,21 @@ extern "C" int lb_gemm_tcgen05_status(int* status) {
     LB_CHECK_CUDA(cudaMemcpyToSymbol(g_status, &zero, sizeof(int)));
     return LB_OK;
 }
+
+// The same word without a device synchronisation: copies it into `host` (pinned memory) on `stream`;
+// lb_gemm_tcgen05_status_clear zeroes it on `stream`.
+extern "C" int lb_gemm_tcgen05_status_async(int* host, void* stream) {
+    int* word = nullptr;
+    const int rc = lb_tc_status_word(&word);
+    if (rc != LB_OK) return rc;
+    LB_CHECK_CUDA(cudaMemcpyAsync(host, word, sizeof(int), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+    return LB_OK;
+}
+
+extern "C" int lb_gemm_tcgen05_status_clear(void* stream) {
+    int* word = nullptr;
+    const int rc = lb_tc_status_word(&word);
+    if (rc != LB_OK) return rc;
+    LB_CHECK_CUDA(cudaMemsetAsync(word, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    return LB_OK;
+}

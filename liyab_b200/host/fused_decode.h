@@ -1,0 +1,47 @@
+// The fused decode step: a stack of pre-norm blocks run by one persistent kernel.
+//
+// A decode step of a few requests is bound by launch count and memory round
+// trips, not by bytes or flops.  Where a model is made of nothing but the standard
+// parts (LayerNorm, attention with a fused projection, dense feed-forward,
+// pre-norm arrangement, learned or no positions) in bfloat16, its decode steps of
+// up to 16 tokens are handed to csrc/decode_stack.cu, which runs the whole step
+// as one cooperative kernel.  Anything else (another mixer, another arrangement,
+// float32, more tokens, prompt portions, a head with a scale or a cap) takes the
+// part-by-part path; the results agree to bfloat16 rounding, which the tests check.
+//
+// This class only describes the model to the kernel: it packs one record per
+// run-order entry from the parts' own parameters and owns the step's buffers.
+#pragma once
+
+#include <memory>
+
+#include "decoder.h"
+
+namespace liyab {
+
+class FusedDecodeStack {
+public:
+    static constexpr int kMaxTokens = 16;
+    // Null when the model or the cache is not of the shape the kernel takes.
+    static std::unique_ptr<FusedDecodeStack> try_build(const DecoderModel& model, const CacheManager& cache);
+
+    bool accepts(int n_tokens) const { return n_tokens >= 1 && n_tokens <= kMaxTokens; }
+    // Computes the logits of a decode step ([n_tokens, vocab] float32, valid until the next run).
+    Rows run(StepContext& ctx);
+
+private:
+    FusedDecodeStack() = default;
+    void splits(int n_tokens, int* n_splits, int* unit_warps) const;
+
+    const DecoderModel* model_ = nullptr;
+    const CacheManager* cache_ = nullptr;
+    int head_dim_ = 0, n_layers_ = 0, max_k_ = 0, max_qd_ = 0, max_inner_ = 0, max_heads_ = 0, max_kv_heads_ = 0;
+    const void* pos_table_ = nullptr;
+    const float* lnf_w_ = nullptr;
+    const float* lnf_b_ = nullptr;
+    float lnf_eps_ = 0.0f;
+    DeviceBuffer layers_, x_, q_, att_, inner_, logits_, partial_, counters_, barrier_;
+    uint64_t launches_ = 0;
+};
+
+}  // namespace liyab

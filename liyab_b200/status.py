@@ -55,3 +55,8 @@ def context_full(msg: str) -> LiyabError:
 
 def backend_error(msg: str) -> LiyabError:
     return LiyabError(ErrorCode.BACKEND_ERROR, msg)
+
+
+class OutOfPages(LiyabError):
+    """A reservation that the free pages cannot cover; nothing was taken."""
+

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from liyab_b200 import ErrorCode, LiyabError
-from liyab_b200.cache import UNMAPPED, CacheManager, KvNeed, OutOfPages, PagePool, StateNeed
+from liyab_b200.cache import UNMAPPED, CacheManager, KvNeed, OutOfPages, StateNeed
 
 
 def manager(num_pages=16, page_size=4, window_units=(), max_requests=4, state=False):
@@ -14,25 +14,28 @@ def manager(num_pages=16, page_size=4, window_units=(), max_requests=4, state=Fa
     return CacheManager(needs, states, page_size, num_pages, max_requests)
 
 
-def test_pool_refuses_double_free_and_counts():
-    pool = PagePool(3)
-    a, b, c = pool.take(), pool.take(), pool.take()
-    assert sorted([a, b, c]) == [0, 1, 2] and pool.free_count == 0
+def test_pool_hands_out_every_page_once_and_reuses_freed_ones():
+    m = CacheManager({0: KvNeed(1, 16, 0)}, {}, page_size=4, num_pages=3, max_requests=3)
+    for r in "abc":
+        m.open(r)
+        m.reserve(r, 4); m.commit(r, 4)
+    pages = [int(m.block_table(0, [r])[0, 0]) for r in "abc"]
+    assert sorted(pages) == [0, 1, 2] and m.free_pages() == {0: 0}
     with pytest.raises(OutOfPages):
-        pool.take()
-    pool.give_back(b)
+        m.reserve("a", 1)
+    m.close("b")
     with pytest.raises(LiyabError):
-        pool.give_back(b)
-    with pytest.raises(LiyabError):
-        pool.give_back(7)
-    assert pool.take() == b          # most recently freed first: pages are used again
-    pool.check()
+        m.close("b")                 # a second close cannot free its pages twice
+    m.open("d")
+    m.reserve("d", 1)
+    assert int(m.block_table(0, ["d"])[0, 0]) == pages[1]          # most recently freed first: pages are used again
+    m.check()
 
 
 def test_groups_by_need_and_tables_per_group():
     m = manager(window_units=(1, 3))
     assert len(m.groups) == 2
-    assert m.groups[m.group_of_unit[0]].units == [0, 2] and m.groups[m.group_of_unit[1]].units == [1, 3]
+    assert m.groups[m.group_of_unit[0]]["units"] == [0, 2] and m.groups[m.group_of_unit[1]]["units"] == [1, 3]
     m.open("a")
     m.reserve("a", 10)
     m.commit("a", 10)
@@ -127,7 +130,7 @@ def test_random_orders_keep_the_invariants(seed):
                 with pytest.raises(OutOfPages):
                     m.reserve(rid, n)
                 assert m.free_pages() == before
-        elif op < 0.9 and not m.groups[-1].need.window:
+        elif op < 0.9 and not m.groups[-1]["window"]:
             rid = rng.choice(list(live))
             cut = rng.randint(0, live[rid])
             m.truncate(rid, cut); live[rid] = cut
@@ -135,11 +138,12 @@ def test_random_orders_keep_the_invariants(seed):
             rid = rng.choice(list(live))
             m.close(rid); del live[rid]
         m.check()
-        for g in m.groups:      # every page a request can still see is mapped
+        for gi, g in enumerate(m.groups):      # every page a request can still see is mapped
             for rid, n in live.items():
-                t = g.tables[rid]
-                first = 0 if not g.need.window else max(0, n - g.need.window + 1) // g.page_size
-                assert all(p != UNMAPPED for p in t[first:(n + g.page_size - 1) // g.page_size])
+                t = m.table_of(gi, rid)
+                first = 0 if not g["window"] else max(0, n - g["window"] + 1) // m.page_size
+                assert len(t) >= (n + m.page_size - 1) // m.page_size or n == 0
+                assert all(p != UNMAPPED for p in t[first:(n + m.page_size - 1) // m.page_size])
     for rid in list(live):
         m.close(rid)
     m.check()

@@ -45,10 +45,9 @@ def oracle(folders):
     return out
 
 
-def make_engine(path, dtype, max_tokens, page_size=16):
-    from liyab_b200.engine.replay import build_replayer
-    _, cache, stepper = build_replayer(path, dtype, max_tokens, page_size=page_size)
-    return cache, stepper
+def make_engine(path, dtype, max_tokens, page_size=16, **options):
+    from liyab_b200.engine import Replayer
+    return Replayer(path, dtype, max_tokens, page_size=page_size, **options)
 
 
 def check_against_oracle(got, want, dtype):
@@ -68,23 +67,23 @@ def test_every_cutting_matches_plain(name, dtype, folders, oracle):
     reqs = request_set(name)
     want = oracle[(name, dtype)]
     n_rows = sum(len(t) for t in reqs.values())
-    cache, stepper = make_engine(folders[(name, dtype)], dtype, max_tokens=4 * 256)
+    engine = make_engine(folders[(name, dtype)], dtype, max_tokens=4 * 256)
     traces = {"whole": tt.whole(reqs), "tail": tt.tail_one_by_one(reqs, 32), "portions": tt.changing_portions(reqs)}
     results = {}
     for kind, steps in traces.items():
-        results[kind] = tt.collect(stepper, cache, steps)
+        results[kind] = tt.collect(engine, steps)
         assert len(results[kind]) == n_rows
         check_against_oracle(results[kind], want, dtype)
     # Mixed, with so few pages that they are used again: a pool for the trace's own peak only.
     steps = tt.mixed(reqs, max_live=4, seed=3)
     assert max(len(e) for e, _ in steps) >= 3, "the mixed trace must batch several requests"
     peak = tt.peak_tokens(steps, 64)
-    cache2, stepper2 = make_engine(folders[(name, dtype)], dtype, max_tokens=peak)
-    results["mixed"] = tt.collect(stepper2, cache2, steps)
+    engine2 = make_engine(folders[(name, dtype)], dtype, max_tokens=peak)
+    results["mixed"] = tt.collect(engine2, steps)
     assert len(results["mixed"]) == n_rows
     check_against_oracle(results["mixed"], want, dtype)
     total_pages = sum(-(-len(t) // 16) for t in reqs.values())
-    assert cache2.groups[0].pool.num_pages < total_pages, "pages must have been used again"
+    assert engine2.cache.groups[0]["num_pages"] < total_pages, "pages must have been used again"
     if dtype == "float32":
         # The engine's own invariant: a position's logits are the same bits however the tokens were cut.
         for kind in ("tail", "portions", "mixed"):
@@ -95,16 +94,16 @@ def test_every_cutting_matches_plain(name, dtype, folders, oracle):
 @pytest.mark.parametrize("page_size", [16, 64])
 def test_page_size_does_not_matter(page_size, folders, oracle):
     reqs = request_set("B")
-    cache, stepper = make_engine(folders[("B", "float32")], "float32", max_tokens=1024, page_size=page_size)
-    got = tt.collect(stepper, cache, tt.changing_portions(reqs, sizes=(63, 2, 1, 64, 17)))
+    engine = make_engine(folders[("B", "float32")], "float32", max_tokens=1024, page_size=page_size)
+    got = tt.collect(engine, tt.changing_portions(reqs, sizes=(63, 2, 1, 64, 17)))
     check_against_oracle(got, oracle[("B", "float32")], "float32")
 
 
 def test_first_tokens_and_long_decoding(folders, oracle):
     """The first tokens of a sequence one by one, then decoding to the model's last position."""
     reqs = {"r0": request_set("A")["r0"]}
-    cache, stepper = make_engine(folders[("A", "float32")], "float32", max_tokens=128)
-    got = tt.collect(stepper, cache, tt.tail_one_by_one(reqs, tail=128))
+    engine = make_engine(folders[("A", "float32")], "float32", max_tokens=128)
+    got = tt.collect(engine, tt.tail_one_by_one(reqs, tail=128))
     assert len(got) == 128
     check_against_oracle(got, oracle[("A", "float32")], "float32")
 
@@ -115,7 +114,7 @@ def test_trace_run_program(dtype, folders, oracle, tmp_path):
     reqs = {k: v for k, v in request_set("B").items() if k in ("r1", "r2", "r3", "r6")}
     steps = tt.mixed(reqs, max_live=4, seed=5)
     out_dir = str(tmp_path / "out")
-    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folders[("B", dtype)],
+    proc = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folders[("B", dtype)],
                            "--dtype", dtype, "--out", out_dir, "--max-tokens", str(tt.peak_tokens(steps))],
                           input=tt.to_jsonl(steps), capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]

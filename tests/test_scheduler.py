@@ -4,7 +4,7 @@ import pytest
 
 from liyab_b200 import ErrorCode, SamplingParams
 from liyab_b200.cache import CacheManager, KvNeed
-from liyab_b200.engine.scheduler import Request, RequestState, Scheduler
+from liyab_b200.engine import Request, Scheduler
 
 
 def make(num_pages=16, page_size=4, max_batched_tokens=16, max_requests=4, max_positions=64, eos=None):
@@ -45,7 +45,7 @@ def test_prompt_is_cut_under_the_budget_and_decodes_go_first():
     plan, _ = run_step(cache, sched)       # decodes first (1 token each), the new prompt gets the rest
     assert [(e.request.id, e.count) for e in plan.entries] == [("r0", 1), ("r1", 1), ("r2", 6)]
     assert [e.tokens for e in plan.entries][0] == [a.tokens[-2]]
-    assert sched.stats.decode_tokens == 2
+    assert sched.stats["decode_tokens"] == 2
 
 
 def test_portions_down_to_one_token():
@@ -101,7 +101,7 @@ def test_admission_waits_for_pages_and_takes_first_come_first():
         sched.add(r)
     plan, _ = run_step(cache, sched)
     # a (11 -> 3 pages) and b (3 pages) fit; c would fit too but waits its turn only if pages are short: 6 pages are gone
-    assert [e.request.id for e in plan.entries] == ["r0", "r1"] and c.state == RequestState.WAITING
+    assert [e.request.id for e in plan.entries] == ["r0", "r1"] and c.state == "waiting"
     order = []
     while sched.has_work():
         plan, fin = run_step(cache, sched)
@@ -120,7 +120,7 @@ def test_preemption_when_pages_run_out_then_recompute():
         preempted += len(plan.preempted)
         log.append([(e.request.id, e.start, e.count) for e in plan.entries])
     assert preempted >= 1 and b.preemptions >= 1 and a.preemptions == 0      # the most recently admitted one yields
-    assert sched.stats.preemptions == preempted
+    assert sched.stats["preemptions"] == preempted
     assert a.finish_reason == "length" and b.finish_reason == "length"
     assert a.generated == [100 + i for i in range(9)] and b.generated == [100 + i for i in range(9)]
     # after preemption b was recomputed from its prompt and the tokens it had generated
@@ -155,14 +155,24 @@ def test_bad_requests_are_refused():
 
 
 def test_draws_do_not_depend_on_batching():
+    """A request's n-th draw is uniform(seed, its stream, n): streams are handed out in order of arrival and a seed of
+    0 is replaced by a random one, so nothing about a batch enters a draw."""
     from liyab_b200.sampling import uniform_draw
     cache, sched = make()
-    a = Request(id="a", prompt=[1, 2], params=SamplingParams(seed=7))
-    sched.add(a)
-    u0 = a.next_uniform()
-    a.tokens.append(5)
-    u1 = a.next_uniform()
-    assert (u0, u1) == (uniform_draw(7, 0, 0), uniform_draw(7, 0, 1)) and u0 != u1
+    a, b, c = (Request(id=n, prompt=[1, 2], params=SamplingParams(seed=s)) for n, s in (("a", 7), ("b", 7), ("c", 0)))
+    for r in (a, b, c):
+        sched.add(r)
+    assert (a.seed, a.stream) == (7, 0) and (b.seed, b.stream) == (7, 1) and c.seed != 0 and c.stream == 2
+    draws = [uniform_draw(7, 0, 0), uniform_draw(7, 0, 1), uniform_draw(7, 1, 0)]
+    assert len(set(draws)) == 3 and all(0.0 <= u < 1.0 for u in draws)
+    # the reference values of the documented generator (SplitMix64 of seed, stream and counter; top 53 bits)
+    def plain(seed, stream, counter):
+        m = (1 << 64) - 1
+        z = (seed * 0x9E3779B97F4A7C15 + stream * 0xD1B54A32D192ED03 + counter * 0x8CB92BA72F3D8DD7 + 0x9E3779B97F4A7C15) & m
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & m
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & m
+        return ((z ^ (z >> 31)) >> 11) / 9007199254740992.0
+    assert draws == [plain(7, 0, 0), plain(7, 0, 1), plain(7, 1, 0)]
 
 
 def run_pipelined(cache, sched, token_of):

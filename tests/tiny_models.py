@@ -33,12 +33,11 @@ CONFIGS = {"A": (CONFIG_A, 0), "B": (CONFIG_B, 1), "C": (CONFIG_C, 2), "D": (CON
 
 def write_model(folder: str, name: str, dtype: str = "float32") -> str:
     """Writes configuration `name` with its seed into `folder`/<name>_<dtype> and returns that path."""
-    from liyab_b200.config import parse_config
     from liyab_b200.weights import write_random_model
     raw, seed = CONFIGS[name]
     path = os.path.join(folder, f"{name}_{dtype}")
     if not os.path.isfile(os.path.join(path, "model.safetensors")):
-        write_random_model(path, parse_config(raw), seed, dtype)
+        write_random_model(path, raw, seed, dtype)
     return path
 
 

@@ -87,24 +87,28 @@ def peak_tokens(steps: List[Step], round_to: int = 64) -> int:
     return peak
 
 
-def collect(stepper, cache, steps: List[Step]) -> Dict[Tuple[str, int], np.ndarray]:
+def collect(replayer, steps: List[Step]) -> Dict[Tuple[str, int], np.ndarray]:
     """Runs the steps through the engine's step function; returns logits by (request, position)."""
     from liyab_b200.engine import StepEntry
+    cache = replayer.cache
     out: Dict[Tuple[str, int], np.ndarray] = {}
+    held: Dict[str, int] = {}
     for entries, end in steps:
         batch = []
         base = {}
         for r, toks, want in entries:
-            if not cache.is_open(r):
+            if r not in held:
                 cache.open(r)
-            base[r] = cache.length(r)
+                held[r] = 0
+            base[r] = held[r]
+            held[r] += len(toks)
             batch.append(StepEntry(request=r, tokens=toks, want=want))
-        res = stepper.step(batch)
+        res = replayer.step(batch)
         if res.logits is not None:
-            rows = res.logits.float().cpu().numpy()
-            for (r, idx), row in zip(res.rows, rows):
+            for (r, idx), row in zip(res.rows, res.logits):
                 out[(r, base[r] + idx)] = row.copy()
         for r in end:
+            assert cache.length(r) == held.pop(r)
             cache.close(r)
     cache.check()
     return out
