@@ -349,8 +349,9 @@ extern "C" int lb_decode_attention_noalloc(const void* q, int64_t q_stride, cons
     if (!lb_decode_attention_supports(n_head, n_kv_head, head_dim, page_size))
         return lb_fail(LB_ERR_UNSUPPORTED, "decode attention (no-alloc): unsupported shape heads %d/%d head_dim %d page_size %d",
                        n_head, n_kv_head, head_dim, page_size);
-    const long long floats = (long long)n_seq * n_head * n_splits * (head_dim + 2);
-    const long long ints = (long long)n_seq * n_kv_head;
+    // An unsplit call touches neither array: no limit applies to it and nothing has to be cleared.
+    const long long floats = n_splits > 1 ? (long long)n_seq * n_head * n_splits * (head_dim + 2) : 0;
+    const long long ints = n_splits > 1 ? (long long)n_seq * n_kv_head : 0;
     LB_CHECK_ARG(floats <= LB_NOALLOC_SCRATCH_FLOATS,
                  "decode attention (no-alloc): %lld floats of scratch needed (n_seq %d x n_head %d x n_splits %d x (head_dim %d + 2)), "
                  "the built-in scratch holds %d; use fewer splits or requests, or lb_decode_attention with your own scratch",
@@ -364,7 +365,7 @@ extern "C" int lb_decode_attention_noalloc(const void* q, int64_t q_stride, cons
     if (rc != LB_OK) return rc;
     auto s = static_cast<cudaStream_t>(stream);
     // The array keeps the last call's contents; the counters have to start at zero.
-    LB_CHECK_CUDA(cudaMemsetAsync(scratch.counters, 0, (size_t)ints * sizeof(int), s));
+    if (ints > 0) LB_CHECK_CUDA(cudaMemsetAsync(scratch.counters, 0, (size_t)ints * sizeof(int), s));
     return lb_decode_attention(q, q_stride, cache, positions, block_table, table_stride, out, out_stride, scratch.partial,
                                scratch.counters, n_seq, n_head, n_kv_head, head_dim, page_size, scale, window, n_splits,
                                stream);

@@ -16,7 +16,8 @@
  *  - Limits: n_seq * n_head * n_splits * (head_dim + 2) <= LB_NOALLOC_SCRATCH_FLOATS
  *    and n_seq * n_kv_head <= LB_NOALLOC_COUNTER_INTS; anything larger is refused
  *    with LB_ERR_INVALID_ARGUMENT (1) and a message (lb_last_error) that names the
- *    limit.  Shapes that lb_decode_attention_supports refuses are refused here too.
+ *    limit.  A call with n_splits = 1 uses no scratch, so neither limit applies to it.
+ *    Shapes that lb_decode_attention_supports refuses are refused here too.
  *  - The first call on each device looks up the array's device address (once per
  *    device, with that device current).  Make that first call before any stream
  *    capture begins.

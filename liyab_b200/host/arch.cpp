@@ -1,12 +1,14 @@
 #include "arch.h"
 
 #include <algorithm>
+#include <cstdlib>
 #include <fstream>
 #include <map>
 #include <mutex>
 #include <sstream>
 
 #include "decoder.h"
+#include "parts.h"
 
 namespace liyab {
 namespace {
@@ -60,6 +62,20 @@ void register_builtin_architectures() {
     std::call_once(once, [] {
         register_gpt2();
         register_architecture({"liyab_spec", {}, [](const Json& raw) { return std::make_unique<SpecConfig>(raw); }});
+    });
+    // Plug-ins named by the environment (paths separated by ':') are loaded once, so that the programs can run
+    // models made of parts from outside the library.
+    static std::once_flag plugins;
+    std::call_once(plugins, [] {
+        const char* env = std::getenv("LIYAB_B200_PLUGINS");
+        if (env == nullptr) return;
+        std::string list = env;
+        size_t at = 0;
+        while (at <= list.size()) {
+            const size_t end = std::min(list.find(':', at), list.size());
+            if (end > at) load_plugin(list.substr(at, end - at));
+            at = end + 1;
+        }
     });
 }
 

@@ -6,7 +6,6 @@
     python -m liyab_b200.kernel_cases sample --rows 8 --vocab 50257 --temp 0.8 --top-k 40 --top-p 0.95
     python -m liyab_b200.kernel_cases decode-step --batch 8 --layers 12 --reps 20 [--eager]
     python -m liyab_b200.kernel_cases prefill-step --tokens 2048 --layers 12 --reps 3
-    python -m liyab_b200.kernel_cases mixed-workload --size xl --batch 64
 
 Each prints one line with the CUDA-event time per repetition and the achieved rate.  The cases are what the
 ncu summaries under profiles/ were captured on (one kernel, a few launches, inputs of a few hundred MB at most).
@@ -17,8 +16,6 @@ import argparse
 import os
 import sys
 import tempfile
-import time
-
 import numpy as np
 import torch
 
@@ -151,83 +148,32 @@ def case_sample(args) -> None:
 
 
 def _model_folder(layers: int, dtype: str, size: str = "small") -> str:
-    from .config import parse_config
     from .weights import write_random_model
     tmp = tempfile.mkdtemp(prefix="liyab_b200_case_")
-    return write_random_model(os.path.join(tmp, "m"), parse_config(dict(GPT2_SIZES[size], n_layer=layers or GPT2_SIZES[size]["n_layer"])), 0, dtype)
+    return write_random_model(os.path.join(tmp, "m"), dict(GPT2_SIZES[size], n_layer=layers or GPT2_SIZES[size]["n_layer"]), 0, dtype)
 
 
 def case_decode_step(args) -> None:
-    from .engine import StepEntry
-    from .engine.replay import build_replayer
+    """A few decode steps of the whole model through the library's own measurement (what bench.py times)."""
+    from .engine import Replayer
     B = args.batch
-    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=B * 1024,
-                                           max_requests=B)
-    stepper.cuda_graphs = not args.eager
-    stepper.workspace.reserve_rows(max(1024, B))
-    V = model.spec.vocab_size
-    rng = np.random.default_rng(0)
-    ids = [f"b{i}" for i in range(B)]
-    for r in ids:
-        cache.open(r)
-    for i in range(0, B, 2):
-        stepper.step([StepEntry(r, rng.integers(0, V, size=args.context).tolist(), []) for r in ids[i:i + 2]])
-
-    def one():
-        if cache.length(ids[0]) + 1 > model.max_positions:
-            for r in ids:
-                cache.truncate(r, args.context)
-        stepper.step([StepEntry(r, [1], [0]) for r in ids])
-
-    ms = _timed(one, args.reps, warmup=3)
-    print(f"decode-step size={args.size} batch={B} layers={len(model.spec.layers)} context~{args.context} graphs={not args.eager}: "
-          f"{ms * 1e3:.1f} us per step, {B / ms * 1e3:.0f} tokens/s")
+    rep = Replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=B * 1024, max_requests=B,
+                   cuda_graphs=not args.eager, fused_decode=not args.no_fused, max_step_tokens=1024)
+    r = rep.bench_decode(B, args.context, args.reps, 3)
+    path = "fused" if r["fused_steps"] else ("graph" if r["graph_steps"] else "parts")
+    print(f"decode-step size={args.size} batch={B} layers={len(rep.info['spec']['layers'])} context~{r['mean_context']:.0f} path={path}: "
+          f"{r['ms_per_step'] * 1e3:.1f} us per step, {B / r['ms_per_step'] * 1e3:.0f} tokens/s, {r['kernel_launches'] // args.reps} launches a step")
 
 
 def case_prefill_step(args) -> None:
-    from .engine import StepEntry
-    from .engine.replay import build_replayer
-    model, cache, stepper = build_replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=2 * args.tokens)
-    V = model.spec.vocab_size
-    rng = np.random.default_rng(0)
+    from .engine import Replayer
     n_seq = max(1, args.tokens // 1024)
     per = args.tokens // n_seq
-
-    prompts = [rng.integers(0, V, size=per).tolist() for _ in range(n_seq)]
-
-    def one():
-        for i in range(n_seq):
-            cache.open(f"p{i}")
-        stepper.step([StepEntry(f"p{i}", prompts[i], [per - 1]) for i in range(n_seq)])
-        for i in range(n_seq):
-            cache.close(f"p{i}")
-
-    ms = _timed(one, args.reps, warmup=2)
-    print(f"prefill-step size={args.size} tokens={n_seq}x{per} layers={len(model.spec.layers)}: {ms:.3f} ms per step, {n_seq * per / ms * 1e3:.0f} tokens/s")
-
-
-def case_mixed_workload(args) -> None:
-    """Requests with prompts of 1 to the model's positions, each generated up to the last position, all submitted
-    at once: chunked prefill beside decoding through the engine's scheduler; host ids in and out."""
-    import time
-    from . import Engine, EngineConfig, SamplingParams
-    folder = _model_folder(args.layers, args.dtype, args.size)
-    n = args.batch
-    eng = Engine(EngineConfig(model=folder, dtype=args.dtype, max_requests=n, max_batched_tokens=args.tokens, page_size=16))
-    V, P = eng.model.spec.vocab_size, eng.max_positions
-    rng = np.random.default_rng(3)
-    lens = rng.integers(1, P + 1, size=n)
-    prompts = [rng.integers(0, V, size=int(k)).tolist() for k in lens]
-    params = [SamplingParams(temperature=0.0, max_tokens=int(P - k), ignore_eos=True) for k in lens]
-    eng.generate_batch([p[:8] for p in prompts[:4]], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    results = eng.generate_batch(prompts, params)
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - t0
-    generated = sum(r.stats.generated_tokens for r in results)
-    print(f"mixed-workload size={args.size} layers={len(eng.model.spec.layers)} requests={n}: {int(lens.sum())} prompt tokens and "
-          f"{generated} generated tokens in {seconds:.2f} s, {generated / seconds:.0f} generated tokens/s")
+    rep = Replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=2 * args.tokens,
+                   cuda_graphs=not args.eager, max_step_tokens=args.tokens)
+    r = rep.bench_prefill(n_seq, per, args.reps)
+    print(f"prefill-step size={args.size} tokens={n_seq}x{per} layers={len(rep.info['spec']['layers'])}: best {r['ms_per_step']:.3f} ms, "
+          f"median {r['wall_ms_per_step']:.3f} ms per step, {n_seq * per / r['ms_per_step'] * 1e3:.0f} tokens/s, {r['kernel_launches']} launches")
 
 
 def main(argv=None) -> int:
@@ -268,7 +214,7 @@ def main(argv=None) -> int:
     sm.add_argument("--top-p", type=float, default=0.95)
     sm.add_argument("--spread", type=float, default=3.0, help="standard deviation of the random logits (8: peaked like a model's)")
     sm.add_argument("--reps", type=int, default=400)
-    for name in ("decode-step", "prefill-step", "mixed-workload"):
+    for name in ("decode-step", "prefill-step"):
         p = sub.add_parser(name)
         p.add_argument("--batch", type=int, default=8)
         p.add_argument("--tokens", type=int, default=2048)
@@ -277,10 +223,11 @@ def main(argv=None) -> int:
         p.add_argument("--size", default="small", choices=sorted(GPT2_SIZES))
         p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
         p.add_argument("--reps", type=int, default=10)
-        p.add_argument("--eager", action="store_true")
+        p.add_argument("--eager", action="store_true", help="no captured graphs")
+        p.add_argument("--no-fused", action="store_true", help="not the one-kernel decode step")
     args = ap.parse_args(argv)
     {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
-     "prefill-step": case_prefill_step, "mixed-workload": case_mixed_workload}[args.case](args)
+     "prefill-step": case_prefill_step}[args.case](args)
     return 0
 
 

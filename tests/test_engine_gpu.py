@@ -47,8 +47,8 @@ def test_greedy_generation_config_a(folders, graphs):
     for p, r in zip(prompts, got):
         assert r.tokens == plain.generate_greedy(oracle, p, 16) and r.finish_reason == "length"
         assert r.stats.prompt_tokens == len(p) and r.stats.generated_tokens == 16
-    assert (engine.stepper.graph_steps > 0) == graphs
-    assert all(v == 0 for v in engine.cache.pages_in_use().values())
+    assert (engine.stats()["graph_steps"] > 0) == graphs
+    assert engine.stats()["pages_in_use"] == 0
 
 
 def test_sampled_generation_config_b(folders):
@@ -63,7 +63,7 @@ def test_sampled_generation_config_b(folders):
     oracle = plain.load_plain_model(folder)
     for stream, (p, r) in enumerate(zip(prompts, got)):
         assert r.tokens == plain_sampled(oracle, p, params, stream, 24)
-    assert engine.scheduler.stats.prefill_tokens == 1 + 5 + 33 + 70
+    assert engine.stats()["prefill_tokens"] == 1 + 5 + 33 + 70
     # the same requests one at a time give the same tokens: a draw belongs to (seed, stream, index), not to a batch
     engine2 = Engine(EngineConfig(model=folder, dtype="float32", max_requests=1, max_batched_tokens=2048, num_pages=64))
     for stream, (p, r) in enumerate(zip(prompts, got)):
@@ -80,9 +80,9 @@ def test_preemption_does_not_change_the_tokens(folders):
     want = [r.tokens for r in roomy.generate_batch(prompts, params)]
     tight = Engine(EngineConfig(model=folder, dtype="float32", max_requests=4, max_batched_tokens=32, num_pages=9))
     got = tight.generate_batch(prompts, params)
-    assert tight.scheduler.stats.preemptions >= 1
+    assert tight.stats()["preemptions"] >= 1
     assert [r.tokens for r in got] == want
-    assert all(v == 0 for v in tight.cache.pages_in_use().values())
+    assert tight.stats()["pages_in_use"] == 0
 
 
 def test_bfloat16_generation_stays_close(folders):
@@ -127,15 +127,24 @@ def test_callback_stop_and_eos(folders, tmp_path):
 def test_command_line(folders):
     folder = folders[("A", "float32")]
     prompt = random_tokens(1, 7, 512)
-    cmd = [sys.executable, os.path.join(ROOT, "bin", "liyab-cli"), "-m", folder, "-p", ",".join(map(str, prompt)),
+    cmd = [os.path.join(ROOT, "bin", "liyab-cli"), "-m", folder, "-p", ",".join(map(str, prompt)),
            "-n", "6", "--temp", "0", "--dtype", "float32", "--num-pages", "16", "--json"]
     proc = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert proc.returncode == 0, proc.stderr[-2000:]
     lines = [json.loads(l) for l in proc.stdout.splitlines() if l.startswith("{")]
     assert "load_ms" in lines[0] and lines[1]["generated_tokens"] == 6
     assert lines[1]["tokens"] == plain.generate_greedy(plain.load_plain_model(folder), prompt, 6)
-    proc = subprocess.run(cmd[:6] + ["--tokenize"], capture_output=True, text=True, timeout=600)
+    proc = subprocess.run(cmd[:5] + ["--tokenize"], capture_output=True, text=True, timeout=600)
     assert proc.stdout.split() == [str(t) for t in prompt]
+    # the summary on stderr: prompt / decode / memory lines, the decode phases when asked for, the scheduler's counters
+    proc = subprocess.run(cmd[:-1] + ["--phases"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert proc.stdout.split() == [str(t) for t in lines[1]["tokens"]]
+    for needle in ("prompt: 7 tokens", "decode: 6 tokens", "memory: KV", "decode phases (ms/token): embed", "scheduler: 6 steps"):
+        assert needle in proc.stderr, proc.stderr
+    # a model folder that does not fit its configuration is refused with the loader's one message
+    proc = subprocess.run([cmd[0], "-m", os.path.join(folder, "nowhere"), "-p", "1"], capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 1 and "config.json" in proc.stderr
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("D", "bfloat16")])
@@ -165,9 +174,9 @@ def test_pipelined_and_stepwise_loops_give_the_same_tokens(name, dtype, tmp_path
             callbacks = [None, None, (lambda t: seen.append(t) or len(seen) < 5), None, None]
             res = engine.generate_batch(prompts, params, callbacks)
             outs.append([(r.tokens, r.finish_reason) for r in res])
-            assert all(v == 0 for v in engine.cache.pages_in_use().values())
+            assert engine.stats()["pages_in_use"] == 0
             if pages == 8:
-                assert engine.scheduler.stats.preemptions >= 1
+                assert engine.stats()["preemptions"] >= 1
     if dtype == "float32":
         # In 32-bit a token's logits do not depend on the batch or the cut, so every way of running agrees exactly.
         assert outs[0] == outs[1] == outs[2] == outs[3]
