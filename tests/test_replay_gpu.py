@@ -50,15 +50,17 @@ def make_engine(path, dtype, max_tokens, page_size=16, **options):
     return Replayer(path, dtype, max_tokens, page_size=page_size, **options)
 
 
+# The reference's gate for a lower precision (liyab-kl: --max-kl, --min-top1; its GPT-2 case reads KL 0.00000 and
+# top-1 100 %, docs/validation/models-stage1/conformance.json:541-587): mean KL of the engine's distribution from the
+# plain one, and the share of rows with the same best token among those whose plain top-two margin exceeds the tolerance.
+MAX_MEAN_KL = 1e-4
+MIN_TOP1 = 0.99
+
+
 def check_against_oracle(got, want, dtype):
-    worst = 0.0
-    for (r, pos), row in got.items():
-        ref = want[r][pos]
-        scale = np.abs(want[r]).max()
-        err = np.abs(row.astype(np.float64) - ref).max() / scale
-        worst = max(worst, err)
-        assert err <= REL_TOL[dtype], f"request {r} position {pos}: relative error {err:.3e} > {REL_TOL[dtype]:.1e}"
-    return worst
+    if dtype == "bfloat16":
+        return tt.check_rows(got, want, REL_TOL[dtype], MAX_MEAN_KL, MIN_TOP1)
+    return tt.check_rows(got, want, REL_TOL[dtype])
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

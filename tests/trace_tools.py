@@ -121,3 +121,59 @@ def to_jsonl(steps: List[Step]) -> str:
         lines.append(json.dumps({"step": i, "entries": [{"id": r, "tokens": t, "want": w} for r, t, w in entries],
                                  "end": end}))
     return "\n".join(lines) + "\n"
+
+
+def thin(steps: List[Step], keep) -> List[Step]:
+    """The same steps with logits wanted only at the positions `keep(request, position)` says (big vocabularies)."""
+    held: Dict[str, int] = {}
+    out: List[Step] = []
+    for entries, end in steps:
+        new = []
+        for r, toks, want in entries:
+            base = held.get(r, 0)
+            new.append((r, toks, [w for w in want if keep(r, base + w)]))
+            held[r] = base + len(toks)
+        out.append((new, end))
+    return out
+
+
+def kl_and_top1(got: np.ndarray, ref: np.ndarray, margin: float):
+    """(KL(plain || engine) of the two softmax distributions, whether the arg-max agrees or None when the plain
+    implementation's two best logits lie within `margin`): the reference gates lower precision with the mean of the
+    first and the share of the second (tools/liyab_kl.cpp:12-15, 93-99)."""
+    ref = ref.astype(np.float64)
+    got = got.astype(np.float64)
+    lp = ref - ref.max()
+    lp -= np.log(np.exp(lp).sum())
+    lq = got - got.max()
+    lq -= np.log(np.exp(lq).sum())
+    kl = float((np.exp(lp) * (lp - lq)).sum())
+    top = np.partition(ref, -2)[-2:]
+    agree = None if top[1] - top[0] <= margin else bool(np.argmax(got) == np.argmax(ref))
+    return kl, agree
+
+
+def check_rows(got: Dict[Tuple[str, int], np.ndarray], want: Dict[str, np.ndarray], rel_tol: float, max_mean_kl: float = None,
+               min_top1: float = None) -> Dict[str, float]:
+    """Every row within rel_tol * max|logit| of its sequence; and, where asked, the reference's gate for a lower
+    precision: mean KL at most max_mean_kl and the best token the same in at least min_top1 of the rows whose plain
+    top-two margin exceeds the tolerance."""
+    worst, kls, agrees = 0.0, [], []
+    for (r, pos), row in got.items():
+        ref = want[r][pos]
+        scale = np.abs(want[r]).max()
+        err = np.abs(row.astype(np.float64) - ref).max() / scale
+        worst = max(worst, err)
+        assert err <= rel_tol, f"request {r} position {pos}: relative error {err:.3e} > {rel_tol:.1e}"
+        if max_mean_kl is not None:
+            kl, agree = kl_and_top1(row, ref, 2 * rel_tol * scale)
+            kls.append(kl)
+            if agree is not None:
+                agrees.append(agree)
+    out = {"worst": worst}
+    if max_mean_kl is not None:
+        out["mean_kl"] = float(np.mean(kls))
+        out["top1"] = float(np.mean(agrees)) if agrees else 1.0
+        assert out["mean_kl"] <= max_mean_kl, f"mean KL {out['mean_kl']:.3e} > {max_mean_kl:.1e}"
+        assert out["top1"] >= min_top1, f"top-1 agreement {out['top1']:.4f} < {min_top1}"
+    return out
