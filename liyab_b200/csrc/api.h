@@ -177,6 +177,9 @@ int lb_gemm_tcgen05_status_async(int* host, void* stream);
 int lb_gemm_tcgen05_status_clear(void* stream);
 int lb_decode_stack_status_async(int* host, void* stream);
 int lb_decode_stack_status_clear(void* stream);
+/* Writes a status word, as a kernel whose bounded wait ran out would (for tests of the host's handling). */
+int lb_gemm_tcgen05_status_set(int value);
+int lb_decode_stack_status_set(int value);
 
 #ifdef __cplusplus
 }

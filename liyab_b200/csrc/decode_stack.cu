@@ -77,7 +77,7 @@ struct StackLayer {
     int n_head, n_kv_head, head_dim, inner, act, window;
     int pad_;
 };
-static_assert(sizeof(StackLayer) == 144, "StackLayer must match the layout the Python side packs");
+static_assert(sizeof(StackLayer) == 144, "StackLayer must match the layout the host packs");
 
 struct StackParams {
     const StackLayer* layers;
@@ -1326,5 +1326,11 @@ extern "C" int lb_decode_stack_status_clear(void* stream) {
     int* word = nullptr;
     LB_CHECK_CUDA(cudaGetSymbolAddress((void**)&word, g_stack_status));
     LB_CHECK_CUDA(cudaMemsetAsync(word, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
+    return LB_OK;
+}
+
+// Writes the word (tests of the host's handling of a reported barrier; synchronises).
+extern "C" int lb_decode_stack_status_set(int value) {
+    LB_CHECK_CUDA(cudaMemcpyToSymbol(g_stack_status, &value, sizeof(int)));
     return LB_OK;
 }

@@ -486,3 +486,9 @@ extern "C" int lb_gemm_tcgen05_status_clear(void* stream) {
     LB_CHECK_CUDA(cudaMemsetAsync(word, 0, sizeof(int), static_cast<cudaStream_t>(stream)));
     return LB_OK;
 }
+
+// Writes the word (tests of the host's handling of a reported wait; synchronises).
+extern "C" int lb_gemm_tcgen05_status_set(int value) {
+    LB_CHECK_CUDA(cudaMemcpyToSymbol(g_status, &value, sizeof(int)));
+    return LB_OK;
+}

@@ -276,6 +276,28 @@ def device_status() -> Tuple[int, int]:
     return words[0], words[1]
 
 
+def set_device_status(which: int, value: int) -> None:
+    """Writes a device status word as a kernel whose bounded wait ran out would (tests of the engine's handling)."""
+    _capi.check(_capi.lib().lb_debug_set_device_status(which, value))
+
+
+def set_log(level: int, callback: Optional[Callable[[int, str], None]] = None) -> None:
+    """Diagnostics: level 0 debug, 1 info, 2 warn (default), 3 error, 4 off; `callback(level, message)` receives the
+    messages at or above it instead of stderr (None: stderr again)."""
+    l = _capi.lib()
+    l.lb_set_log_level(level)
+    global _log_keep
+    if callback is None:
+        _log_keep = None
+        l.lb_set_log_callback(_capi.LogCallback(), None)
+    else:
+        _log_keep = _capi.LogCallback(lambda lvl, msg, _user: callback(int(lvl), msg.decode("utf-8", "replace")))
+        l.lb_set_log_callback(_log_keep, None)
+
+
+_log_keep = None
+
+
 # ---- the scheduler, for tests that play the step function ---------------------------------------------------
 
 @dataclass
@@ -408,4 +430,4 @@ class Scheduler:
 
 
 __all__ = ["Engine", "EngineConfig", "GenerationResult", "GenerationStats", "generate", "StepEntry", "StepOutput", "Replayer",
-           "device_status", "Request", "PlannedEntry", "StepPlan", "Scheduler", "FINISH_REASONS"]
+           "device_status", "set_device_status", "set_log", "Request", "PlannedEntry", "StepPlan", "Scheduler", "FINISH_REASONS"]

@@ -280,6 +280,10 @@ LB_API int32_t lb_replayer_timer_start(lb_replayer* r);
 LB_API int32_t lb_replayer_timer_stop(lb_replayer* r, double* ms);
 /* Reads and clears the two device status words (tcgen05/TMA waits, the fused step's barrier); synchronises. */
 LB_API int32_t lb_device_status(int32_t* words2);
+/* Writes status word `which` (0 or 1) as a kernel whose bounded wait ran out would: for tests of what the engine does
+ * when a step reports one (its requests end with LB_STATUS_INTERNAL, the words are cleared, a failing fused step is
+ * switched off, the engine goes on). */
+LB_API int32_t lb_debug_set_device_status(int32_t which, int32_t value);
 
 /* Measurements on a replayer, timed on the device with events around exactly the stated work (the reference's
  * liyab-bench and liyab-seq-bench are programs of the engine too: tools/liyab_bench.cpp, tools/liyab_seq_bench.cpp).

@@ -189,3 +189,38 @@ def test_pipelined_and_stepwise_loops_give_the_same_tokens(name, dtype, tmp_path
             for (tokens, reason), p in zip(run, params):
                 assert reason in ("eos", "length", "stopped") and 1 <= len(tokens) <= p.max_tokens
                 assert (reason == "eos") == (tokens[-1] == eos) or reason == "stopped"
+
+
+def test_a_reported_wait_ends_the_step_with_an_error_and_the_engine_goes_on(tmp_path):
+    """A kernel whose bounded wait ran out leaves a status word; the engine reads the words with every step's ids.
+    Here the word of the fused step's barrier is written by hand: the requests of the step that meets it end with
+    INTERNAL and a message, the words are cleared, the one-kernel step is switched off, and the next call generates
+    as before (part by part)."""
+    from liyab_b200 import Engine, EngineConfig, ErrorCode, SamplingParams
+    from liyab_b200.engine import device_status, set_device_status, set_log
+    folder = write_model(str(tmp_path), "D", "bfloat16")
+    prompt = random_tokens(5, 30, CONFIGS["D"][0]["vocab_size"])
+    params = SamplingParams(temperature=0.0, max_tokens=12)
+    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32))
+    good = engine.generate_tokens(prompt, params)
+    assert good.error is None and engine.stats()["fused_steps"] > 0 and engine.stats()["device_faults"] == 0
+    seen = []
+    set_log(3, lambda level, message: seen.append((level, message)))
+    try:
+        set_device_status(1, 0x51)
+        bad = engine.generate_tokens(prompt, params)
+    finally:
+        set_log(2, None)
+    assert bad.error is not None and bad.error.code == ErrorCode.INTERNAL and "bounded wait" in bad.error.message
+    assert bad.finish_reason == "error" and len(bad.tokens) < 12
+    assert seen and seen[0][0] == 3 and "0x51" in seen[0][1]
+    st = engine.stats()
+    assert st["device_faults"] == 1 and st["pages_in_use"] == 0 and device_status() == (0, 0)
+    fused_before = st["fused_steps"]
+    again = engine.generate_tokens(prompt, params)
+    assert again.error is None and again.finish_reason == "length" and len(again.tokens) == 12
+    assert engine.stats()["fused_steps"] == fused_before, "the one-kernel step stays off after it reported a fault"
+    logits = plain.forward_logits(plain.load_plain_model(folder), prompt + again.tokens)
+    for i, tok in enumerate(again.tokens):
+        row = logits[len(prompt) - 1 + i]
+        assert row.max() - row[tok] <= 2.5e-2 * np.abs(row).max()
