@@ -3,14 +3,17 @@
 // key/value groups, with all arithmetic in 32-bit.
 //
 // This is the 32-bit engine's attention and the fallback of the bfloat16 engine
-// for shapes its tensor-core kernels refuse.  One warp serves one (token, head):
-// it walks the token's visible keys 32 at a time from the first visible key, so
-// the order of every sum depends on the token's position only, never on the
-// batch or on where its pages lie (the reference cuts a token's keys by its
-// position alone for the same reason: src/core/transformer.cpp:2130-2144,
-// 2225-2227).  Scores s_j = (q . k_j) * scale, running maximum, p = exp(s - m),
-// o = sum p_j v_j, out = o / sum p (src/core/transformer.cpp:2303-2313, 2327-2341,
-// 2344-2358, 2367-2385).
+// for shapes its tensor-core kernels refuse.  One block serves one (token, head).
+// The token's visible keys are cut into tiles of 32 from the first visible key;
+// tile i goes to warp i mod W (W, the warps of a block, is fixed by the head size),
+// every warp keeps a running softmax over its tiles in ascending order, and the
+// warps' states are merged in warp order.  So the order of every sum depends on
+// the token's position only, never on the batch or on where its pages lie (the
+// reference cuts a token's keys into spans by its position alone for the same
+// reason and merges the spans in order: src/core/transformer.cpp:2130-2144,
+// 2225-2227, 2367-2385).  Scores s_j = (q . k_j) * scale, running maximum,
+// p = exp(s - m), o = sum p_j v_j, out = o / sum p (src/core/transformer.cpp:2303-2313,
+// 2327-2341, 2344-2358).
 #include "api.h"
 #include "common.cuh"
 
@@ -18,7 +21,6 @@
 
 namespace {
 
-constexpr int kWarps = 4;
 constexpr int kTile = 32;       // keys per step, one per lane
 constexpr int kMaxHeadDim = 256;
 
@@ -91,16 +93,15 @@ __device__ __forceinline__ void load_tile(const T* __restrict__ cache, long long
 }
 
 template <typename T>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(512)
 paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const T* __restrict__ cache,
                                const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
                                const int32_t* __restrict__ block_table, int table_stride, T* __restrict__ out,
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
                                int page_size, float scale, int window) {
     extern __shared__ float smem[];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int pair = blockIdx.x * kWarps + warp;
-    if (pair >= n_tokens * n_head) return;     // whole warps leave; no block-wide barrier below
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int pair = blockIdx.x;
     const int t = pair / n_head, h = pair - t * n_head;
     const int kvh = h / (n_head / n_kv_head);
     const int pos = positions[t];
@@ -121,7 +122,7 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
     for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
 
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
-    for (int j0 = first; j0 <= pos; j0 += kTile) {
+    for (int j0 = first + warp * kTile; j0 <= pos; j0 += n_warps * kTile) {
         const int n_keys = min(kTile, pos + 1 - j0);
         // Each lane resolves its own key's row once; the others fetch it by shuffle.
         long long base = -1;
@@ -160,20 +161,46 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
         }
         __syncwarp();
     }
-    const float inv = 1.0f / l;
-    T* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
+    // The warps' states (m, l, o) meet in shared memory and are merged in warp order.  A warp without a tile
+    // has m = -inf, l = 0, o = 0 and weighs nothing.
+    float* merge = smem + (size_t)n_warps * (head_dim + kTile * tile_stride + kTile);
+    float* mine = merge + (size_t)warp * (head_dim + 2);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
     for (int i = 0; i < kMaxHeadDim / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) o_row[d] = lb_from_float<T>(acc[i] * inv);
+        if (d < head_dim) mine[2 + d] = acc[i];
     }
+    __syncthreads();
+    T* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float top = -CUDART_INF_F;
+        for (int w = 0; w < n_warps; ++w) top = fmaxf(top, merge[(size_t)w * (head_dim + 2)]);
+        float total = 0.0f, o = 0.0f;
+        for (int w = 0; w < n_warps; ++w) {
+            const float* st = merge + (size_t)w * (head_dim + 2);
+            const float f = expf(st[0] - top);      // exp(-inf) = 0 for a warp without keys
+            total = fmaf(st[1], f, total);
+            o = fmaf(st[2 + d], f, o);
+        }
+        o_row[d] = lb_from_float<T>(o / total);
+    }
+}
+
+// Warps per block, by the head size alone: eight while three such blocks fit the shared memory of an SM (up to head size 64), fewer for larger heads.
+int warps_for(int head_dim) {
+    const size_t per_warp = (size_t)(head_dim + kTile * (head_dim + 1) + kTile + head_dim + 2) * sizeof(float);
+    int w = 8;
+    while (w > 1 && 3 * w * per_warp > 220 * 1024) w >>= 1;
+    return w;
 }
 
 template <typename T>
 int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* tok_seq, const int32_t* positions,
            const int32_t* block_table, int table_stride, void* out, int64_t out_stride, int n_tokens, int n_head,
            int n_kv_head, int head_dim, int page_size, float scale, int window, cudaStream_t s) {
-    const size_t smem = (size_t)kWarps * (head_dim + kTile * (head_dim + 1) + kTile) * sizeof(float);
+    const int warps = warps_for(head_dim);
+    const size_t smem = (size_t)warps * (head_dim + kTile * (head_dim + 1) + kTile + head_dim + 2) * sizeof(float);
     static size_t configured = 0;   // largest dynamic shared memory asked for so far
     if (smem > configured) {
         LB_CHECK_CUDA(cudaFuncSetAttribute(paged_attention_generic_kernel<T>,
@@ -181,8 +208,8 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* to
         configured = smem;
     }
     const long long pairs = (long long)n_tokens * n_head;
-    const unsigned blocks = (unsigned)((pairs + kWarps - 1) / kWarps);
-    paged_attention_generic_kernel<T><<<blocks, kWarps * 32, smem, s>>>(
+    LB_CHECK_ARG(pairs <= 2147483647ll, "attention: %lld (token, head) pairs are too many for one launch", pairs);
+    paged_attention_generic_kernel<T><<<(unsigned)pairs, warps * 32, smem, s>>>(
         (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
         n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);
     LB_CHECK_LAUNCH();

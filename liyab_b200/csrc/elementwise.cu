@@ -155,6 +155,76 @@ layernorm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ r
     }
 }
 
+// Wider rows (up to 4 * 128 * NV values, a multiple of 4): four warps per row, the row held in registers (each
+// thread float4s t, t + 128, ...), the two sums by warp shuffles and then over the four warps in warp order.  A row
+// of a few thousand values is then a handful of loads per thread, all in flight together, instead of one warp's long
+// chain.  The order of additions depends on the width alone.
+template <typename T, int NV>
+__global__ void __launch_bounds__(128)
+layernorm_row_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w,
+                     const float* __restrict__ b, T* __restrict__ y, int width, float eps) {
+    __shared__ float part[2][4];
+    const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int n4 = width >> 2;
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows != nullptr ? rows[r] : r) * width);
+    float4 v[NV], gain[NV], offs[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 128 * i;
+        const bool live = c < n4;
+        v[i] = live ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        gain[i] = (live && w != nullptr) ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
+        offs[i] = (live && b != nullptr) ? reinterpret_cast<const float4*>(b)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) sum += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    sum = lb_warp_sum(sum);
+    if (lane == 0) part[0][warp] = sum;
+    __syncthreads();
+    const float mean = (((part[0][0] + part[0][1]) + part[0][2]) + part[0][3]) / (float)width;
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (tid + 128 * i < n4) {
+            const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+            ss += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    ss = lb_warp_sum(ss);
+    if (lane == 0) part[1][warp] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf((((part[1][0] + part[1][1]) + part[1][2]) + part[1][3]) / (float)width + eps);
+    T* out = y + (size_t)r * width;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 128 * i;
+        if (c < n4) {
+            float4 o = make_float4((v[i].x - mean) * inv, (v[i].y - mean) * inv, (v[i].z - mean) * inv, (v[i].w - mean) * inv);
+            if (w != nullptr) { o.x *= gain[i].x; o.y *= gain[i].y; o.z *= gain[i].z; o.w *= gain[i].w; }
+            if (b != nullptr) { o.x += offs[i].x; o.y += offs[i].y; o.z += offs[i].z; o.w += offs[i].w; }
+            if constexpr (sizeof(T) == 4) {
+                reinterpret_cast<float4*>(out)[c] = o;
+            } else {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                reinterpret_cast<uint2*>(out)[c] = pk;
+            }
+        }
+    }
+}
+
+template <typename T>
+static void launch_layernorm_row(const float* x, const int32_t* rows, const float* w, const float* b, T* y, int n_rows,
+                                 int width, float eps, cudaStream_t s) {
+    const int n4 = width / 4;
+    if (n4 <= 128 * 2) layernorm_row_kernel<T, 2><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
+    else if (n4 <= 128 * 4) layernorm_row_kernel<T, 4><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
+    else layernorm_row_kernel<T, 8><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
+}
+
 template <typename T>
 static void launch_layernorm_warp(const float* x, const int32_t* rows, const float* w, const float* b, T* y, int n_rows,
                                   int width, float eps, cudaStream_t s) {
@@ -176,7 +246,15 @@ extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, 
     // Rows of float4s that fit a warp's registers take the warp-per-row kernel (everything 16-byte aligned).
     const bool warp_rows = width % 4 == 0 && width <= 2048 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
                            (weight == nullptr || ((uintptr_t)weight & 15) == 0) && (bias == nullptr || ((uintptr_t)bias & 15) == 0);
-    if (warp_rows && out_dtype == LB_F32) {
+    // By the width alone (never by the number of rows: a row's sums must not depend on the batch): up to 512 values
+    // a warp per row, up to 4096 four warps per row.
+    const bool block_rows = warp_rows || (width % 4 == 0 && width <= 4096 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+                                          (weight == nullptr || ((uintptr_t)weight & 15) == 0) && (bias == nullptr || ((uintptr_t)bias & 15) == 0));
+    if (block_rows && width > 512 && out_dtype == LB_F32) {
+        launch_layernorm_row<float>(x, rows, weight, bias, (float*)y, n_rows, width, eps, s);
+    } else if (block_rows && width > 512 && out_dtype == LB_BF16) {
+        launch_layernorm_row<__nv_bfloat16>(x, rows, weight, bias, (__nv_bfloat16*)y, n_rows, width, eps, s);
+    } else if (warp_rows && out_dtype == LB_F32) {
         launch_layernorm_warp<float>(x, rows, weight, bias, (float*)y, n_rows, width, eps, s);
     } else if (warp_rows && out_dtype == LB_BF16) {
         launch_layernorm_warp<__nv_bfloat16>(x, rows, weight, bias, (__nv_bfloat16*)y, n_rows, width, eps, s);

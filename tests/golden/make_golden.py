@@ -15,9 +15,12 @@ The reference keeps its cache in 16-bit at best (include/liyab/types.h:208-213),
 its logits differ from exact arithmetic by about 1e-4 of their scale; the test that
 reads these files uses that tolerance.  The reference's gpt2 row has the tanh
 GELU only and no per-layer attention factor (src/compat/architecture.cpp:81-88),
-so both golden models use gelu_new and no inverse-layer scaling.
+so the golden models use gelu_new and no inverse-layer scaling.  It does read a
+factor on the scores for the whole model (`gpt2.attention.scale`,
+architecture.cpp:975-985): gpt2_ref_c has `scale_attn_weights: false`, written as
+that key with the value 1, which anchors the unscaled scores on the reference too.
 
-Usage: make_golden.py --reference /path/to/liyab --build /path/to/its/build
+Usage: make_golden.py --reference /path/to/liyab --build /path/to/its/build [--only gpt2_ref_c]
 """
 from __future__ import annotations
 
@@ -39,6 +42,8 @@ CASES = {
                         layer_norm_epsilon=1e-5, activation_function="gelu_new"), 11, 20, 6),
     "gpt2_ref_b": (dict(n_layer=3, n_embd=48, n_head=3, n_inner=64, vocab_size=61, n_positions=40,
                         layer_norm_epsilon=1e-6, activation_function="gelu_new"), 12, 9, 12),
+    "gpt2_ref_c": (dict(n_layer=2, n_embd=40, n_head=5, n_inner=72, vocab_size=70, n_positions=32,
+                        layer_norm_epsilon=1e-5, activation_function="gelu_new", scale_attn_weights=False), 13, 14, 8),
 }
 
 
@@ -51,6 +56,8 @@ def write_gguf(path: str, cfg: dict, tensors: dict) -> None:
     w.add_head_count(cfg["n_head"])
     w.add_context_length(cfg["n_positions"])
     w.add_layer_norm_eps(cfg["layer_norm_epsilon"])
+    if not cfg.get("scale_attn_weights", True):
+        w.add_float32("gpt2.attention.scale", 1.0)
     names = {"wte.weight": "token_embd.weight", "wpe.weight": "position_embd.weight",
              "ln_f.weight": "output_norm.weight", "ln_f.bias": "output_norm.bias"}
     per_layer = {"ln_1": "attn_norm", "attn.c_attn": "attn_qkv", "attn.c_proj": "attn_output",
@@ -74,9 +81,10 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True)
     ap.add_argument("--build", required=True)
+    ap.add_argument("--only", action="append", help="make this case only (repeatable)")
     args = ap.parse_args()
-    from liyab_b200.config import GPT2Config
-    from liyab_b200.weights import random_tensors
+    from liyab_b200.config import parse_config
+    from liyab_b200.weights import read_tensor, safetensors_describe, write_random_model
 
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "reference_forward")
@@ -87,17 +95,21 @@ def main() -> int:
                "-lpthread", "-ldl"]
         subprocess.run(cmd, check=True)
         for name, (raw, seed, whole, singles) in CASES.items():
-            cfg = GPT2Config.parse(raw)
-            tensors = {k: v.numpy() for k, v in random_tensors(cfg, seed, "float32").items()}
+            if args.only and name not in args.only:
+                continue
+            raw = dict(raw, model_type="gpt2")
+            cfg = parse_config(raw)
+            st = os.path.join(write_random_model(os.path.join(tmp, name), raw, seed, "float32"), "model.safetensors")
+            tensors = {k: read_tensor(st, k, i) for k, i in safetensors_describe(st)["tensors"].items()}
             rng = np.random.default_rng(seed)
-            tokens = rng.integers(0, cfg.vocab_size, size=whole + singles).astype(np.int32)
+            tokens = rng.integers(0, cfg["vocab_size"], size=whole + singles).astype(np.int32)
             gguf_path = os.path.join(tmp, name + ".gguf")
             out_path = os.path.join(tmp, name + ".f32")
             write_gguf(gguf_path, raw, tensors)
             subprocess.run([exe, gguf_path, out_path, str(whole), *[str(t) for t in tokens]], check=True)
-            logits = np.fromfile(out_path, dtype="<f4").reshape(len(tokens), cfg.vocab_size)
+            logits = np.fromfile(out_path, dtype="<f4").reshape(len(tokens), cfg["vocab_size"])
             np.savez_compressed(os.path.join(HERE, name + ".npz"), tokens=tokens, whole=np.int32(whole),
-                                logits=logits, config_json=np.bytes_(__import__("json").dumps(cfg.to_dict())),
+                                logits=logits, config_json=np.bytes_(__import__("json").dumps(cfg)),
                                 **{"tensor:" + k: v for k, v in tensors.items()})
             print(f"{name}: {logits.shape} logits, max |logit| {np.abs(logits).max():.4f}")
     return 0

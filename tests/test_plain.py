@@ -11,8 +11,10 @@ import plain_gpt2 as plain
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 
 
-@pytest.mark.parametrize("name", ["gpt2_ref_a", "gpt2_ref_b"])
+@pytest.mark.parametrize("name", ["gpt2_ref_a", "gpt2_ref_b", "gpt2_ref_c"])
 def test_plain_matches_the_reference_engine(name):
+    """a and b: GPT-2 as the reference runs it.  c: `scale_attn_weights: false`, which the reference computes from
+    its per-model factor on the scores (gpt2.attention.scale = 1)."""
     z = np.load(os.path.join(GOLDEN, name + ".npz"))
     cfg = json.loads(bytes(z["config_json"]).decode())
     tensors = {k[len("tensor:"):]: z[k].astype(np.float64) for k in z.files if k.startswith("tensor:")}
