@@ -60,6 +60,13 @@ int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, in
                     const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
                     int token_tile, float* partial, int* counters, int n_splits, void* stream);
 int lb_gemm_tcgen05_token_tile(int M, int N);
+/* The split product as a fused projection of queries, keys and values (bias only): its second half also puts the
+ * features from q_dim on into the tokens' cache slots (bfloat16 pages of one layer; token i at slot_mapping[i];
+ * negative: nowhere), as lb_kv_append would.  Needs a real split: lb_gemm_tcgen05_splits(M, K, n_splits) > 1. */
+int lb_gemm_tcgen05_splits(int M, int K, int n_splits);
+int lb_gemm_tcgen05_kv(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, void* out,
+                       int64_t ldo, int M, int N, int K, float* partial, int n_splits, void* kv_cache,
+                       const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size, void* stream);
 /* The same product for 17 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
  * no second kernel): lb_gemm_rows_supports tells whether it takes the product.  With kv_cache given (bfloat16 pages
  * of one layer), features from q_dim on are the keys and values of a fused projection and are also written to the

@@ -272,10 +272,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
     }
 }
 
+// Where a split product is a fused projection of queries, keys and values, its second half also puts the keys and
+// values (the features from q_dim on) into the tokens' cache slots, as lb_kv_append would.
+struct FinishKv {
+    __nv_bfloat16* cache = nullptr;
+    const int32_t* slot_mapping = nullptr;
+    int q_dim = 0, n_kv_head = 0, head_dim = 0, page_size = 0;
+};
+
 // out[t, f] = act(sum over splits, in order, of partial[split][t][f] + bias[f]) + residual[t, f].
 template <typename TO>
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const float* residual,
-                                     int64_t ldr, TO* out, int64_t ldo, int M, int N, int n_splits, int act) {
+                                     int64_t ldr, TO* out, int64_t ldo, int M, int N, int n_splits, int act, const FinishKv kv) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= M * N) return;
     const int t = idx / N, f = idx - t * N;
@@ -288,6 +296,17 @@ __global__ void splitk_finish_kernel(const float* __restrict__ partial, const fl
     float y = lb_activate(acc + (bias != nullptr ? bias[f] : 0.0f), act);
     if (residual != nullptr) y += residual[(size_t)t * ldr + f];
     out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
+    if (kv.cache != nullptr && f >= kv.q_dim) {
+        const int slot = kv.slot_mapping[t];
+        if (slot >= 0) {
+            const int kv_dim = kv.n_kv_head * kv.head_dim, kvf = f - kv.q_dim, which = kvf >= kv_dim ? 1 : 0;
+            const int within = kvf - which * kv_dim, head = within / kv.head_dim, dd = within - head * kv.head_dim;
+            const int page = slot / kv.page_size, off = slot - page * kv.page_size;
+            const size_t plane = (size_t)kv.n_kv_head * kv.page_size * kv.head_dim;
+            kv.cache[(size_t)page * 2 * plane + (size_t)which * plane + ((size_t)head * kv.page_size + off) * kv.head_dim + dd] =
+                __float2bfloat16_rn(y);
+        }
+    }
 }
 
 // ------------------------------------------------------------------ host side
@@ -396,9 +415,9 @@ extern "C" int lb_gemm_tcgen05_token_tile(int M, int N) {
     return big_tiles >= 4 * 148 ? 256 : 128;
 }
 
-extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
-                               const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
-                               int token_tile, float* partial, int* counters, int n_splits, void* stream) {
+static int gemm_tcgen05_run(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                            const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                            int token_tile, float* partial, int* counters, int n_splits, const FinishKv& kv, void* stream) {
     LB_CHECK_ARG(M >= 0 && N > 0 && K > 0, "gemm_tcgen05: bad sizes M=%d N=%d K=%d", M, N, K);
     if (n_splits < 1) n_splits = 1;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0)
@@ -411,6 +430,7 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
     const int tile = token_tile > 0 ? token_tile : lb_gemm_tcgen05_token_tile(M, N);
     LB_CHECK_ARG(tile == 16 || tile == 32 || tile == 64 || tile == 128 || tile == 256, "gemm_tcgen05: token tile %d", tile);
     const bool tokens_on_lanes = tile >= 128;
+    LB_CHECK_ARG(kv.cache == nullptr || n_splits > 1, "gemm_tcgen05: the cache is filled from the second half of a split product only");
     if (n_splits > 1) {
         const int all_kb = (K + kBlockK - 1) / kBlockK;
         LB_CHECK_ARG(!tokens_on_lanes && partial != nullptr && n_splits <= 16,
@@ -438,7 +458,7 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
                                          act, vec_ok, partial, counters, n_splits, s);                            \
         if (rc != LB_OK || n_splits == 1) return rc;                                                              \
         splitk_finish_kernel<TO><<<(M * N + 255) / 256, 256, 0, s>>>(partial, bias, residual, ldr, (TO*)out, ldo, M, N, \
-                                                                    n_splits, act);                              \
+                                                                    n_splits, act, kv);                          \
         LB_CHECK_LAUNCH();                                                                                        \
         return LB_OK;                                                                                             \
     }
@@ -459,6 +479,41 @@ extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const 
         default: LB_GO(256, 4, true, float);
     }
 #undef LB_GO
+}
+
+extern "C" int lb_gemm_tcgen05(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                               const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
+                               int token_tile, float* partial, int* counters, int n_splits, void* stream) {
+    return gemm_tcgen05_run(out_dtype, A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, token_tile, partial, counters,
+                            n_splits, FinishKv{}, stream);
+}
+
+// How many ways lb_gemm_tcgen05 would really split K when asked for n_splits (no block is left without a k-block).
+extern "C" int lb_gemm_tcgen05_splits(int M, int K, int n_splits) {
+    if (M > 64 || n_splits <= 1) return 1;
+    const int all_kb = (K + kBlockK - 1) / kBlockK;
+    n_splits = n_splits > 16 ? 16 : n_splits;
+    n_splits = n_splits > all_kb ? all_kb : n_splits;
+    const int per = (all_kb + n_splits - 1) / n_splits;
+    return (all_kb + per - 1) / per;
+}
+
+extern "C" int lb_gemm_tcgen05_kv(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
+                                  void* out, int64_t ldo, int M, int N, int K, float* partial, int n_splits, void* kv_cache,
+                                  const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size, void* stream) {
+    LB_CHECK_ARG(kv_cache != nullptr && slot_mapping != nullptr && n_kv_head > 0 && head_dim > 0 && page_size > 0 && q_dim >= 0 &&
+                     q_dim + 2 * n_kv_head * head_dim == N,
+                 "gemm_tcgen05_kv: %d features are not [q %d | k | v] of %d heads of %d", N, q_dim, n_kv_head, head_dim);
+    if (lb_gemm_tcgen05_splits(M, K, n_splits) <= 1)
+        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_tcgen05_kv: needs a split of K (at most 64 tokens, more than one k-block)");
+    FinishKv kv;
+    kv.cache = static_cast<__nv_bfloat16*>(kv_cache);
+    kv.slot_mapping = slot_mapping;
+    kv.q_dim = q_dim;
+    kv.n_kv_head = n_kv_head;
+    kv.head_dim = head_dim;
+    kv.page_size = page_size;
+    return gemm_tcgen05_run(out_dtype, A, lda, W, ldw, bias, nullptr, 0, out, ldo, M, N, K, 0, 0, partial, nullptr, n_splits, kv, stream);
 }
 
 // Reads and clears the status word of the bounded waits (0: every wait so far completed).  Synchronises the device.

@@ -159,6 +159,8 @@ public:
                    kernels::gemm_persistent_kv_supports(w, qkv_out, dest)) {
             // Many tokens: the same from the tensor-core product's epilogue (only the queries go to `qkv_out`).
             kernels::gemm_persistent(ctx.stream(), h, w, qkv.bias, qkv_out, T, kernels::kNone, nullptr, &dest);
+        } else if (unit.write && dt == DType::BF16 && kernels::linear_with_cache(ctx.runtime, &ws, h, w, qkv.bias, qkv_out, T, dest)) {
+            // Few tokens, K split over blocks: the split product's second half filled the cache as well.
         } else {
             qkv.forward(ctx, h, qkv_out, T);
             if (unit.write)

@@ -163,6 +163,21 @@ void linear(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, co
     gemm_ffma(rt.stream, a, w, bias, out, m, act, residual);
 }
 
+bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m,
+                       const KvDestination& kv) {
+    if (ws == nullptr || m > 64 || !tcgen05_accepts(a, w)) return false;
+    const int n = static_cast<int>(w.dim(0)), k = static_cast<int>(w.dim(1));
+    if (m > 16 && k <= 1024 && gemm_rows_supports(a, w, m)) return false;          // that kernel has a cache epilogue of its own
+    const int splits = gemm_splits(m, n, k);
+    if (lb_gemm_tcgen05_splits(m, k, splits) <= 1) return false;
+    check_product(a, w, out, nullptr);
+    float* partial = static_cast<float*>(ws->flat("gemm.partial", static_cast<int64_t>(splits) * m * n, DType::F32));
+    check(lb_gemm_tcgen05_kv(code(out.dtype, "out"), a.data, a.stride, w.data, w.dim(1), bias, out.data, out.stride, m, n, k, partial, splits,
+                             kv.cache, kv.slot_mapping, kv.q_dim, kv.n_kv_head, kv.head_dim, kv.page_size, rt.stream),
+          "gemm_tcgen05_kv");
+    return true;
+}
+
 bool decode_scalar_supports(const AttentionShape& a) { return lb_decode_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
 bool decode_mma_supports(const AttentionShape& a) { return lb_decode_attention_mma_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }
 bool prefill_supports(const AttentionShape& a) { return lb_prefill_attention_supports(a.n_head, a.n_kv_head, a.head_dim, a.page_size) != 0; }

@@ -58,6 +58,11 @@ void gemm_persistent(cudaStream_t s, const Rows& a, const Tensor& w, const float
 // The product with the kernel chosen by type and size; `ws` lends scratch for products of few tokens.
 void linear(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m,
             int act, const Rows* residual);
+// A fused projection of few tokens (at most 64) whose keys and values should also reach the cache: true when the
+// chosen kernel did both (the split product's second half scatters them); false when nothing was launched and the
+// caller should run the product and the cache write separately.
+bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m,
+                       const KvDestination& kv);
 
 struct AttentionShape {
     int n_head = 0, n_kv_head = 0, head_dim = 0, page_size = 0;

