@@ -187,6 +187,11 @@ int lb_decode_stack_status_clear(void* stream);
 /* Writes a status word, as a kernel whose bounded wait ran out would (for tests of the host's handling). */
 int lb_gemm_tcgen05_status_set(int value);
 int lb_decode_stack_status_set(int value);
+/* Makes the NEXT launch meet a wait that nothing ends, once: the one-tile tcgen05 product leaves its
+ * accumulator-ready barrier unsignalled; the fused step's block 0 is not counted at its first grid barrier.
+ * The waits run to their limit (about two seconds), set the status word and the kernel returns. */
+int lb_gemm_tcgen05_withhold_next(int on);
+int lb_decode_stack_withhold_next(int on);
 
 #ifdef __cplusplus
 }

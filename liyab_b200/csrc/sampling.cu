@@ -122,8 +122,13 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     const int per = (vocab + kThreads - 1) / kThreads;
     const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
 
+    // A logit that is no number counts as the lowest: every row, even one of nothing else, gets an id inside the
+    // vocabulary (the next step reads the embedding table with it).
     ArgMax best{-CUDART_INF_F, 0x7fffffff};
-    for (int i = tid; i < vocab; i += kThreads) best = better(best, ArgMax{x[i], i});
+    for (int i = tid; i < vocab; i += kThreads) {
+        const float v = x[i];
+        best = better(best, ArgMax{v == v ? v : -CUDART_INF_F, i});
+    }
     const uint32_t my_max_key = best.i != 0x7fffffff ? order_key(best.v) : 0u;      // largest key among this thread's logits
     best = block_argmax(best, am_scratch);
     if (temp <= 0.0f) {

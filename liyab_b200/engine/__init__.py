@@ -276,6 +276,14 @@ def device_status() -> Tuple[int, int]:
     return words[0], words[1]
 
 
+def withhold_next(which: int, on: bool = True) -> None:
+    """The next launch of kernel family `which` (0: the one-tile tcgen05 product, 1: the one-kernel decode step) meets
+    a wait that nothing ends, once: its bounded wait runs to its limit (about two seconds), sets the status word and
+    the kernel returns.  `on=False` takes back an order that no launch has used.  For tests of that path; the device
+    stays usable."""
+    _capi.check(_capi.lib().lb_debug_withhold_next(which, 1 if on else 0))
+
+
 def set_device_status(which: int, value: int) -> None:
     """Writes a device status word as a kernel whose bounded wait ran out would (tests of the engine's handling)."""
     _capi.check(_capi.lib().lb_debug_set_device_status(which, value))
@@ -430,4 +438,4 @@ class Scheduler:
 
 
 __all__ = ["Engine", "EngineConfig", "GenerationResult", "GenerationStats", "generate", "StepEntry", "StepOutput", "Replayer",
-           "device_status", "set_device_status", "set_log", "Request", "PlannedEntry", "StepPlan", "Scheduler", "FINISH_REASONS"]
+           "device_status", "set_device_status", "withhold_next", "set_log", "Request", "PlannedEntry", "StepPlan", "Scheduler", "FINISH_REASONS"]

@@ -805,6 +805,14 @@ int32_t lb_debug_set_device_status(int32_t which, int32_t value) {
     });
 }
 
+int32_t lb_debug_withhold_next(int32_t which, int32_t on) {
+    return guarded([&] {
+        if (which == 0) kernels::check(lb_gemm_tcgen05_withhold_next(on), "withhold_next");
+        else if (which == 1) kernels::check(lb_decode_stack_withhold_next(on), "withhold_next");
+        else throw invalid_argument("wait {} does not exist (0: the tcgen05 product's accumulator barrier, 1: the fused step's grid barrier)", which);
+    });
+}
+
 static void to_c_bench(const BenchResult& b, lb_bench_result* out) {
     *out = lb_bench_result{b.ms_total, b.ms_per_step, b.wall_ms_per_step, b.mean_context, b.kernel_launches, b.graph_steps, b.fused_steps,
                            b.eager_steps, b.h2d_bytes_per_step, b.d2h_bytes_per_step, b.checksum};

@@ -284,6 +284,11 @@ LB_API int32_t lb_device_status(int32_t* words2);
  * when a step reports one (its requests end with LB_STATUS_INTERNAL, the words are cleared, a failing fused step is
  * switched off, the engine goes on). */
 LB_API int32_t lb_debug_set_device_status(int32_t which, int32_t value);
+/* With `on`, the next launch of kernel family `which` (0: the one-tile tcgen05 product, 1: the one-kernel decode
+ * step) meets a wait that nothing ends, once.  Its bounded wait runs to its limit (about two seconds), sets the
+ * status word and the kernel returns; the context stays usable.  Without `on`, takes an order back that no launch
+ * has used yet.  For tests of that path. */
+LB_API int32_t lb_debug_withhold_next(int32_t which, int32_t on);
 
 /* Measurements on a replayer, timed on the device with events around exactly the stated work (the reference's
  * liyab-bench and liyab-seq-bench are programs of the engine too: tools/liyab_bench.cpp, tools/liyab_seq_bench.cpp).

@@ -262,6 +262,32 @@ def test_greedy_takes_the_first_maximum(dev):
     assert out.tolist() == [77, 0]
 
 
+def test_sampling_of_rows_that_hold_no_numbers_stays_inside_the_vocabulary(dev):
+    """Logits that are no numbers (a model that overflowed) count as the lowest; whatever the row holds, the id
+    that comes out indexes the embedding table of the next step, so it lies inside the vocabulary."""
+    from liyab_b200 import ops
+    vocab = 3001
+    nan = float("nan")
+    logits = torch.full((6, vocab), nan, dtype=torch.float32, device=dev)
+    logits[1, 100] = -3.0
+    logits[2, :] = 1.0
+    logits[2, ::7] = nan
+    logits[2, 2222] = 4.0
+    logits[4, 5] = 2.0
+    logits[4, 9] = 2.5
+    logits[5, :] = float("-inf")
+    temp = torch.tensor([0, 0, 0, 0.8, 0.8, 0.8], dtype=torch.float32, device=dev)
+    top_k = torch.tensor([0, 0, 0, 0, 40, 0], dtype=torch.int32, device=dev)
+    top_p = torch.tensor([1, 1, 1, 0.9, 1.0, 0.5], dtype=torch.float32, device=dev)
+    u = torch.tensor([0.1, 0.2, 0.3, 0.4, 0.99, 0.6], dtype=torch.float64, device=dev)
+    out = torch.full((6,), -7, dtype=torch.int32, device=dev)
+    ops.sample(logits, 6, temp, top_k, top_p, u, out)
+    ids = out.tolist()
+    assert ids[:3] == [0, 100, 2222]
+    assert all(0 <= i < vocab for i in ids), ids
+    assert ids[4] in (5, 9)
+
+
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 @pytest.mark.parametrize("M,N,K,tile", [
     (1, 128, 64, 0), (8, 768, 768, 0), (5, 1000, 96, 0), (16, 130, 72, 0), (33, 50257, 256, 0), (64, 2304, 768, 0),
