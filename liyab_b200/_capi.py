@@ -100,6 +100,7 @@ _SIGNATURES = {
     "lb_replayer_set_tap": ([vp, TapCallback, vp], i32), "lb_replayer_timer_start": ([vp], i32),
     "lb_replayer_timer_stop": ([vp, P(f64)], i32), "lb_device_status": ([P(i32)], i32), "lb_debug_set_device_status": ([i32, i32], i32),
     "lb_debug_withhold_next": ([i32, i32], i32),
+    "lb_replayer_fused_stamps": ([vp, P(C.c_uint64), i32, P(i32)], i32),
     "lb_replayer_bench_decode": ([vp, i32, i32, i32, i32, u64, P(BenchResultC)], i32),
     "lb_replayer_bench_prefill": ([vp, i32, i32, i32, u64, P(BenchResultC)], i32),
 }

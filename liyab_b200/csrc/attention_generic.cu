@@ -23,6 +23,7 @@ namespace {
 
 constexpr int kTile = 32;       // keys per step, one per lane
 constexpr int kMaxHeadDim = 256;
+constexpr long long kFewPairs = 1024;   // up to this many (token, head) pairs take the latency-arranged float32 kernel
 
 // Four consecutive elements as floats with one load (the address is aligned to the four of them).
 __device__ __forceinline__ float4 lb_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -187,6 +188,150 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
     }
 }
 
+// ---- float32, few (token, head) pairs: the same sums in the same order, arranged around memory latency --------
+//
+// A decode step of a few requests launches fewer blocks than the GPU has SMs, and each warp's chain of round
+// trips to memory sets the pace.  Here keys and values have a buffer each and travel by asynchronous 16-byte copies
+// (no registers in between): a tile's values are in flight while its scores are computed, the next tile's keys
+// while the values are summed, and the page of the next tile is looked up a tile ahead.  Rows lie head_dim + 4
+// floats apart, so a lane reads its key's row as 16-byte pieces without meeting a bank twice.  Every product and
+// sum is the one paged_attention_generic_kernel makes, in its order: the two kernels agree bit for bit.
+
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+
+// The rows of up to 32 keys (lane i knows the row of key i: `base`, negative if there is none) -> the tile, as copies in flight.
+__device__ __forceinline__ void tile_in_flight(const float* __restrict__ cache, long long base, long long offset, float* tile,
+                                               int tile_stride, int head_dim, int lane) {
+    const int quads = head_dim / 4;
+#pragma unroll 4
+    for (int key = 0; key < kTile; ++key) {
+        const long long b = __shfl_sync(0xffffffffu, base, key);
+        if (b >= 0)
+            for (int c = lane; c < quads; c += 32) cp_async16(tile + key * tile_stride + 4 * c, cache + b + offset + 4 * c);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(256, 1)
+paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, const float* __restrict__ cache,
+                               const int32_t* __restrict__ tok_seq, const int32_t* __restrict__ positions,
+                               const int32_t* __restrict__ block_table, int table_stride, float* __restrict__ out,
+                               int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
+                               int page_size, float scale, int window) {
+    extern __shared__ __align__(16) float smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+    const int pair = blockIdx.x;
+    const int t = pair / n_head, h = pair - t * n_head;
+    const int kvh = h / (n_head / n_kv_head);
+    const int pos = positions[t];
+    const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
+
+    const int tile_stride = head_dim + 4;
+    float* q_s = smem + (size_t)warp * (head_dim + 2 * kTile * tile_stride + kTile);
+    float* k_tile = q_s + head_dim;
+    float* v_tile = k_tile + kTile * tile_stride;
+    float* p_s = v_tile + kTile * tile_stride;
+
+    const size_t plane = (size_t)n_kv_head * page_size * head_dim;
+    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int step = n_warps * kTile;
+    auto row_of = [&](int j0) -> long long {      // this lane's key of the tile that starts at j0
+        const int j = j0 + lane;
+        if (j0 > pos || j > pos) return -1;
+        const int page = __ldg(table + j / page_size);
+        return (long long)page * 2 * (long long)plane + ((long long)kvh * page_size + (j % page_size)) * head_dim;
+    };
+    int j0 = first + warp * kTile;
+    long long base = row_of(j0);
+    if (j0 <= pos) {
+        tile_in_flight(cache, base, 0, k_tile, tile_stride, head_dim, lane);
+        tile_in_flight(cache, base, (long long)plane, v_tile, tile_stride, head_dim, lane);
+    }
+    const float* q_row = q + (size_t)t * q_stride + (size_t)h * head_dim;
+    for (int d = lane; d < head_dim; d += 32) q_s[d] = q_row[d];
+
+    float m = -CUDART_INF_F, l = 0.0f;
+    float acc[kMaxHeadDim / 32];
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.0f;
+
+    for (; j0 <= pos; j0 += step) {
+        const int n_keys = min(kTile, pos + 1 - j0);
+        const bool more = j0 + step <= pos;
+        const long long next_base = row_of(j0 + step);           // the next tile's page, asked for a tile ahead
+        asm volatile("cp.async.wait_group 1;" ::: "memory");     // this tile's keys have landed (its values may not have)
+        __syncwarp();
+        float s = -CUDART_INF_F;
+        if (lane < n_keys) {
+            float dot = 0.0f;
+            const float4* krow = reinterpret_cast<const float4*>(k_tile + lane * tile_stride);
+            const float4* qv = reinterpret_cast<const float4*>(q_s);
+            for (int c = 0; c < head_dim / 4; ++c) {
+                const float4 kq = krow[c], qq = qv[c];
+                dot = fmaf(qq.x, kq.x, dot);
+                dot = fmaf(qq.y, kq.y, dot);
+                dot = fmaf(qq.z, kq.z, dot);
+                dot = fmaf(qq.w, kq.w, dot);
+            }
+            s = dot * scale;
+        }
+        const float m_new = fmaxf(m, lb_warp_max(s));
+        const float p = lane < n_keys ? expf(s - m_new) : 0.0f;
+        const float corr = expf(m - m_new);      // exp(-inf) = 0 on the first tile
+        l = l * corr + lb_warp_sum(p);
+        m = m_new;
+        p_s[lane] = p;
+        __syncwarp();                            // every lane has read the keys: the next tile's go into the buffer
+        if (more) tile_in_flight(cache, next_base, 0, k_tile, tile_stride, head_dim, lane);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");     // this tile's values have landed
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < head_dim) {
+                float o = acc[i] * corr;
+                for (int j = 0; j < n_keys; ++j) o = fmaf(p_s[j], v_tile[j * tile_stride + d], o);
+                acc[i] = o;
+            }
+        }
+        __syncwarp();
+        if (more) tile_in_flight(cache, next_base, (long long)plane, v_tile, tile_stride, head_dim, lane);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    float* merge = smem + (size_t)n_warps * (head_dim + 2 * kTile * tile_stride + kTile);
+    float* mine = merge + (size_t)warp * (head_dim + 2);
+    if (lane == 0) { mine[0] = m; mine[1] = l; }
+#pragma unroll
+    for (int i = 0; i < kMaxHeadDim / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < head_dim) mine[2 + d] = acc[i];
+    }
+    __syncthreads();
+    float* o_row = out + (size_t)t * out_stride + (size_t)h * head_dim;
+    for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
+        float top = -CUDART_INF_F;
+        for (int w = 0; w < n_warps; ++w) top = fmaxf(top, merge[(size_t)w * (head_dim + 2)]);
+        float total = 0.0f, o = 0.0f;
+        for (int w = 0; w < n_warps; ++w) {
+            const float* st = merge + (size_t)w * (head_dim + 2);
+            const float f = expf(st[0] - top);      // exp(-inf) = 0 for a warp without keys
+            total = fmaf(st[1], f, total);
+            o = fmaf(st[2 + d], f, o);
+        }
+        o_row[d] = o / total;
+    }
+}
+
+// Whether a launch takes the kernel above: float32, 16-byte rows, few enough pairs that latency and not throughput
+// sets the time, and a block's two tiles per warp fit the shared memory of an SM.
+size_t few_smem(int warps, int head_dim) {
+    return (size_t)warps * (head_dim + 2 * kTile * (head_dim + 4) + kTile + head_dim + 2) * sizeof(float);
+}
+
 // Warps per block, by the head size alone: eight while three such blocks fit the shared memory of an SM (up to head size 64), fewer for larger heads.
 int warps_for(int head_dim) {
     const size_t per_warp = (size_t)(head_dim + kTile * (head_dim + 1) + kTile + head_dim + 2) * sizeof(float);
@@ -209,6 +354,22 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* to
     }
     const long long pairs = (long long)n_tokens * n_head;
     LB_CHECK_ARG(pairs <= 2147483647ll, "attention: %lld (token, head) pairs are too many for one launch", pairs);
+    if constexpr (sizeof(T) == 4) {
+        // Few pairs: the kernel arranged around latency (the same warps per block, so the same sums).
+        const size_t few = few_smem(warps, head_dim);
+        if (pairs <= kFewPairs && head_dim % 4 == 0 && q_stride % 4 == 0 && few <= 227 * 1024 && ((uintptr_t)cache & 15) == 0) {
+            static size_t few_configured = 0;
+            if (few > few_configured) {
+                LB_CHECK_CUDA(cudaFuncSetAttribute(paged_attention_f32_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few));
+                few_configured = few;
+            }
+            paged_attention_f32_few_kernel<<<(unsigned)pairs, warps * 32, few, s>>>(
+                (const float*)q, q_stride, (const float*)cache, tok_seq, positions, block_table, table_stride, (float*)out, out_stride,
+                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);
+            LB_CHECK_LAUNCH();
+            return LB_OK;
+        }
+    }
     paged_attention_generic_kernel<T><<<(unsigned)pairs, warps * 32, smem, s>>>(
         (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
         n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);

@@ -140,8 +140,9 @@ gemm_ffma_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W
 // ---- up to 16 tokens: the weights are read once, everything else is arranged around that -----------------
 
 constexpr int kSkinnyFeatures = 8;       // features per block
-constexpr int kSkinnyTokens = 16;
-constexpr int kSkinnyPitch = kSkinnyTokens * kChunk + 8;      // floats between the buffers of a warp's four slots: banks 8 apart
+constexpr int kSkinnyTokens = 16;        // the most tokens; the kernel is also built for 8 (half the products and buffers)
+// Floats between the buffers of a warp's four slots: banks 8 apart.
+__host__ __device__ constexpr int skinny_pitch(int tokens) { return tokens * kChunk + 8; }
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
     const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
@@ -179,12 +180,14 @@ struct WeightChunk<__nv_bfloat16> {
 };
 
 // K, lda and ldw are multiples of the 16-byte vector (4 floats, 8 bfloat16) and the bases 16-byte aligned.
-template <typename TI, typename TO>
+// The block has as many warps as the reduction length has groups of chunks to give them (four groups a warp).
+template <typename TI, typename TO, int TOKENS>
 __global__ void __launch_bounds__(256)
 gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W, int64_t ldw,
                         const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M,
                         int N, int K, int act) {
     constexpr int VEC = 16 / (int)sizeof(TI);                   // elements per 16-byte piece
+    constexpr int kPitch = skinny_pitch(TOKENS);
     extern __shared__ __align__(16) float skinny_smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int fi = lane & 7, slot = lane >> 3;                   // feature within the block, chunk slot within the warp
@@ -193,11 +196,11 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
     const int n_chunks = (K + kChunk - 1) / kChunk, G = chunks_per_group(K);
     const int c_begin = min(n_chunks, group * G), c_end = min(n_chunks, c_begin + G);
     // The warp's buffers: [slot][token][64] floats of activations (as stored: float or bfloat16 widened on use).
-    float* my_buf = skinny_smem + (size_t)warp * 4 * kSkinnyPitch;
+    float* my_buf = skinny_smem + (size_t)warp * 4 * kPitch;
     const TI* w_row = W + (size_t)min(f, N - 1) * ldw;
-    float grp[kSkinnyTokens];
+    float grp[TOKENS];
 #pragma unroll
-    for (int r = 0; r < kSkinnyTokens; ++r) grp[r] = 0.0f;
+    for (int r = 0; r < TOKENS; ++r) grp[r] = 0.0f;
     for (int ci = 0; ci < G; ++ci) {                             // the same trip count for the whole warp
         const int c = c_begin + ci;
         const bool live = c < c_end;
@@ -206,27 +209,27 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
         w.load(w_row, k0, K, live && f < N);
         // The warp's four slots bring their chunks of the tokens' activations: slot s2's chunk, token r, piece q.
         __syncwarp();
-        for (int idx = lane; idx < 4 * kSkinnyTokens * (kChunk / VEC); idx += 32) {
-            const int s2 = idx / (kSkinnyTokens * (kChunk / VEC)), rem = idx - s2 * (kSkinnyTokens * (kChunk / VEC));
+        for (int idx = lane; idx < 4 * TOKENS * (kChunk / VEC); idx += 32) {
+            const int s2 = idx / (TOKENS * (kChunk / VEC)), rem = idx - s2 * (TOKENS * (kChunk / VEC));
             const int r = rem / (kChunk / VEC), q = rem - r * (kChunk / VEC);
             const int c2 = min(n_chunks, (warp * 4 + s2) * G) + ci;
             const int kk = c2 * kChunk + q * VEC;
             const bool valid = c2 < min(n_chunks, min(n_chunks, (warp * 4 + s2) * G) + G) && r < M && kk < K;
-            TI* dst = reinterpret_cast<TI*>(my_buf + (size_t)s2 * kSkinnyPitch) + r * kChunk + q * VEC;
+            TI* dst = reinterpret_cast<TI*>(my_buf + (size_t)s2 * kPitch) + r * kChunk + q * VEC;
             cp_async16_zfill(dst, A + (size_t)(valid ? r : 0) * lda + (valid ? kk : 0), valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncwarp();
-        const TI* a_s = reinterpret_cast<const TI*>(my_buf + (size_t)slot * kSkinnyPitch);
-        float acc[kSkinnyTokens];
+        const TI* a_s = reinterpret_cast<const TI*>(my_buf + (size_t)slot * kPitch);
+        float acc[TOKENS];
 #pragma unroll
-        for (int r = 0; r < kSkinnyTokens; ++r) acc[r] = 0.0f;
+        for (int r = 0; r < TOKENS; ++r) acc[r] = 0.0f;
 #pragma unroll
         for (int i = 0; i < kChunk / 4; ++i) {
             const float4 wq = w.quad(i);
 #pragma unroll
-            for (int r = 0; r < kSkinnyTokens; ++r) {
+            for (int r = 0; r < TOKENS; ++r) {
                 float4 aq;
                 if constexpr (sizeof(TI) == 4) {
                     aq = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(a_s) + r * kChunk + 4 * i);
@@ -243,22 +246,22 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
         }
         if (live) {
 #pragma unroll
-            for (int r = 0; r < kSkinnyTokens; ++r) grp[r] = ci == 0 ? acc[r] : grp[r] + acc[r];
+            for (int r = 0; r < TOKENS; ++r) grp[r] = ci == 0 ? acc[r] : grp[r] + acc[r];
         }
     }
     // The group sums of the block meet in shared memory (over the activation buffers) and are added in ascending order.
     __syncthreads();
     float* red = skinny_smem;                                    // [group][token][feature]
 #pragma unroll
-    for (int r = 0; r < kSkinnyTokens; ++r) red[(group * kSkinnyTokens + r) * kSkinnyFeatures + fi] = grp[r];
+    for (int r = 0; r < TOKENS; ++r) red[(group * TOKENS + r) * kSkinnyFeatures + fi] = grp[r];
     __syncthreads();
-    if (threadIdx.x < kSkinnyTokens * kSkinnyFeatures) {
-        const int r = threadIdx.x / kSkinnyFeatures, ff = threadIdx.x % kSkinnyFeatures;
+    for (int idx = threadIdx.x; idx < TOKENS * kSkinnyFeatures; idx += blockDim.x) {
+        const int r = idx / kSkinnyFeatures, ff = idx % kSkinnyFeatures;
         const int gn = blockIdx.x * kSkinnyFeatures + ff;
         if (r < M && gn < N) {
             const int n_groups = (n_chunks + G - 1) / G;
-            float v = red[(0 * kSkinnyTokens + r) * kSkinnyFeatures + ff];
-            for (int g2 = 1; g2 < n_groups; ++g2) v += red[(g2 * kSkinnyTokens + r) * kSkinnyFeatures + ff];
+            float v = red[(0 * TOKENS + r) * kSkinnyFeatures + ff];
+            for (int g2 = 1; g2 < n_groups; ++g2) v += red[(g2 * TOKENS + r) * kSkinnyFeatures + ff];
             if (bias != nullptr) v += bias[gn];
             v = lb_activate(v, act);
             if (residual != nullptr) v += residual[(size_t)r * ldr + gn];
@@ -273,15 +276,32 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
     constexpr int VEC = 16 / (int)sizeof(TI);
     const bool vectors = K % VEC == 0 && lda % VEC == 0 && ldw % VEC == 0 && ((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0;
     if (M <= kSkinnyTokens && vectors) {
-        // Few tokens: bound by reading the weights once (see the head of the file).
-        const size_t smem = (size_t)8 * 4 * kSkinnyPitch * sizeof(float);
-        static bool configured = false;
-        if (!configured) {
-            LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_ffma_skinny_kernel<TI, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            configured = true;
+        // Few tokens: bound by reading the weights once (see the head of the file).  A warp serves four groups of
+        // chunks, so a short reduction length makes small blocks, of which several share an SM.
+        const int n_chunks = (K + kChunk - 1) / kChunk, per_group = chunks_per_group(K);
+        const int n_groups = (n_chunks + per_group - 1) / per_group, warps = (n_groups + 3) / 4;
+        const dim3 grid((N + kSkinnyFeatures - 1) / kSkinnyFeatures);
+        if (M <= 8) {
+            const size_t smem = (size_t)warps * 4 * skinny_pitch(8) * sizeof(float);
+            static bool configured = false;
+            if (!configured) {
+                LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_ffma_skinny_kernel<TI, TO, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)(8 * 4 * skinny_pitch(8) * sizeof(float))));
+                configured = true;
+            }
+            gemm_ffma_skinny_kernel<TI, TO, 8><<<grid, warps * 32, smem, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
+                                                                             (TO*)out, ldo, M, N, K, act);
+        } else {
+            const size_t smem = (size_t)warps * 4 * skinny_pitch(16) * sizeof(float);
+            static bool configured = false;
+            if (!configured) {
+                LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_ffma_skinny_kernel<TI, TO, 16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   (int)(8 * 4 * skinny_pitch(16) * sizeof(float))));
+                configured = true;
+            }
+            gemm_ffma_skinny_kernel<TI, TO, 16><<<grid, warps * 32, smem, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
+                                                                              (TO*)out, ldo, M, N, K, act);
         }
-        gemm_ffma_skinny_kernel<TI, TO><<<(N + kSkinnyFeatures - 1) / kSkinnyFeatures, 256, smem, s>>>(
-            (const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act);
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64);
         gemm_ffma_kernel<TI, TO, 64, 64, 16, 4, 4><<<grid, 256, 0, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias,

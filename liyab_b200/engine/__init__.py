@@ -229,6 +229,17 @@ class Replayer:
     def set(self, option: str, value: int) -> None:
         _capi.check(self._lib.lb_replayer_set(self._h, _capi.b(option), int(value)))
 
+    def fused_stamps(self) -> np.ndarray:
+        """The last one-kernel decode step's time stamps in ns (after `set("fused_stamps", 1)`): entry b = block 0 left
+        grid barrier b; 128 + 8 * layer + mark = marks inside the phases; 256 + 160 * j + block = every block's
+        arrival at barrier j of layer 5.  Entries never written are 0."""
+        n = C.c_int32(0)
+        _capi.check(self._lib.lb_replayer_fused_stamps(self._h, None, 0, C.byref(n)))
+        out = np.zeros(n.value, dtype=np.uint64)
+        if n.value:
+            _capi.check(self._lib.lb_replayer_fused_stamps(self._h, out.ctypes.data_as(C.POINTER(C.c_uint64)), n.value, C.byref(n)))
+        return out
+
     def set_tap(self, fn: Optional[Callable[[str, np.ndarray], None]]) -> None:
         """`fn(name, rows)` is called with every part's output (float32 on the host) of the following steps."""
         if fn is None:

@@ -725,7 +725,23 @@ int32_t lb_replayer_set(lb_replayer* r, const char* option, int32_t value) {
         if (o == "cuda_graphs") r->replayer->stepper->cuda_graphs = value != 0;
         else if (o == "fused_decode" && value == 0) r->replayer->stepper->disable_fused();
         else if (o == "reserve_rows") r->replayer->stepper->workspace.reserve_rows(value);
+        else if (o == "fused_stamps") {
+            if (r->replayer->stepper->fused() == nullptr) throw invalid_argument("this replayer has no one-kernel decode step to take stamps from");
+            r->replayer->stepper->fused()->record_stamps(value != 0);
+        }
         else throw invalid_argument("unknown replayer option '{}'", o);
+    });
+}
+
+int32_t lb_replayer_fused_stamps(lb_replayer* r, uint64_t* out, int32_t capacity, int32_t* n) {
+    return guarded([&] {
+        need(r, "replayer");
+        need(n, "n");
+        std::vector<uint64_t> stamps;
+        if (r->replayer->stepper->fused() != nullptr) stamps = r->replayer->stepper->fused()->stamps();
+        *n = static_cast<int32_t>(stamps.size());
+        if (out != nullptr)
+            for (int32_t i = 0; i < std::min<int32_t>(capacity, *n); ++i) out[i] = stamps[static_cast<size_t>(i)];
     });
 }
 

@@ -112,6 +112,16 @@ void FusedDecodeStack::splits(int n_tokens, int* n_splits, int* unit_warps) cons
     *unit_warps = 4;
 }
 
+void FusedDecodeStack::record_stamps(bool on) {
+    stamps_ = on ? DeviceBuffer(kStamps * sizeof(uint64_t), true) : DeviceBuffer();
+}
+
+std::vector<uint64_t> FusedDecodeStack::stamps() const {
+    std::vector<uint64_t> out(stamps_.data() != nullptr ? kStamps : 0);
+    if (!out.empty()) LIYAB_CUDA(cudaMemcpy(out.data(), stamps_.data(), out.size() * sizeof(uint64_t), cudaMemcpyDeviceToHost));
+    return out;
+}
+
 Rows FusedDecodeStack::run(StepContext& ctx) {
     const ModelSpec& spec = model_->spec;
     const int B = ctx.n_tokens;
@@ -124,8 +134,8 @@ Rows FusedDecodeStack::run(StepContext& ctx) {
                                    model_->head_weight.data, model_->head_bias, ctx.tokens, ctx.positions, view.block_table,
                                    view.table_width, view.slot_mapping, cache_->page_size, static_cast<float*>(x_.data()), q_.data(),
                                    att_.data(), inner_.data(), static_cast<float*>(partial_.data()), static_cast<int*>(counters_.data()),
-                                   static_cast<float*>(logits_.data()), barrier, max_k_, head_dim_, n_splits, unit_warps, nullptr,
-                                   ctx.stream()),
+                                   static_cast<float*>(logits_.data()), barrier, max_k_, head_dim_, n_splits, unit_warps,
+                                   static_cast<unsigned long long*>(stamps_.data()), ctx.stream()),
                    "decode_stack");
     ++launches_;
     return Rows{logits_.data(), DType::F32, B, spec.vocab_size(), spec.vocab_size()};

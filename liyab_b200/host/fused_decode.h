@@ -14,6 +14,7 @@
 #pragma once
 
 #include <memory>
+#include <vector>
 
 #include "decoder.h"
 
@@ -28,6 +29,12 @@ public:
     bool accepts(int n_tokens) const { return n_tokens >= 1 && n_tokens <= kMaxTokens; }
     // Computes the logits of a decode step ([n_tokens, vocab] float32, valid until the next run).
     Rows run(StepContext& ctx);
+    // Time stamps from inside the kernel (a measuring aid): once switched on, every launch has block 0 write the
+    // global timer after each grid barrier (entry = barrier number) and at the marks inside the phases, and every
+    // block its arrival at the five barriers of one middle layer; `stamps` copies the last launch's out.
+    static constexpr size_t kStamps = 2048;
+    void record_stamps(bool on);
+    std::vector<uint64_t> stamps() const;
 
 private:
     FusedDecodeStack() = default;
@@ -40,7 +47,7 @@ private:
     const float* lnf_w_ = nullptr;
     const float* lnf_b_ = nullptr;
     float lnf_eps_ = 0.0f;
-    DeviceBuffer layers_, x_, q_, att_, inner_, logits_, partial_, counters_, barrier_;
+    DeviceBuffer layers_, x_, q_, att_, inner_, logits_, partial_, counters_, barrier_, stamps_;
     uint64_t launches_ = 0;
 };
 

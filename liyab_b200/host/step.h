@@ -81,6 +81,7 @@ public:
     int max_positions;
     bool has_fused() const { return fused_ != nullptr; }
     void disable_fused() { fused_.reset(); }
+    FusedDecodeStack* fused() { return fused_.get(); }
     // counters
     uint64_t steps = 0, graph_steps = 0, fused_steps = 0, eager_steps = 0, tokens_run = 0, graphs_captured = 0;
 

@@ -271,6 +271,11 @@ LB_API int32_t lb_replayer_step(lb_replayer* r, size_t n_entries, const int64_t*
 /* Options at run time: "cuda_graphs" 0/1, "fused_decode" 0 (cannot be switched back on). */
 LB_API int32_t lb_replayer_set(lb_replayer* r, const char* option, int32_t value);
 /* {"steps", "graph_steps", "fused_steps", "eager_steps", "graphs_captured", "tokens_run", "kernel_launches"} */
+/* Time stamps from inside the one-kernel decode step (a measuring aid): after lb_replayer_set(r, "fused_stamps", 1)
+ * every such step has block 0 write the device's global timer (ns) after each grid barrier (entry = the barrier's
+ * number, from 1), at marks inside the phases (entries 128 + 8 * layer + mark) and every block its arrival at the five
+ * barriers of layer 5 (entries 256 + 160 * barrier + block).  Copies the last step's stamps out; *n = how many exist. */
+LB_API int32_t lb_replayer_fused_stamps(lb_replayer* r, uint64_t* out, int32_t capacity, int32_t* n);
 LB_API int32_t lb_replayer_counters(const lb_replayer* r, char* buffer, size_t size, size_t* needed);
 /* Every part's output of the following steps is handed to `tap` as float32 rows on the host (NULL removes it). */
 typedef void (*lb_tap_callback)(const char* name, const float* rows, int32_t n_rows, int32_t n_cols, void* user_data);

@@ -163,6 +163,20 @@ def case_decode_step(args) -> None:
     path = "fused" if r["fused_steps"] else ("graph" if r["graph_steps"] else "parts")
     print(f"decode-step size={args.size} batch={B} layers={len(rep.info['spec']['layers'])} context~{r['mean_context']:.0f} path={path}: "
           f"{r['ms_per_step'] * 1e3:.1f} us per step, {B / r['ms_per_step'] * 1e3:.0f} tokens/s, {r['kernel_launches'] // args.reps} launches a step")
+    if args.stamps and r["fused_steps"]:
+        # Where the one-kernel step's time goes: the five barriers of layer 5 (numbers 27..31), all blocks' arrivals.
+        rep.set("fused_stamps", 1)
+        rep.bench_decode(B, args.context, 3, 1)
+        t = rep.fused_stamps().astype(np.float64) / 1e3
+        n_blocks = int(np.count_nonzero(t[256:256 + 160]))
+        last_barrier = int(np.flatnonzero(t[:126]).max())
+        print(f"  whole kernel after its first barrier: {t[last_barrier] - t[1]:.1f} us over {last_barrier - 1} barriers; head {t[127] - t[126]:.1f} us")
+        names = ["LayerNorm + projection", "attention", "output projection", "LayerNorm + up", "down"]
+        for j, name in enumerate(names):
+            arrive = np.sort(t[256 + 160 * j:256 + 160 * j + n_blocks])
+            before, after = t[26 + j], t[27 + j]
+            print(f"  layer 5 {name:>22}: work {arrive[0] - before:5.2f} / {np.median(arrive) - before:5.2f} / {arrive[-1] - before:5.2f} us "
+                  f"(first / median / last block to arrive), barrier left {after - arrive[-1]:5.2f} us after the last arrival, phase {after - before:5.2f} us")
 
 
 def case_prefill_step(args) -> None:
@@ -225,6 +239,7 @@ def main(argv=None) -> int:
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true", help="no captured graphs")
         p.add_argument("--no-fused", action="store_true", help="not the one-kernel decode step")
+        p.add_argument("--stamps", action="store_true", help="decode-step: per-phase times from inside the one-kernel step")
     args = ap.parse_args(argv)
     {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
      "prefill-step": case_prefill_step}[args.case](args)

@@ -157,6 +157,29 @@ def test_paged_attention_generic(dev, dtype, n_head, n_kv_head, head_dim, page_s
     assert (out.double().cpu() - ref).abs().max().item() < tol
 
 
+@pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window", [(4, 2, 64, 16, 0), (3, 3, 48, 32, 70), (2, 1, 128, 16, 0)])
+def test_float32_attention_of_few_and_of_many_pairs_agree_bit_for_bit(dev, n_head, n_kv_head, head_dim, page_size, window):
+    """Launches of few (token, head) pairs take a kernel arranged around memory latency, larger ones the plain one;
+    both make the same sums in the same order, so a token's output does not depend on how many others ran beside it."""
+    from liyab_b200 import ops
+    lens, q_lens = [330, 210, 97], [330, 210, 97]
+    scale = 1.0 / math.sqrt(head_dim)
+    q, cache, tok_seq, positions, table, refs = _paged_case(dev, torch.float32, n_head, n_kv_head, head_dim, page_size, lens,
+                                                            q_lens, seed=3 * head_dim)
+    n = q.shape[0]
+    assert n * n_head > 1024
+    whole = torch.empty_like(q)
+    ops.paged_attention_generic(q, cache, tok_seq, positions, table, whole, n, n_head, n_kv_head, head_dim, page_size, scale, window)
+    ref = _attention_reference(refs, n_head, n_kv_head, scale, window)
+    assert (whole.double().cpu() - ref).abs().max().item() < 2e-5
+    for lo, hi in ((0, 1), (300, 340), (529, 540), (n - 64, n)):
+        assert (hi - lo) * n_head <= 1024
+        part = torch.empty((hi - lo, q.shape[1]), dtype=torch.float32, device=dev)
+        ops.paged_attention_generic(q[lo:hi].contiguous(), cache, tok_seq[lo:hi].contiguous(), positions[lo:hi].contiguous(), table,
+                                    part, hi - lo, n_head, n_kv_head, head_dim, page_size, scale, window)
+        assert torch.equal(part, whole[lo:hi]), (lo, hi)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_a_far_key(dev, dtype):
     """One key far back, scaled so that its score stands out among hundreds: a kernel that drops a page,
