@@ -201,15 +201,22 @@ __device__ __forceinline__ void cp_async16(float* dst, const float* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
 }
 
-// The rows of up to 32 keys (lane i knows the row of key i: `base`, negative if there is none) -> the tile, as copies in flight.
-__device__ __forceinline__ void tile_in_flight(const float* __restrict__ cache, long long base, long long offset, float* tile,
-                                               int tile_stride, int head_dim, int lane) {
-    const int quads = head_dim / 4;
-#pragma unroll 4
-    for (int key = 0; key < kTile; ++key) {
-        const long long b = __shfl_sync(0xffffffffu, base, key);
-        if (b >= 0)
-            for (int c = lane; c < quads; c += 32) cp_async16(tile + key * tile_stride + 4 * c, cache + b + offset + 4 * c);
+// Which 16-byte pieces of a 32-key tile a lane copies: piece lane + 32 u, u = 0 .. head_dim / 4 - 1, of the tile's
+// [key][piece of the row]; (key, piece) advance by fixed steps, so nothing is divided inside the loop.
+struct PieceWalk {
+    int key0, c0, dk, dc, quads;
+};
+
+// The rows of up to 32 keys (row_s[i]: where key i's row starts, negative if there is none) -> the tile, as copies in flight.
+__device__ __forceinline__ void tile_in_flight(const float* __restrict__ cache, const long long* row_s, long long offset,
+                                               float* tile, int tile_stride, const PieceWalk& w) {
+    int key = w.key0, c = w.c0;
+    for (int u = 0; u < w.quads; ++u) {
+        const long long b = row_s[key];
+        if (b >= 0) cp_async16(tile + key * tile_stride + 4 * c, cache + b + offset + 4 * c);
+        key += w.dk;
+        c += w.dc;
+        if (c >= w.quads) { c -= w.quads; ++key; }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
 }
@@ -229,10 +236,13 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
     const int32_t* table = block_table + (size_t)tok_seq[t] * table_stride;
 
     const int tile_stride = head_dim + 4;
-    float* q_s = smem + (size_t)warp * (head_dim + 2 * kTile * tile_stride + kTile);
+    float* q_s = smem + (size_t)warp * (head_dim + 2 * kTile * tile_stride + kTile + 2 * kTile);
     float* k_tile = q_s + head_dim;
     float* v_tile = k_tile + kTile * tile_stride;
     float* p_s = v_tile + kTile * tile_stride;
+    long long* row_s = reinterpret_cast<long long*>(p_s + kTile);      // where each key's row of the coming tile starts
+    const int quads = head_dim / 4;
+    const PieceWalk walk{lane / quads, lane % quads, 32 / quads, 32 % quads, quads};
 
     const size_t plane = (size_t)n_kv_head * page_size * head_dim;
     const int first = window > 0 ? max(0, pos - window + 1) : 0;
@@ -244,10 +254,11 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
         return (long long)page * 2 * (long long)plane + ((long long)kvh * page_size + (j % page_size)) * head_dim;
     };
     int j0 = first + warp * kTile;
-    long long base = row_of(j0);
+    row_s[lane] = row_of(j0);
+    __syncwarp();
     if (j0 <= pos) {
-        tile_in_flight(cache, base, 0, k_tile, tile_stride, head_dim, lane);
-        tile_in_flight(cache, base, (long long)plane, v_tile, tile_stride, head_dim, lane);
+        tile_in_flight(cache, row_s, 0, k_tile, tile_stride, walk);
+        tile_in_flight(cache, row_s, (long long)plane, v_tile, tile_stride, walk);
     }
     const float* q_row = q + (size_t)t * q_stride + (size_t)h * head_dim;
     for (int d = lane; d < head_dim; d += 32) q_s[d] = q_row[d];
@@ -283,26 +294,30 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
         l = l * corr + lb_warp_sum(p);
         m = m_new;
         p_s[lane] = p;
+        row_s[lane] = next_base;                 // this tile's copies were all issued: the rows of the next one
         __syncwarp();                            // every lane has read the keys: the next tile's go into the buffer
-        if (more) tile_in_flight(cache, next_base, 0, k_tile, tile_stride, head_dim, lane);
+        if (more) tile_in_flight(cache, row_s, 0, k_tile, tile_stride, walk);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 1;" ::: "memory");     // this tile's values have landed
         __syncwarp();
+        // Each element's sum runs over the keys in ascending order, as in the plain kernel; the elements of a lane
+        // advance side by side and share the weight they read.
 #pragma unroll
-        for (int i = 0; i < kMaxHeadDim / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < head_dim) {
-                float o = acc[i] * corr;
-                for (int j = 0; j < n_keys; ++j) o = fmaf(p_s[j], v_tile[j * tile_stride + d], o);
-                acc[i] = o;
-            }
+        for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] *= corr;
+#pragma unroll 4
+        for (int j = 0; j < n_keys; ++j) {
+            const float pj = p_s[j];
+            const float* vrow = v_tile + j * tile_stride + lane;
+#pragma unroll
+            for (int i = 0; i < kMaxHeadDim / 32; ++i)
+                if (32 * i < head_dim && lane + 32 * i < head_dim) acc[i] = fmaf(pj, vrow[32 * i], acc[i]);
         }
         __syncwarp();
-        if (more) tile_in_flight(cache, next_base, (long long)plane, v_tile, tile_stride, head_dim, lane);
+        if (more) tile_in_flight(cache, row_s, (long long)plane, v_tile, tile_stride, walk);
         else asm volatile("cp.async.commit_group;" ::: "memory");
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
-    float* merge = smem + (size_t)n_warps * (head_dim + 2 * kTile * tile_stride + kTile);
+    float* merge = smem + (size_t)n_warps * (head_dim + 2 * kTile * tile_stride + kTile + 2 * kTile);
     float* mine = merge + (size_t)warp * (head_dim + 2);
     if (lane == 0) { mine[0] = m; mine[1] = l; }
 #pragma unroll
@@ -329,7 +344,7 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
 // Whether a launch takes the kernel above: float32, 16-byte rows, few enough pairs that latency and not throughput
 // sets the time, and a block's two tiles per warp fit the shared memory of an SM.
 size_t few_smem(int warps, int head_dim) {
-    return (size_t)warps * (head_dim + 2 * kTile * (head_dim + 4) + kTile + head_dim + 2) * sizeof(float);
+    return (size_t)warps * (head_dim + 2 * kTile * (head_dim + 4) + kTile + 2 * kTile + head_dim + 2) * sizeof(float);
 }
 
 // Warps per block, by the head size alone: eight while three such blocks fit the shared memory of an SM (up to head size 64), fewer for larger heads.

@@ -110,6 +110,40 @@ def case_decode_attention(args) -> None:
           f"{nbytes / ms / 1e6:.1f} GB/s of cache ({nbytes / 1e6:.1f} MB)")
 
 
+def case_generic_attention(args) -> None:
+    """The 32-bit engine's attention: `batch` requests at `context`, each with `new` tokens in this step."""
+    from . import ops
+    dev = torch.device("cuda:0")
+    dt = torch.float32 if args.dtype == "float32" else torch.bfloat16
+    B, H, hd, ps, ctx, new = args.batch, args.heads, args.head_dim, 16, args.context, args.new
+    pages_per = -(-ctx // ps)
+    cache = torch.randn(B * pages_per, 2, H, ps, hd, device=dev).to(dt)
+    table = torch.arange(B * pages_per, dtype=torch.int32, device=dev).view(B, pages_per)
+    q = torch.randn(B * new, H * hd, device=dev).to(dt)
+    out = torch.empty_like(q)
+    tok_seq = torch.arange(B, dtype=torch.int32, device=dev).repeat_interleave(new)
+    positions = torch.arange(ctx - new, ctx, dtype=torch.int32, device=dev).repeat(B)
+    launch = lambda: ops.paged_attention_generic(q, cache, tok_seq, positions, table, out, B * new, H, H, hd, ps, hd ** -0.5, 0)
+    ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
+    nbytes = B * ctx * 2 * H * hd * cache.element_size()
+    print(f"generic-attention {args.dtype} batch={B} new={new} heads={H} head_dim={hd} context={ctx}: {ms * 1e3:.1f} us, "
+          f"{nbytes / ms / 1e6:.1f} GB/s of cache ({nbytes / 1e6:.1f} MB)")
+
+
+def case_gemm_f32(args) -> None:
+    """The 32-bit engine's product (FMA pipe, one summation order for every number of tokens)."""
+    from . import ops
+    dev = torch.device("cuda:0")
+    a = torch.randn(args.m, args.k, device=dev)
+    w = torch.randn(args.n, args.k, device=dev) * 0.05
+    bias = torch.randn(args.n, device=dev)
+    out = torch.zeros(args.m, args.n, device=dev)
+    launch = lambda: ops.gemm_ffma(a, w, bias, out, args.m, args.act)
+    ms = _graph_timed(launch, args.reps) if args.graph else _timed(launch, args.reps)
+    print(f"gemm-f32 M={args.m} N={args.n} K={args.k}: {ms * 1e3:.1f} us per launch, {2 * args.m * args.n * args.k / ms / 1e9:.2f} TFLOP/s, "
+          f"{(args.n * args.k * 4) / ms / 1e6:.1f} GB/s of weights")
+
+
 def case_prefill_attention(args) -> None:
     from . import ops
     dev = torch.device("cuda:0")
@@ -212,6 +246,22 @@ def main(argv=None) -> int:
     d.add_argument("--splits", type=int, default=0, help="key ranges per request and head (0: the engine's choice)")
     d.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     d.add_argument("--scalar", action="store_true", help="the scalar kernel even where the tensor-core one takes the shape")
+    ga = sub.add_parser("generic-attention")
+    ga.add_argument("--batch", type=int, default=8)
+    ga.add_argument("--new", type=int, default=1, help="tokens of each request in this step")
+    ga.add_argument("--heads", type=int, default=12)
+    ga.add_argument("--head-dim", type=int, default=64)
+    ga.add_argument("--context", type=int, default=768)
+    ga.add_argument("--dtype", default="float32", choices=["bfloat16", "float32"])
+    ga.add_argument("--reps", type=int, default=20)
+    ga.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
+    gf = sub.add_parser("gemm-f32")
+    gf.add_argument("--m", type=int, default=8)
+    gf.add_argument("--n", type=int, default=2304)
+    gf.add_argument("--k", type=int, default=768)
+    gf.add_argument("--act", default="none", choices=["none", "gelu_tanh", "gelu_erf"])
+    gf.add_argument("--reps", type=int, default=20)
+    gf.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     a = sub.add_parser("prefill-attention")
     a.add_argument("--seqs", type=int, default=2)
     a.add_argument("--length", type=int, default=1024)
@@ -241,7 +291,7 @@ def main(argv=None) -> int:
         p.add_argument("--no-fused", action="store_true", help="not the one-kernel decode step")
         p.add_argument("--stamps", action="store_true", help="decode-step: per-phase times from inside the one-kernel step")
     args = ap.parse_args(argv)
-    {"gemm": case_gemm, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
+    {"gemm": case_gemm, "generic-attention": case_generic_attention, "gemm-f32": case_gemm_f32, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,
      "prefill-step": case_prefill_step}[args.case](args)
     return 0
 
