@@ -38,6 +38,11 @@ PROGRAMS = ("liyab_cli", "trace_run")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-warn-spills"]
 CXX_FLAGS = ["-std=c++20", "-O2", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter"]
+# LIYAB_B200_SANITIZE=address,undefined builds the C++ host with those sanitizers into a folder of its own
+# (`_build_sanitize`); the process that loads it needs the sanitizer's runtime first (LD_PRELOAD=libasan.so for Python).
+SANITIZE = os.environ.get("LIYAB_B200_SANITIZE", "")
+if SANITIZE:
+    CXX_FLAGS = CXX_FLAGS + [f"-fsanitize={SANITIZE}", "-fno-omit-frame-pointer", "-g", "-O1"]
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -95,7 +100,7 @@ def build_dir() -> str:
     if env:
         os.makedirs(env, exist_ok=True)
         return env
-    local = os.path.join(HERE, "_build")
+    local = os.path.join(HERE, "_build_sanitize" if SANITIZE else "_build")
     try:
         os.makedirs(local, exist_ok=True)
         probe = os.path.join(local, f".write_probe_{os.getpid()}")
@@ -125,7 +130,7 @@ def ensure_built(verbose: bool = True) -> str:
     """Compiles what is out of date and returns the path of the library."""
     out = build_dir()
     srcs, hdrs = sources(), _headers()
-    flags = " ".join(NVCC_FLAGS)
+    flags = " ".join(NVCC_FLAGS + CXX_FLAGS)
     whole = _digest(srcs + hdrs, flags)
     lib = os.path.join(out, LIB_NAME)
     stamp = os.path.join(out, "stamp")
@@ -146,12 +151,19 @@ def ensure_built(verbose: bool = True) -> str:
             if fresh():
                 return lib
             nvcc = find_nvcc()
-            hdr_digest = _digest(hdrs, flags)
+            # An object's name carries the digest of its source, the headers and its own compiler's flags, so the
+            # kernels' objects are the same with and without sanitizers on the host and are taken over from `_build`.
+            hdr_digest = {True: _digest(hdrs, " ".join(NVCC_FLAGS)), False: _digest(hdrs, " ".join(CXX_FLAGS))}
+            plain_dir = os.path.join(HERE, "_build")
             todo, objs = [], []
             for src in srcs:
-                tag = _digest([src], hdr_digest)
-                obj = os.path.join(out, f"{os.path.splitext(os.path.basename(src))[0]}.{tag}.o")
+                tag = _digest([src], hdr_digest[src.endswith(".cu")])
+                name = f"{os.path.splitext(os.path.basename(src))[0]}.{tag}.o"
+                obj = os.path.join(out, name)
                 objs.append(obj)
+                if not os.path.isfile(obj) and out != plain_dir and os.path.isfile(os.path.join(plain_dir, name)):
+                    shutil.copyfile(os.path.join(plain_dir, name), obj + f".tmp{os.getpid()}")
+                    os.replace(obj + f".tmp{os.getpid()}", obj)
                 if not os.path.isfile(obj):
                     todo.append((src, obj))
             if todo and verbose:
@@ -172,6 +184,10 @@ def ensure_built(verbose: bool = True) -> str:
                 list(pool.map(work, todo))
             tmp_lib = lib + f".tmp{os.getpid()}"
             link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ldl", "-lpthread"]
+            if SANITIZE:         # the host compiler finds its own sanitizer runtimes; nvcc's link line does not
+                cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
+                link = [find_cxx(), "-shared", "-o", tmp_lib, *objs, f"-fsanitize={SANITIZE}", "-L", cuda_lib, "-lcudart_static",
+                        "-ldl", "-lpthread", "-lrt"]
             proc = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             if proc.returncode != 0:
                 raise backend_error(f"linking {LIB_NAME} failed:\n{proc.stdout[-4000:]}")
@@ -179,7 +195,7 @@ def ensure_built(verbose: bool = True) -> str:
             for prog in PROGRAMS:       # the programs talk to the library through its C interface only
                 tmp_prog = os.path.join(out, f"{prog}.tmp{os.getpid()}")
                 cmd = [find_cxx(), "-std=c++17", "-O2", os.path.join(HOST, "tools", prog + ".cpp"), "-o", tmp_prog,
-                       "-L", out, "-lliyab_b200", "-Wl,-rpath,$ORIGIN"]
+                       "-L", out, "-lliyab_b200", "-Wl,-rpath,$ORIGIN"] + ([f"-fsanitize={SANITIZE}"] if SANITIZE else [])
                 proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
                 if proc.returncode != 0:
                     raise backend_error(f"building {prog} failed:\n{proc.stdout[-4000:]}")
