@@ -103,6 +103,10 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     const int tile0 = begin / kTile;                                                // first tile of the range
     const int n_tiles = end > begin ? (end - 1) / kTile + 1 - tile0 : 0;
 
+    // Positions and block table came from the host before any kernel of the step; queries, and the newest keys and
+    // values, come from the kernel before this one.
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     // Q as the A operand: row r = query head kvh * G + r (rows past G are zero).
     uint32_t qf[KS][4];
     {
@@ -359,10 +363,10 @@ struct Variant {
                       int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
                       int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
         dim3 grid(n_splits, n_kv_head, n_seq);
-        decode_attention_mma_kernel<HD, kWarps, kStages, TMA><<<grid, kWarps * 32, smem, s>>>(
-            map_kv, kv_rows, status, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
-            (__nv_bfloat16*)out, out_stride, partial, counters, n_head, n_kv_head, page_shift, scale, window, n_splits);
-        LB_CHECK_LAUNCH();
+        LB_CHECK_CUDA(lb_launch_overlapped_kind(3, decode_attention_mma_kernel<HD, kWarps, kStages, TMA>, grid, dim3(kWarps * 32), smem, s, map_kv,
+                                           kv_rows, status, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions,
+                                           block_table, table_stride, (__nv_bfloat16*)out, out_stride, partial, counters, n_head,
+                                           n_kv_head, page_shift, scale, window, n_splits));
         return LB_OK;
     }
 };

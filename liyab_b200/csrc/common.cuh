@@ -52,6 +52,38 @@ int lb_fail(int code, const char* fmt, ...);
 
 #define LB_CHECK_LAUNCH() LB_CHECK_CUDA(cudaGetLastError())
 
+// ---- launches that overlap the end of the kernel before ----
+//
+// A kernel launched through lb_launch_overlapped may be started while the kernel before it on the stream is still
+// running (programmatic dependent launch): its blocks set up, ask for what does not depend on the kernel before
+// (weights, block tables) and only then wait for it with lb_wait_for_predecessor(), which returns once that kernel
+// has completed and its writes are visible.  Every thread of such a kernel passes lb_wait_for_predecessor() before
+// it reads what an earlier kernel wrote or writes what an earlier kernel may still read.  The kernel before
+// lets its successor start by lb_dependents_may_launch() (from all its blocks; without it the successor starts when
+// it ends); a thread calls it only after its own lb_wait_for_predecessor(): let go before that, a step's later
+// kernels ran ahead of data they needed (measured: wrong logits), whatever the reading of the instruction says.  In a kernel launched the ordinary way both are no-ops, and an ordinary launch after an overlapped one
+// waits for the whole of it, as always.  lb_set_launch_overlap(0) makes every launch ordinary (measurements).
+__device__ __forceinline__ void lb_dependents_may_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void lb_wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool lb_launch_overlap_enabled(int kind = 0);
+
+template <typename... Params, typename... Args>
+inline cudaError_t lb_launch_overlapped_kind(int kind, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = lb_launch_overlap_enabled(kind) ? 1 : 0;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ float lb_to_float(float v) { return v; }
 __device__ __forceinline__ float lb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
 
@@ -107,4 +139,9 @@ __device__ __forceinline__ float lb_activate(float x, int act) {
     if (act == LB_ACT_GELU_TANH) return lb_gelu_tanh(x);
     if (act == LB_ACT_GELU_ERF) return lb_gelu_erf(x);
     return x;
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t lb_launch_overlapped(void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    return lb_launch_overlapped_kind(0, kernel, grid, block, smem, stream, args...);
 }

@@ -4,6 +4,8 @@
 #include "api.h"
 #include "common.cuh"
 
+#include <cstdlib>
+
 #include <cstring>
 
 // ---------------------------------------------------------------- errors
@@ -26,6 +28,22 @@ extern "C" void lb_set_last_error(const char* message) {
 }
 
 extern "C" int lb_abi_version(void) { return LB_ABI_VERSION; }
+
+// On unless the environment says LIYAB_B200_LAUNCH_OVERLAP=0 (measurements) or lb_set_launch_overlap(0) was called.
+static bool g_launch_overlap = [] {
+    const char* env = getenv("LIYAB_B200_LAUNCH_OVERLAP");
+    return !(env != nullptr && env[0] == '0');
+}();
+static int g_overlap_mask = [] {
+    const char* env = getenv("LIYAB_B200_OVERLAP_MASK");
+    return env != nullptr ? atoi(env) : 15;
+}();
+bool lb_launch_overlap_enabled(int kind) { return g_launch_overlap && ((g_overlap_mask >> kind) & 1); }
+// Whether launches made through lb_launch_overlapped may overlap the kernel before (1, the default) or not (0).
+extern "C" int lb_set_launch_overlap(int on) {
+    g_launch_overlap = on != 0;
+    return LB_OK;
+}
 
 // ---------------------------------------------------------------- embedding
 
@@ -78,6 +96,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int32_t* __r
                                  const float* __restrict__ w, const float* __restrict__ b, T* __restrict__ y,
                                  int width, float eps) {
     __shared__ float scratch[33];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int r = blockIdx.x;
     const float* in = x + (size_t)(rows != nullptr ? rows[r] : r) * width;
     T* out = y + (size_t)r * width;
@@ -106,6 +126,8 @@ template <typename T, int NV>
 __global__ void __launch_bounds__(128)
 layernorm_warp_kernel(const float* __restrict__ x, const int32_t* __restrict__ rows, const float* __restrict__ w,
                       const float* __restrict__ b, T* __restrict__ y, int n_rows, int width, float eps) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int r = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (r >= n_rows) return;
     const int n4 = width >> 2;
@@ -166,15 +188,22 @@ layernorm_row_kernel(const float* __restrict__ x, const int32_t* __restrict__ ro
     __shared__ float part[2][4];
     const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int n4 = width >> 2;
-    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows != nullptr ? rows[r] : r) * width);
     float4 v[NV], gain[NV], offs[NV];
+    // Gains and offsets are weights: they are asked for before the kernel before this one has ended.
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = tid + 128 * i;
         const bool live = c < n4;
-        v[i] = live ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
         gain[i] = (live && w != nullptr) ? reinterpret_cast<const float4*>(w)[c] : make_float4(1.f, 1.f, 1.f, 1.f);
         offs[i] = (live && b != nullptr) ? reinterpret_cast<const float4*>(b)[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(rows != nullptr ? rows[r] : r) * width);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = tid + 128 * i;
+        v[i] = c < n4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     float sum = 0.0f;
 #pragma unroll
@@ -220,21 +249,21 @@ template <typename T>
 static void launch_layernorm_row(const float* x, const int32_t* rows, const float* w, const float* b, T* y, int n_rows,
                                  int width, float eps, cudaStream_t s) {
     const int n4 = width / 4;
-    if (n4 <= 128 * 2) layernorm_row_kernel<T, 2><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
-    else if (n4 <= 128 * 4) layernorm_row_kernel<T, 4><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
-    else layernorm_row_kernel<T, 8><<<n_rows, 128, 0, s>>>(x, rows, w, b, y, width, eps);
+    if (n4 <= 128 * 2) lb_launch_overlapped_kind(0, layernorm_row_kernel<T, 2>, dim3(n_rows), dim3(128), 0, s, x, rows, w, b, y, width, eps);
+    else if (n4 <= 128 * 4) lb_launch_overlapped_kind(0, layernorm_row_kernel<T, 4>, dim3(n_rows), dim3(128), 0, s, x, rows, w, b, y, width, eps);
+    else lb_launch_overlapped_kind(0, layernorm_row_kernel<T, 8>, dim3(n_rows), dim3(128), 0, s, x, rows, w, b, y, width, eps);
 }
 
 template <typename T>
 static void launch_layernorm_warp(const float* x, const int32_t* rows, const float* w, const float* b, T* y, int n_rows,
                                   int width, float eps, cudaStream_t s) {
     const int blocks = (n_rows + 3) / 4, n4 = width / 4;
-    if (n4 <= 32 * 2) layernorm_warp_kernel<T, 2><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
-    else if (n4 <= 32 * 4) layernorm_warp_kernel<T, 4><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
-    else if (n4 <= 32 * 6) layernorm_warp_kernel<T, 6><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
-    else if (n4 <= 32 * 8) layernorm_warp_kernel<T, 8><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
-    else if (n4 <= 32 * 13) layernorm_warp_kernel<T, 13><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
-    else layernorm_warp_kernel<T, 16><<<blocks, 128, 0, s>>>(x, rows, w, b, y, n_rows, width, eps);
+    if (n4 <= 32 * 2) lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 2>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 4) lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 4>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 6) lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 6>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 8) lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 8>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
+    else if (n4 <= 32 * 13) lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 13>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
+    else lb_launch_overlapped_kind(0, layernorm_warp_kernel<T, 16>, dim3(blocks), dim3(128), 0, s, x, rows, w, b, y, n_rows, width, eps);
 }
 
 extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, const float* weight,
@@ -259,9 +288,9 @@ extern "C" int lb_layernorm(int out_dtype, const float* x, const int32_t* rows, 
     } else if (warp_rows && out_dtype == LB_BF16) {
         launch_layernorm_warp<__nv_bfloat16>(x, rows, weight, bias, (__nv_bfloat16*)y, n_rows, width, eps, s);
     } else if (out_dtype == LB_F32) {
-        layernorm_kernel<float><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (float*)y, width, eps);
+        lb_launch_overlapped_kind(0, layernorm_kernel<float>, dim3(n_rows), dim3(threads), 0, s, x, rows, weight, bias, (float*)y, width, eps);
     } else if (out_dtype == LB_BF16) {
-        layernorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, s>>>(x, rows, weight, bias, (__nv_bfloat16*)y, width, eps);
+        lb_launch_overlapped_kind(0, layernorm_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), 0, s, x, rows, weight, bias, (__nv_bfloat16*)y, width, eps);
     } else {
         return lb_fail(LB_ERR_INVALID_ARGUMENT, "layernorm: unknown dtype %d", out_dtype);
     }

@@ -120,8 +120,22 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < n_kb; ++kb) {
+            // The weights of the first ring of stages are asked for before the kernel before this one has ended
+            // (they do not depend on it); the activations of those stages follow once it has.
+            const int ahead = n_kb < STAGES ? n_kb : STAGES;
+            for (int kb = 0; kb < ahead; ++kb) {
+                mbar_expect_tx(&s.full[kb], kStageBytes);
+                if (TOKENS_ON_LANES) tma_load_2d(s.col_tile[kb], &map_col, &s.full[kb], (kb_first + kb) * kBlockK, col_row0);
+                else tma_load_2d(s.lane_tile[kb], &map_lane, &s.full[kb], (kb_first + kb) * kBlockK, lane_row0);
+            }
+            lb_wait_for_predecessor();
+            lb_dependents_may_launch();
+            for (int kb = 0; kb < ahead; ++kb) {
+                if (TOKENS_ON_LANES) tma_load_2d(s.lane_tile[kb], &map_lane, &s.full[kb], (kb_first + kb) * kBlockK, lane_row0);
+                else tma_load_2d(s.col_tile[kb], &map_col, &s.full[kb], (kb_first + kb) * kBlockK, col_row0);
+            }
+            int issued = ahead;
+            for (int kb = ahead; kb < n_kb; ++kb) {
                 const int st = kb % STAGES;
                 const uint32_t ph = (kb / STAGES) & 1;
                 if (!mbar_wait(&s.empty[st], ph ^ 1, abort_flag)) {
@@ -170,6 +184,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_lane, const __grid_c
         // Epilogue: warp w may touch tensor-memory lanes 32 * (w % 4) .. + 31.
         const int quarter = warp & 3;
         const uint32_t tmem_row = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        lb_wait_for_predecessor();           // before the residual is read and anything is written
+        lb_dependents_may_launch();
         if (!mbar_wait(&s.acc_ready, 0, abort_flag)) {
             if (lane == 0) atomicCAS(&g_status, 0, (3 << 8) | quarter);
             s.abort_flag = 1;
@@ -287,6 +303,8 @@ struct FinishKv {
 template <typename TO>
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const float* residual,
                                      int64_t ldr, TO* out, int64_t ldo, int M, int N, int n_splits, int act, const FinishKv kv) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= M * N) return;
     const int t = idx / N, f = idx - t * N;
@@ -375,10 +393,10 @@ int launch(const CUtensorMap& map_lane, const CUtensorMap& map_col, const float*
     }
     dim3 grid(TOKENS_ON_LANES ? (N + BN - 1) / BN : (N + kLaneTile - 1) / kLaneTile,
               TOKENS_ON_LANES ? (M + kLaneTile - 1) / kLaneTile : (M + BN - 1) / BN, n_splits);
-    gemm_tcgen05_kernel<BN, STAGES, TOKENS_ON_LANES, TO><<<grid, kThreads, smem, stream>>>(
-        map_lane, map_col, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, vec_ok, partial, counters, n_splits, g_withhold_next);
+    LB_CHECK_CUDA(lb_launch_overlapped_kind(1, gemm_tcgen05_kernel<BN, STAGES, TOKENS_ON_LANES, TO>, grid, dim3(kThreads), smem, stream, map_lane,
+                                       map_col, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, vec_ok, partial, counters, n_splits,
+                                       g_withhold_next));
     g_withhold_next = 0;
-    LB_CHECK_LAUNCH();
     return LB_OK;
 }
 
@@ -461,9 +479,8 @@ static int gemm_tcgen05_run(int out_dtype, const void* A, int64_t lda, const voi
         rc = launch<BN, STAGES, TOL, TO>(TOL ? map_a : map_w, TOL ? map_w : map_a, bias, residual, ldr, out, ldo, M, N, K, \
                                          act, vec_ok, partial, counters, n_splits, s);                            \
         if (rc != LB_OK || n_splits == 1) return rc;                                                              \
-        splitk_finish_kernel<TO><<<(M * N + 255) / 256, 256, 0, s>>>(partial, bias, residual, ldr, (TO*)out, ldo, M, N, \
-                                                                    n_splits, act, kv);                          \
-        LB_CHECK_LAUNCH();                                                                                        \
+        LB_CHECK_CUDA(lb_launch_overlapped_kind(2, splitk_finish_kernel<TO>, dim3((M * N + 255) / 256), dim3(256), 0, s, partial, bias, residual, \
+                                           ldr, (TO*)out, ldo, M, N, n_splits, act, kv));                          \
         return LB_OK;                                                                                             \
     }
     if (out_dtype == LB_BF16) {
