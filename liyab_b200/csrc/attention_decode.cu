@@ -64,6 +64,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, c
     constexpr int STATE = HD + 2;               // m, l, values
     __shared__ float red[kWarps][G][STATE];
     __shared__ int is_last;
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -227,9 +229,9 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* po
            int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_kv_head,
            int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
     dim3 grid(n_splits, n_kv_head, n_seq);
-    decode_attention_kernel<HD, G><<<grid, kThreads, 0, s>>>(
+    LB_CHECK_CUDA(lb_launch_overlapped(decode_attention_kernel<HD, G>, dim3(grid), dim3(kThreads), 0, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits);
+        (__nv_bfloat16*)out, out_stride, partial, counters, n_kv_head, page_shift, scale, window, n_splits));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -101,6 +101,8 @@ paged_attention_generic_kernel(const T* __restrict__ q, int64_t q_stride, const 
                                int64_t out_stride, int n_tokens, int n_head, int n_kv_head, int head_dim,
                                int page_size, float scale, int window) {
     extern __shared__ float smem[];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
     const int pair = blockIdx.x;
     const int t = pair / n_head, h = pair - t * n_head;
@@ -254,7 +256,9 @@ paged_attention_f32_few_kernel(const float* __restrict__ q, int64_t q_stride, co
         return (long long)page * 2 * (long long)plane + ((long long)kvh * page_size + (j % page_size)) * head_dim;
     };
     int j0 = first + warp * kTile;
-    row_s[lane] = row_of(j0);
+    row_s[lane] = row_of(j0);            // positions and block table came from the host: looked up before the wait
+    lb_wait_for_predecessor();           // queries, and the newest keys and values, come from the kernel before this one
+    lb_dependents_may_launch();
     __syncwarp();
     if (j0 <= pos) {
         tile_in_flight(cache, row_s, 0, k_tile, tile_stride, walk);
@@ -378,16 +382,16 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* to
                 LB_CHECK_CUDA(cudaFuncSetAttribute(paged_attention_f32_few_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)few));
                 few_configured = few;
             }
-            paged_attention_f32_few_kernel<<<(unsigned)pairs, warps * 32, few, s>>>(
+            LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_f32_few_kernel, dim3((unsigned)pairs), dim3(warps * 32), few, s, 
                 (const float*)q, q_stride, (const float*)cache, tok_seq, positions, block_table, table_stride, (float*)out, out_stride,
-                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);
+                n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window));
             LB_CHECK_LAUNCH();
             return LB_OK;
         }
     }
-    paged_attention_generic_kernel<T><<<(unsigned)pairs, warps * 32, smem, s>>>(
+    LB_CHECK_CUDA(lb_launch_overlapped(paged_attention_generic_kernel<T>, dim3((unsigned)pairs), dim3(warps * 32), smem, s, 
         (const T*)q, q_stride, (const T*)cache, tok_seq, positions, block_table, table_stride, (T*)out, out_stride,
-        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window);
+        n_tokens, n_head, n_kv_head, head_dim, page_size, scale, window));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -80,6 +80,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, int64_t q_stride, 
     constexpr int OT = HD / 8;                  // output n-tiles
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);            // [kBM][LD]
+    lb_wait_for_predecessor();            // queries, keys and values come from the kernel before this one
+    lb_dependents_may_launch();
     __nv_bfloat16* k_s = q_s + kBM * LD;                                           // [kStages][kBN][LD]
     __nv_bfloat16* v_s = k_s + kStages * kBN * LD;                                 // [kStages][kBN][LD]
 
@@ -261,9 +263,9 @@ int launch(const void* q, int64_t q_stride, const void* cache, const int32_t* q_
         configured = true;
     }
     dim3 grid((max_q_len + kBM - 1) / kBM, n_head, n_seq);
-    prefill_attention_kernel<HD><<<grid, kThreads, smem, s>>>(
+    LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_kernel<HD>, dim3(grid), dim3(kThreads), smem, s, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, q_start, n_past, block_table, table_stride,
-        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window);
+        (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift, scale, window));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -110,6 +110,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             int* status) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    lb_wait_for_predecessor();            // queries, keys and values come from the kernel before this one
+    lb_dependents_may_launch();
     uint8_t* q_s = base;                                   // 16 KB
     uint8_t* k_s = q_s + kTileBytes;                       // [kStages] 16 KB
     uint8_t* v_s = k_s + kStages * kTileBytes;             // [kStages] 16 KB
@@ -437,9 +439,9 @@ extern "C" int lb_prefill_attention_tc(const void* q, int64_t q_stride, int n_to
         configured = true;
     }
     dim3 grid(n_head * n_seq, (max_q_len + kBM - 1) / kBM);
-    prefill_attention_tc_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+    LB_CHECK_CUDA(lb_launch_overlapped(prefill_attention_tc_kernel, dim3(grid), dim3(kThreads), smem, static_cast<cudaStream_t>(stream), 
         map_q, map_kv, q_start, n_past, block_table, table_stride, (__nv_bfloat16*)out, out_stride, n_head, n_kv_head, page_shift,
-        (int)kv_rows, scale, window, status);
+        (int)kv_rows, scale, window, status));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -308,6 +308,8 @@ template <typename T>
 __global__ void kv_append_kernel(const T* __restrict__ k, const T* __restrict__ v, int64_t row_stride,
                                  const int32_t* __restrict__ slot_mapping, T* __restrict__ cache, int n_kv_head,
                                  int head_dim, int page_size) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int t = blockIdx.x;
     const int slot = slot_mapping[t];
     if (slot < 0) return;
@@ -333,6 +335,8 @@ __global__ void __launch_bounds__(256)
 kv_append_vec_kernel(const T* __restrict__ k, const T* __restrict__ v, int64_t row_stride,
                      const int32_t* __restrict__ slot_mapping, T* __restrict__ cache, int n_tokens, int n_kv_head,
                      int head_dim, int page_size) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     constexpr int kPer = 16 / (int)sizeof(T);                    // elements per piece
     const int pieces_head = head_dim / kPer, pieces_row = n_kv_head * pieces_head;
     const int per_token = 2 * pieces_row;
@@ -365,19 +369,19 @@ extern "C" int lb_kv_append(int dtype, const void* k, const void* v, int64_t row
         const long pieces = (long)n_tokens * 2 * n_kv_head * (head_dim * elem / 16);
         const int blocks = (int)((pieces + 255) / 256);
         if (dtype == LB_F32)
-            kv_append_vec_kernel<float><<<blocks, 256, 0, s>>>((const float*)k, (const float*)v, row_stride, slot_mapping,
-                                                              (float*)cache, n_tokens, n_kv_head, head_dim, page_size);
+            LB_CHECK_CUDA(lb_launch_overlapped(kv_append_vec_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)k, (const float*)v, row_stride, slot_mapping,
+                                                              (float*)cache, n_tokens, n_kv_head, head_dim, page_size));
         else
-            kv_append_vec_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride,
+            LB_CHECK_CUDA(lb_launch_overlapped(kv_append_vec_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v, row_stride,
                                                                       slot_mapping, (__nv_bfloat16*)cache, n_tokens, n_kv_head,
-                                                                      head_dim, page_size);
+                                                                      head_dim, page_size));
     } else if (dtype == LB_F32) {
-        kv_append_kernel<float><<<n_tokens, threads, 0, s>>>((const float*)k, (const float*)v, row_stride, slot_mapping,
-                                                            (float*)cache, n_kv_head, head_dim, page_size);
+        LB_CHECK_CUDA(lb_launch_overlapped(kv_append_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)k, (const float*)v, row_stride, slot_mapping,
+                                                            (float*)cache, n_kv_head, head_dim, page_size));
     } else if (dtype == LB_BF16) {
-        kv_append_kernel<__nv_bfloat16><<<n_tokens, threads, 0, s>>>((const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
+        LB_CHECK_CUDA(lb_launch_overlapped(kv_append_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
                                                                     row_stride, slot_mapping, (__nv_bfloat16*)cache,
-                                                                    n_kv_head, head_dim, page_size);
+                                                                    n_kv_head, head_dim, page_size));
     } else {
         return lb_fail(LB_ERR_INVALID_ARGUMENT, "kv_append: unknown dtype %d", dtype);
     }
@@ -408,6 +412,8 @@ extern "C" int lb_gather_tokens(int32_t* dst, const int32_t* src, const int32_t*
 // The head's finishing touches where a model has them (the reference's finish_logits and
 // apply_final_softcap: src/core/transformer.cpp:2613-2620): x * scale, then cap * tanh(x / cap).
 __global__ void scale_softcap_kernel(float* __restrict__ x, int64_t n, float scale, float cap) {
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
         float v = x[i] * scale;
         if (cap > 0.0f) v = cap * tanhf(v / cap);
@@ -419,7 +425,7 @@ extern "C" int lb_scale_softcap(float* logits, int64_t count, float scale, float
     LB_CHECK_ARG(logits != nullptr && count >= 0, "scale_softcap: bad arguments");
     if (count == 0) return LB_OK;
     const int blocks = (int)((count + 255) / 256 < 1184 ? (count + 255) / 256 : 1184);
-    scale_softcap_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(logits, count, scale, soft_cap);
+    LB_CHECK_CUDA(lb_launch_overlapped(scale_softcap_kernel, dim3(blocks), dim3(256), 0, static_cast<cudaStream_t>(stream), logits, count, scale, soft_cap));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }

@@ -46,6 +46,8 @@ gemm_ffma_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restrict__ W
     constexpr int THREADS = (BM / TM) * (BN / TN);
     __shared__ float As[BK][BM + 1];
     __shared__ float Ws[BK][BN + 1];
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int tid = threadIdx.x;
     const int tx = tid % (BN / TN), ty = tid / (BN / TN);
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -207,6 +209,11 @@ gemm_ffma_skinny_kernel(const TI* __restrict__ A, int64_t lda, const TI* __restr
         const int k0 = c * kChunk;
         WeightChunk<TI> w;
         w.load(w_row, k0, K, live && f < N);
+        if (ci == 0) {
+            // The first chunk's weights are under way; the activations come from the kernel before this one.
+            lb_wait_for_predecessor();
+            lb_dependents_may_launch();
+        }
         // The warp's four slots bring their chunks of the tokens' activations: slot s2's chunk, token r, piece q.
         __syncwarp();
         for (int idx = lane; idx < 4 * TOKENS * (kChunk / VEC); idx += 32) {
@@ -289,8 +296,8 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
                                                    (int)(8 * 4 * skinny_pitch(8) * sizeof(float))));
                 configured = true;
             }
-            gemm_ffma_skinny_kernel<TI, TO, 8><<<grid, warps * 32, smem, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
-                                                                             (TO*)out, ldo, M, N, K, act);
+            LB_CHECK_CUDA(lb_launch_overlapped(gemm_ffma_skinny_kernel<TI, TO, 8>, dim3(grid), dim3(warps * 32), smem, s, (const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
+                                                                             (TO*)out, ldo, M, N, K, act));
         } else {
             const size_t smem = (size_t)warps * 4 * skinny_pitch(16) * sizeof(float);
             static bool configured = false;
@@ -299,13 +306,13 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
                                                    (int)(8 * 4 * skinny_pitch(16) * sizeof(float))));
                 configured = true;
             }
-            gemm_ffma_skinny_kernel<TI, TO, 16><<<grid, warps * 32, smem, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
-                                                                              (TO*)out, ldo, M, N, K, act);
+            LB_CHECK_CUDA(lb_launch_overlapped(gemm_ffma_skinny_kernel<TI, TO, 16>, dim3(grid), dim3(warps * 32), smem, s, (const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
+                                                                              (TO*)out, ldo, M, N, K, act));
         }
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_ffma_kernel<TI, TO, 64, 64, 16, 4, 4><<<grid, 256, 0, s>>>((const TI*)A, lda, (const TI*)W, ldw, bias,
-                                                                      residual, ldr, (TO*)out, ldo, M, N, K, act);
+        LB_CHECK_CUDA(lb_launch_overlapped(gemm_ffma_kernel<TI, TO, 64, 64, 16, 4, 4>, dim3(grid), dim3(256), 0, s, (const TI*)A, lda, (const TI*)W, ldw, bias,
+                                                                      residual, ldr, (TO*)out, ldo, M, N, K, act));
     }
     LB_CHECK_LAUNCH();
     return LB_OK;

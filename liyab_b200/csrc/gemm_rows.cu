@@ -101,6 +101,11 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
         for (int i = 0; i < NG; ++i)
 #pragma unroll
             for (int m = 0; m < MT; ++m) acc[i][m][0] = acc[i][m][1] = acc[i][m][2] = acc[i][m][3] = 0.0f;
+        if (gp == g_begin) {
+            // The first pass's weights are under way; the activations come from the kernel before this one.
+            lb_wait_for_predecessor();
+            lb_dependents_may_launch();
+        }
         stage(0);
         cp_async_commit();
 #pragma unroll
@@ -184,9 +189,8 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
     }
     const int n_groups = (N + 7) / 8;
     const int grid = n_groups < n_sm ? n_groups : n_sm;
-    gemm_rows_kernel<MT, NG, TO><<<grid, kThreads, smem, s>>>((const __nv_bfloat16*)A, lda, (const __nv_bfloat16*)W, ldw, bias,
-                                                              residual, ldr, (TO*)out, ldo, M, N, K, act, kv);
-    LB_CHECK_LAUNCH();
+    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
+                                       (const __nv_bfloat16*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, kv));
     return LB_OK;
 }
 

@@ -237,9 +237,41 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // The residual goes out once the ring is full for the first time in a tile (or after the tile's
             // last k-block): by then the loads that the MMAs wait for first are under way.
             const int res_at = (n_kb < n_stages ? n_kb : n_stages) - 1;
+            // The first tile's first ring of stages: the weights are asked for before the kernel before this one has
+            // ended (they do not depend on it); activations and residual follow once it has.
+            const int ahead = res_at + 1;
+            int kb_start = 0;
+            if ((int)blockIdx.x < total) {
+                const int tile = blockIdx.x;
+                const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < ahead; ++kb) {
+                    expect_tx_u32(full_u32 + 8 * kb, stage_bytes);
+                    tma_load_u32(stages_u32 + kb * stage_bytes + kATileBytes, &map_w, full_u32 + 8 * kb, kb * kBlockK, n0);
+                }
+                lb_wait_for_predecessor();
+                lb_dependents_may_launch();
+                for (int kb = 0; kb < ahead; ++kb)
+                    tma_load_u32(stages_u32 + kb * stage_bytes, &map_a, full_u32 + 8 * kb, kb * kBlockK, m0);
+                issued = ahead;
+                last_stage = ahead - 1;
+                last_parity = 0;
+                st = (uint32_t)ahead;
+                if (st == (uint32_t)n_stages) {
+                    st = 0;
+                    empty_parity ^= 1;
+                }
+                if (HAS_RES) {                     // the staging buffer is free before the first tile
+                    mbar_expect_tx(&c->res_full, (uint32_t)n_strips * kStripBytes);
+                    for (int sp = 0; sp < n_strips; ++sp)
+                        tma_load_2d(staging + (size_t)sp * kStripBytes, &map_res, &c->res_full, n0 + sp * kStripCols, m0);
+                    res_in_flight = true;
+                    res_parity = 0;
+                }
+                kb_start = ahead;
+            }
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
                 const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < n_kb; ++kb) {
+                for (int kb = kb_start; kb < n_kb; ++kb) {
                     if (!wait_u32(empty_u32 + 8 * st, empty_parity, abort_flag)) {
                         give_up(c, status, 1, st);
                         ok = false;
@@ -269,6 +301,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         res_parity = it & 1;
                     }
                 }
+                kb_start = 0;
             }
             stamp(timing, 7);
             if (*abort_flag != 0) {
@@ -330,6 +363,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         const bool elected = (et & 127) == 0;                          // one per group: issues and tracks its stores
         const uint32_t swz = (uint32_t)(row & 7);
         const uint32_t row_u32 = staging_u32 + (uint32_t)row * 128u;
+        lb_wait_for_predecessor();           // before anything this block stores, and before a cache page is written
+        lb_dependents_may_launch();
         int it = 0;
         for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
             const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
@@ -566,8 +601,8 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));           \
             configured = true;                                                                                           \
         }                                                                                                                \
-        gemm_persistent_kernel<TO, ACT, RES, KV><<<grid, kThreads, smem, s>>>(map_a, map_w, map_res, map_out, bias, M, N, K, \
-                                                                              bn, n_stages, status, g_timing, kv);       \
+        LB_CHECK_CUDA(lb_launch_overlapped(gemm_persistent_kernel<TO, ACT, RES, KV>, dim3(grid), dim3(kThreads), smem, s, map_a, map_w, \
+                                           map_res, map_out, bias, M, N, K, bn, n_stages, status, g_timing, kv));         \
     }
 #define LB_GO(TO, ACT, RES) LB_GO_KV(TO, ACT, RES, false)
 #define LB_GO_ACT(TO, RES)                                                  \

@@ -113,6 +113,8 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     __shared__ double sh_double;
     __shared__ int sh_choice;
 
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* x = logits + (size_t)row * row_stride;
     float* probs = out_probs != nullptr ? out_probs + (size_t)row * vocab : nullptr;
@@ -509,8 +511,8 @@ extern "C" int lb_sample(const float* logits, int64_t row_stride, int n_rows, in
                          float* out_probs, void* stream) {
     LB_CHECK_ARG(n_rows >= 0 && vocab > 0 && row_stride >= vocab, "sample: bad sizes rows=%d vocab=%d", n_rows, vocab);
     if (n_rows == 0) return LB_OK;
-    sample_kernel<<<n_rows, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs);
+    LB_CHECK_CUDA(lb_launch_overlapped(sample_kernel, dim3(n_rows), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), 
+        logits, row_stride, vocab, temperature, top_k, top_p, uniform, out_ids, out_probs));
     LB_CHECK_LAUNCH();
     return LB_OK;
 }
