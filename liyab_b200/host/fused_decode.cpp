@@ -97,6 +97,10 @@ std::unique_ptr<FusedDecodeStack> FusedDecodeStack::try_build(const DecoderModel
     return s;
 }
 
+bool FusedDecodeStack::accepts(int n_tokens) const {
+    return n_tokens >= 1 && n_tokens <= kMaxTokens && n_tokens * max_kv_heads_ <= model_->runtime.sm_count;
+}
+
 void FusedDecodeStack::splits(int n_tokens, int* n_splits, int* unit_warps) const {
     // (key ranges per (token, key/value head), warps per work item): a function of the batch's shape only.
     // A range merged across blocks costs a round of atomics and reloads, so from 64 pairs on a pair is one item,

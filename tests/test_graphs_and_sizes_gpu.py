@@ -150,3 +150,27 @@ def test_the_benchmark_layer_sizes_in_every_cutting(label, raw, dtype, tmp_path)
     if dtype == "float32":
         for kind in results:
             assert all(np.array_equal(row, results[kind][key]) for key, row in results["whole"].items()), f"{kind} differs from the whole run"
+
+
+def test_the_one_kernel_step_is_taken_while_its_attention_fits_one_round(tmp_path):
+    """Twelve heads: twelve decode tokens are 144 (token, head) pairs for 148 SMs and take the one-kernel step, fourteen
+    would need a second round of its attention phase and go part by part (captured); both agree with the plain model."""
+    from liyab_b200.engine import Replayer, StepEntry
+    from liyab_b200.weights import write_random_model
+    raw = dict(SMALL_WIDTH, n_layer=2)
+    folder = write_random_model(str(tmp_path / "m"), raw, seed=9, dtype="bfloat16")
+    oracle = plain.load_plain_model(folder)
+    rng = np.random.default_rng(4)
+    toks = {f"q{i}": rng.integers(0, raw["vocab_size"], size=5 + 3 * i).tolist() for i in range(14)}
+    want = {r: plain.forward_logits(oracle, t) for r, t in toks.items()}
+    for n, fused in ((12, True), (14, False)):
+        engine = Replayer(folder, "bfloat16", max_tokens=16 * 128, max_requests=16)
+        names = list(toks)[:n]
+        for r in names:
+            engine.cache.open(r)
+            engine.step([StepEntry(r, toks[r][:-1], [])])
+        out = engine.step([StepEntry(r, toks[r][-1:], [0]) for r in names]).logits
+        assert (engine.counters()["fused_steps"] == 1) == fused
+        for i, r in enumerate(names):
+            assert np.abs(out[i] - want[r][-1]).max() <= BIG_REL_TOL["bfloat16"] * np.abs(want[r]).max(), (n, r)
+        engine.close()
