@@ -182,8 +182,12 @@ def case_sample(args) -> None:
 
 
 def _model_folder(layers: int, dtype: str, size: str = "small") -> str:
+    """A random model of the asked size in a temporary folder that is removed when the process ends."""
+    import atexit
+    import shutil
     from .weights import write_random_model
     tmp = tempfile.mkdtemp(prefix="liyab_b200_case_")
+    atexit.register(shutil.rmtree, tmp, ignore_errors=True)
     return write_random_model(os.path.join(tmp, "m"), dict(GPT2_SIZES[size], n_layer=layers or GPT2_SIZES[size]["n_layer"]), 0, dtype)
 
 
