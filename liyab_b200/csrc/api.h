@@ -67,7 +67,7 @@ int lb_gemm_tcgen05_splits(int M, int K, int n_splits);
 int lb_gemm_tcgen05_kv(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, void* out,
                        int64_t ldo, int M, int N, int K, float* partial, int n_splits, void* kv_cache,
                        const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size, void* stream);
-/* The same product for 17 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
+/* The same product for 1 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
  * no second kernel): lb_gemm_rows_supports tells whether it takes the product.  With kv_cache given (bfloat16 pages
  * of one layer), features from q_dim on are the keys and values of a fused projection and are also written to the
  * tokens' cache slots (as lb_kv_append would). */

@@ -1,6 +1,6 @@
-// out[M, N] = epilogue(A[M, K] . W[N, K]^T) for 17 to 64 tokens (bfloat16
-// operands): the products of a decode step that is too large for the one-kernel
-// fused step and too small to fill a tcgen05 tile row.
+// out[M, N] = epilogue(A[M, K] . W[N, K]^T) for 1 to 64 tokens (bfloat16
+// operands): the products of a decode step, too small to fill a tcgen05 tile row,
+// whose reduction is short enough (the host takes it for K up to 1024).
 //
 // At these sizes a product reads a few MB of weights and does next to no
 // arithmetic; what it costs is latency.  The tcgen05 kernel needs K split over
@@ -12,7 +12,7 @@
 // current one is used), each warp takes 32 columns of every chunk, requests all
 // its weights of the pass (up to four groups of eight features) at the start with
 // 16-byte loads that go straight into mma.sync m16n8k16 fragments (tokens are the
-// rows: up to four tiles of 16), and the eight warps' partial tiles are summed in
+// rows: one to four tiles of 16), and the eight warps' partial tiles are summed in
 // warp order through shared memory.
 // Every weight byte is read once; a row's result does not depend on the other
 // rows.  Accumulators, bias, activation and residual sum are 32-bit, in the
@@ -204,11 +204,11 @@ int launch_by_k(const void* A, int64_t lda, const void* W, int64_t ldw, const fl
 
 }  // namespace
 
-// Whether the kernel takes the product: 17 to 64 tokens, a reduction length of up to 4096, K and the row strides of
+// Whether the kernel takes the product: 1 to 64 tokens, a reduction length of up to 4096, K and the row strides of
 // A and W multiples of 8, 16-byte aligned bases, and at most four passes over the feature groups of a block (the
 // head's vocabulary is left to the tcgen05 kernel, whose tiles suit it).
 extern "C" int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, int64_t ldw, int M, int N, int K) {
-    if (M <= 16 || M > kMaxRows || N <= 0 || K <= 0) return 0;
+    if (M <= 0 || M > kMaxRows || N <= 0 || K <= 0) return 0;
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || ((uintptr_t)A & 15) != 0 || ((uintptr_t)W & 15) != 0) return 0;
     if (K > kWRegs * kChunk) return 0;
     const int ng = K <= 4 * kChunk ? 4 : K <= 8 * kChunk ? 2 : 1;
@@ -221,7 +221,7 @@ extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const voi
                             void* stream) {
     LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows: unknown output dtype %d", out_dtype);
     if (!lb_gemm_rows_supports(A, lda, W, ldw, M, N, K))
-        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows: takes 17 to 64 tokens, K and row strides multiples of 8 and 16-byte aligned "
+        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows: takes 1 to 64 tokens, K and row strides multiples of 8 and 16-byte aligned "
                        "bases (M=%d N=%d K=%d lda=%lld ldw=%lld)", M, N, K, (long long)lda, (long long)ldw);
     LB_CHECK_ARG(lda >= K && ldw >= K && ldo >= N, "gemm_rows: a row stride is shorter than the row");
     static int n_sm = 0;
@@ -241,7 +241,8 @@ extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const voi
 #define LB_GO(MT)                                                                                                          \
     return out_dtype == LB_F32 ? launch_by_k<MT, float>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)   \
                                : launch_by_k<MT, __nv_bfloat16>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)
-    if (mt <= 2) LB_GO(2);
+    if (mt <= 1) LB_GO(1);
+    if (mt == 2) LB_GO(2);
     if (mt == 3) LB_GO(3);
     LB_GO(4);
 #undef LB_GO

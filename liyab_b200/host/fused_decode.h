@@ -28,8 +28,15 @@ public:
 
     // Up to 16 tokens, and no more (token, key/value head) pairs than the GPU has SMs: beyond that the attention phase
     // takes two rounds and the part-by-part path with its overlapped launches is faster (measured: GPT-2 small at 14
-    // tokens 537 us against 486 us, medium at 12 tokens 1,042 us against 1,005 us; below, the one kernel wins).
+    // tokens 537 us against 486 us, medium at 12 tokens 1,042 us against 1,005 us).  And only for layers heavy enough:
+    // the one kernel streams a layer's matrices better (it asks for them while blocks wait at its barriers: about 1.7 us
+    // more a layer from GPT-2 small's 14 MB to medium's 25 MB, against 4.2 us part by part), the part-by-part path has
+    // the shorter chain per layer (small: 28.8 against 29.5 us a layer, 8 tokens: 396 against 417 us a step; medium: 33.0
+    // against 31.2 us, 864 against 803 us), so the one kernel is taken from 18 MB of matrices a layer on.
     bool accepts(int n_tokens) const;
+    static constexpr int64_t kMinLayerBytes = 18 << 20;
+    // Lifts that last condition (tests of the kernel with tiny models; measurements).
+    void take_light_layers() { light_layers_too_ = true; }
     // Computes the logits of a decode step ([n_tokens, vocab] float32, valid until the next run).
     Rows run(StepContext& ctx);
     // Time stamps from inside the kernel (a measuring aid): once switched on, every launch has block 0 write the
@@ -51,6 +58,8 @@ private:
     const float* lnf_b_ = nullptr;
     float lnf_eps_ = 0.0f;
     DeviceBuffer layers_, x_, q_, att_, inner_, logits_, partial_, counters_, barrier_, stamps_;
+    int64_t min_layer_bytes_ = 0;    // the lightest layer's matrices
+    bool light_layers_too_ = false;
     uint64_t launches_ = 0;
 };
 

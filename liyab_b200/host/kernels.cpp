@@ -150,10 +150,10 @@ void linear(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, co
         const int n = static_cast<int>(w.dim(0)), k = static_cast<int>(w.dim(1));
         if (m > 64 && gemm_persistent_tile(a, w, out, m, residual) > 0)
             return gemm_persistent(rt.stream, a, w, bias, out, m, act, residual, nullptr);
-        // 17 to 64 tokens: one launch on mma.sync where every block can afford to fetch all activations (measured on
+        // Up to 64 tokens: one launch on mma.sync where every block can afford to fetch all activations (measured on
         // B200, 64 tokens: 6-7 us against 8-9 us for K = 768; for K = 3072 the 393 KB of activations per block cost
         // more than the split of K saves: 13 us against 8 us).
-        if (m > 16 && m <= 64 && k <= 1024 && gemm_rows_supports(a, w, m))
+        if (m <= 64 && k <= kRowsMaxK && gemm_rows_supports(a, w, m))
             return gemm_rows(rt.stream, a, w, bias, out, m, act, residual, nullptr);
         const int splits = ws != nullptr ? gemm_splits(m, n, k) : 1;
         float* partial = nullptr;
@@ -167,7 +167,7 @@ bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Te
                        const KvDestination& kv) {
     if (ws == nullptr || m > 64 || !tcgen05_accepts(a, w)) return false;
     const int n = static_cast<int>(w.dim(0)), k = static_cast<int>(w.dim(1));
-    if (m > 16 && k <= 1024 && gemm_rows_supports(a, w, m)) return false;          // that kernel has a cache epilogue of its own
+    if (k <= kRowsMaxK && gemm_rows_supports(a, w, m)) return false;          // that kernel has a cache epilogue of its own
     const int splits = gemm_splits(m, n, k);
     if (lb_gemm_tcgen05_splits(m, k, splits) <= 1) return false;
     check_product(a, w, out, nullptr);

@@ -48,6 +48,10 @@ void gemm_ffma(cudaStream_t s, const Rows& a, const Tensor& w, const float* bias
                const Rows* residual);
 void gemm_tcgen05(cudaStream_t s, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m, int act,
                   const Rows* residual, float* partial, int n_splits);
+// Products of up to 64 tokens take the one-launch kernel on mma.sync while every block can afford to fetch all
+// activations: a reduction length of up to 1024 (measured: with K = 1600 or 3072 the tcgen05 kernel with K split over
+// blocks and a second half wins, at 8 tokens as at 64).
+inline constexpr int kRowsMaxK = 1024;
 bool gemm_rows_supports(const Rows& a, const Tensor& w, int m);
 void gemm_rows(cudaStream_t s, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m, int act,
                const Rows* residual, const KvDestination* kv);

@@ -196,7 +196,7 @@ def case_decode_step(args) -> None:
     from .engine import Replayer
     B = args.batch
     rep = Replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=B * 1024, max_requests=B,
-                   cuda_graphs=not args.eager, fused_decode=not args.no_fused, max_step_tokens=1024)
+                   cuda_graphs=not args.eager, fused_decode=False if args.no_fused else (True if args.fused else None), max_step_tokens=1024)
     r = rep.bench_decode(B, args.context, args.reps, 3)
     path = "fused" if r["fused_steps"] else ("graph" if r["graph_steps"] else "parts")
     print(f"decode-step size={args.size} batch={B} layers={len(rep.info['spec']['layers'])} context~{r['mean_context']:.0f} path={path}: "
@@ -208,7 +208,8 @@ def case_decode_step(args) -> None:
         t = rep.fused_stamps().astype(np.float64) / 1e3
         n_blocks = int(np.count_nonzero(t[256:256 + 160]))
         last_barrier = int(np.flatnonzero(t[:126]).max())
-        print(f"  whole kernel after its first barrier: {t[last_barrier] - t[1]:.1f} us over {last_barrier - 1} barriers; head {t[127] - t[126]:.1f} us")
+        print(f"  whole kernel after its first barrier: {t[last_barrier] - t[1]:.1f} us over {last_barrier - 1} barriers; head {t[127] - t[126]:.1f} us; "
+              f"from block 0's start to the first barrier's end {t[1] - t[0]:.1f} us")
         names = ["LayerNorm + projection", "attention", "output projection", "LayerNorm + up", "down"]
         for j, name in enumerate(names):
             arrive = np.sort(t[256 + 160 * j:256 + 160 * j + n_blocks])
@@ -293,6 +294,7 @@ def main(argv=None) -> int:
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true", help="no captured graphs")
         p.add_argument("--no-fused", action="store_true", help="not the one-kernel decode step")
+        p.add_argument("--fused", action="store_true", help="the one-kernel decode step wherever it fits (default: where it is expected to win)")
         p.add_argument("--stamps", action="store_true", help="decode-step: per-phase times from inside the one-kernel step")
     args = ap.parse_args(argv)
     {"gemm": case_gemm, "generic-attention": case_generic_attention, "gemm-f32": case_gemm_f32, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,

@@ -228,7 +228,7 @@ def _kv_args(kv: Optional[tuple]) -> tuple:
 
 
 def gemm_rows_supports(a: torch.Tensor, w: torch.Tensor, m: int) -> bool:
-    """Whether the one-launch product for 17 to 64 tokens takes these operands."""
+    """Whether the one-launch product for 1 to 64 tokens takes these operands."""
     if not tcgen05_accepts(a, w):
         return False
     return bool(lib().lb_gemm_rows_supports(_dev(a, "a"), a.stride(0), _dev(w, "w"), w.stride(0), m, w.shape[0], w.shape[1]))
@@ -236,7 +236,7 @@ def gemm_rows_supports(a: torch.Tensor, w: torch.Tensor, m: int) -> bool:
 
 def gemm_rows(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, m: int,
               activation: str = "none", residual: Optional[torch.Tensor] = None, kv: Optional[tuple] = None) -> torch.Tensor:
-    """out[:m] = act(a[:m] @ w.T + bias) + residual for 17 to 64 tokens: one launch, weights streamed once.
+    """out[:m] = act(a[:m] @ w.T + bias) + residual for 1 to 64 tokens: one launch, weights streamed once.
     `kv` = (cache, slot_mapping, q_dim, n_kv_head, head_dim, page_size): the features from q_dim on are keys and
     values of a fused projection and also go to the tokens' cache slots."""
     n, k = w.shape
@@ -304,10 +304,10 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     if tcgen05_accepts(a, w):
         if m > 64 and gemm_persistent_tile(a, w, out, m, residual) > 0:
             return gemm_persistent(a, w, bias, out, m, activation, residual)
-        # 17 to 64 tokens: one launch on mma.sync where every block can afford to fetch all activations (measured on
+        # Up to 64 tokens: one launch on mma.sync where every block can afford to fetch all activations (measured on
         # B200, 64 tokens: 6-7 us against 8-9 us for K = 768; for K = 3072 the 393 KB of activations per block cost
-        # more than the split of K saves: 13 us against 8 us).
-        if 16 < m <= 64 and w.shape[1] <= 1024 and gemm_rows_supports(a, w, m):
+        # more than the split of K saves: 13 us against 8 us; 8 tokens with K = 1600 or 3072 lose to the split too).
+        if m <= 64 and w.shape[1] <= 1024 and gemm_rows_supports(a, w, m):
             return gemm_rows(a, w, bias, out, m, activation, residual)
         splits = gemm_splits(m, w.shape[0], w.shape[1]) if workspace is not None else 1
         if splits > 1:

@@ -88,14 +88,18 @@ def test_fused_step_whose_barrier_is_one_block_short_gives_up_and_later_steps_ar
     assert device_status() == (0, 0)
 
 
-def test_engine_ends_the_requests_of_a_step_whose_wait_ran_out_and_goes_on(folder):
+def test_engine_ends_the_requests_of_a_step_whose_wait_ran_out_and_goes_on(tmp_path):
     from liyab_b200 import ErrorCode
     from liyab_b200.engine import Engine, EngineConfig, device_status, withhold_next
     from liyab_b200.sampling import SamplingParams
-    raw, seed = CONFIGS["D"]
+    from liyab_b200.weights import write_random_model
+    # An inner size above 1,024: the down projection of a few tokens is then a split tcgen05 product (shorter
+    # reductions take the one-launch mma.sync kernel), the family whose wait this test makes run out.
+    raw, seed = dict(CONFIGS["D"][0], n_inner=1096), CONFIGS["D"][1]
+    folder = write_random_model(str(tmp_path / "m"), raw, seed=seed, dtype="bfloat16")
     prompt = random_tokens(77 + seed, 5, raw["vocab_size"])
     params = SamplingParams(temperature=0.0, max_tokens=8)
-    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32))
+    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32, fused_decode=True))
     good = engine.generate_tokens(prompt, params)
     assert good.error is None and len(good.tokens) == 8
     withhold_next(0)

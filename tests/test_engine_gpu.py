@@ -91,7 +91,7 @@ def test_bfloat16_generation_stays_close(folders):
     from liyab_b200 import Engine, EngineConfig, SamplingParams
     folder = folders[("B", "bfloat16")]
     prompt = random_tokens(5, 40, 1000)
-    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32))
+    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32, fused_decode=True))
     out = engine.generate_tokens(prompt, SamplingParams(temperature=0.0, max_tokens=20)).tokens
     logits = plain.forward_logits(plain.load_plain_model(folder), prompt + out)
     for i, tok in enumerate(out):
@@ -201,7 +201,7 @@ def test_a_reported_wait_ends_the_step_with_an_error_and_the_engine_goes_on(tmp_
     folder = write_model(str(tmp_path), "D", "bfloat16")
     prompt = random_tokens(5, 30, CONFIGS["D"][0]["vocab_size"])
     params = SamplingParams(temperature=0.0, max_tokens=12)
-    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32))
+    engine = Engine(EngineConfig(model=folder, dtype="bfloat16", max_requests=2, max_batched_tokens=64, num_pages=32, fused_decode=True))
     good = engine.generate_tokens(prompt, params)
     assert good.error is None and engine.stats()["fused_steps"] > 0 and engine.stats()["device_faults"] == 0
     seen = []

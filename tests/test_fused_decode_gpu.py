@@ -55,7 +55,7 @@ def test_fused_decode_up_to_sixteen_requests_and_long_contexts(folders):
     from liyab_b200.engine import Replayer, StepEntry
     raw, _ = CONFIGS["D"]
     P, V = raw["n_positions"], raw["vocab_size"]
-    stepper = Replayer(folders["D"], "bfloat16", max_tokens=17 * 320, max_requests=17)
+    stepper = Replayer(folders["D"], "bfloat16", max_tokens=17 * 320, max_requests=17, fused_decode=True)
     cache = stepper.cache
     oracle = plain.load_plain_model(folders["D"])
     lens = [1, 2, 15, 16, 17, 31, 64, 65, 100, 128, 129, 200, 255, 256, 290, P - 1]

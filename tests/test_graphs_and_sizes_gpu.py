@@ -139,7 +139,8 @@ def test_the_benchmark_layer_sizes_in_every_cutting(label, raw, dtype, tmp_path)
     for kind, steps in traces.items():
         steps = tt.thin(steps, keep)
         tokens = tt.peak_tokens(steps) if kind == "mixed" else 1024        # the mixed trace gets a pool for its own peak only
-        engine = Replayer(folder, dtype, max_tokens=tokens, cuda_graphs=(kind == "mixed"), max_step_tokens=256)
+        engine = Replayer(folder, dtype, max_tokens=tokens, cuda_graphs=(kind == "mixed"), max_step_tokens=256,
+                          fused_decode=(kind != "tail"))       # decode steps through the one kernel in all but one of the cuttings
         results[kind] = tt.collect(engine, steps)
         assert len(results[kind]) == n_rows
         if dtype == "bfloat16":
@@ -164,7 +165,7 @@ def test_the_one_kernel_step_is_taken_while_its_attention_fits_one_round(tmp_pat
     toks = {f"q{i}": rng.integers(0, raw["vocab_size"], size=5 + 3 * i).tolist() for i in range(14)}
     want = {r: plain.forward_logits(oracle, t) for r, t in toks.items()}
     for n, fused in ((12, True), (14, False)):
-        engine = Replayer(folder, "bfloat16", max_tokens=16 * 128, max_requests=16)
+        engine = Replayer(folder, "bfloat16", max_tokens=16 * 128, max_requests=16, fused_decode=True)
         names = list(toks)[:n]
         for r in names:
             engine.cache.open(r)

@@ -389,9 +389,10 @@ def test_gemm_persistent(dev, out_dtype, M, N, K, tile):
 @pytest.mark.parametrize("out_dtype,M,N,K", [
     (torch.float32, 17, 768, 768), (torch.float32, 64, 768, 3072), (torch.float32, 33, 1000, 200), (torch.float32, 48, 36, 4096),
     (torch.float32, 50, 130, 1032), (torch.bfloat16, 64, 2304, 768), (torch.bfloat16, 40, 3072, 768), (torch.bfloat16, 25, 4800, 1600),
-    (torch.bfloat16, 64, 72, 328), (torch.bfloat16, 18, 5000, 2048)])
+    (torch.bfloat16, 64, 72, 328), (torch.bfloat16, 18, 5000, 2048), (torch.bfloat16, 1, 2304, 768), (torch.float32, 8, 768, 768),
+    (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 130, 72)])
 def test_gemm_rows(dev, out_dtype, M, N, K):
-    """The one-launch product for 17 to 64 tokens against float64: every number of token tiles and of groups per
+    """The one-launch product for 1 to 64 tokens against float64: every number of token tiles and of groups per
     pass, several passes per block, ragged edges in M, N and K, all epilogues, the residual in place, a strided
     input; and a row's bits do not depend on how many rows share the launch."""
     from liyab_b200 import ops
@@ -412,9 +413,10 @@ def test_gemm_rows(dev, out_dtype, M, N, K):
         out2 = res.clone()
         ops.gemm_rows(a, w, bias, out2, M, "none", residual=out2)
         assert (out2.double() - (base + bias.double() + res.double())).abs().max().item() <= tol * scale
-        fewer = torch.empty((17, N), dtype=out_dtype, device=dev)
-        ops.gemm_rows(a[:17], w, bias, fewer, 17, "none", residual=res[:17])
-        assert torch.equal(fewer, out2[:17])
+        n_few = 17 if M > 17 else max(1, M - 3)
+        fewer = torch.empty((n_few, N), dtype=out_dtype, device=dev)
+        ops.gemm_rows(a[:n_few], w, bias, fewer, n_few, "none", residual=res[:n_few])
+        assert torch.equal(fewer, out2[:n_few])
     wide = torch.zeros((M + 3, K + 8), dtype=torch.bfloat16, device=dev)
     wide[:M, :K] = a
     out3 = torch.full((M + 3, N), 7.0, dtype=out_dtype, device=dev)
@@ -449,7 +451,8 @@ def test_gemm_rows_refuses_what_it_cannot_take(dev):
     from liyab_b200 import ops, LiyabError
     a, w = _rand((64, 4104), 1, dev, torch.bfloat16), _rand((16, 4104), 2, dev, torch.bfloat16)
     assert not ops.gemm_rows_supports(a, w, 64)                # a reduction length past 4096
-    assert not ops.gemm_rows_supports(a[:, :768], w[:, :768], 16) and not ops.gemm_rows_supports(a[:, :768], w[:, :768], 65)
+    assert ops.gemm_rows_supports(a[:, :768], w[:, :768], 16) and ops.gemm_rows_supports(a[:, :768], w[:, :768], 1)
+    assert not ops.gemm_rows_supports(a[:, :768], w[:, :768], 0) and not ops.gemm_rows_supports(a[:, :768], w[:, :768], 65)
     big = _rand((50304, 64), 3, dev, torch.bfloat16)
     assert not ops.gemm_rows_supports(a[:, :64].contiguous(), big, 64)          # a vocabulary: too many groups per block
     with pytest.raises(LiyabError):

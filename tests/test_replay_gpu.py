@@ -47,6 +47,7 @@ def oracle(folders):
 
 def make_engine(path, dtype, max_tokens, page_size=16, **options):
     from liyab_b200.engine import Replayer
+    options.setdefault("fused_decode", True)      # tiny models would not take the one-kernel step by themselves: keep it covered
     return Replayer(path, dtype, max_tokens, page_size=page_size, **options)
 
 
