@@ -67,6 +67,14 @@ int lb_gemm_tcgen05_splits(int M, int K, int n_splits);
 int lb_gemm_tcgen05_kv(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, void* out,
                        int64_t ldo, int M, int N, int K, float* partial, int n_splits, void* kv_cache,
                        const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim, int page_size, void* stream);
+/* lb_gemm_rows for up to 16 tokens and K up to 1024 with the activations made in the kernel: every block normalises the
+ * float32 rows x itself (LayerNorm with two-pass 32-bit statistics, eps, gain and offset or null), which saves the
+ * LayerNorm's launch.  Everything else as lb_gemm_rows. */
+int lb_gemm_rows_normed_supports(const void* x, int64_t ldx, const void* W, int64_t ldw, int M, int N, int K);
+int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, const float* gain, const float* offset, float eps, const void* W,
+                        int64_t ldw, const float* bias, const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N,
+                        int K, int act, void* kv_cache, const int32_t* slot_mapping, int q_dim, int n_kv_head, int head_dim,
+                        int page_size, void* stream);
 /* The same product for 1 to 64 tokens in one launch on mma.sync (weights streamed once, no split of K over blocks,
  * no second kernel): lb_gemm_rows_supports tells whether it takes the product.  With kv_cache given (bfloat16 pages
  * of one layer), features from q_dim on are the keys and values of a fused projection and are also written to the

@@ -28,6 +28,7 @@ constexpr int kChunk = 256;           // columns of the activations per chunk: o
 constexpr int kChunkLd = kChunk + 32; // row stride in a buffer: 64 bytes mod 128, conflict-free 16-byte reads
 constexpr int kMaxRows = 64;
 constexpr int kWRegs = 16;            // 16-byte weight pieces a thread holds: groups per pass x chunks
+constexpr int kNormLd = 4 * kChunk + 32;   // row stride where all columns (up to 1024) of normalised rows are kept
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -54,18 +55,92 @@ struct KvScatter {
     int q_dim, n_kv_head, head_dim, page_size;
 };
 
-// MT: tiles of 16 tokens (2, 3 or 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
+// Activations made in the kernel from the float32 residual rows by a LayerNorm (two-pass 32-bit statistics,
+// (x - mean) / sqrt(var + eps) * gain + offset, as the separate kernel computes them): for up to 16 tokens and a
+// reduction length of up to 1024 a block normalises the rows itself, one warp per row with the row in registers (one
+// round trip), and keeps them in shared memory for all its passes.  That saves the LayerNorm's launch.  x == nullptr: off.
+struct RowNorm {
+    const float* x;
+    int64_t ldx;
+    const float* gain;
+    const float* offset;
+    float eps;
+};
+
+__device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bfloat16* act, int ld, int k_pad) {
+    constexpr int kVecs = 8;                       // float4 per lane: rows of up to 1024 values
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_vec = K / 4;
+    float4 gain[kVecs], offs[kVecs];
+#pragma unroll
+    for (int j = 0; j < kVecs; ++j) {              // weights: asked for before the kernel before this one has ended
+        const int i = lane + 32 * j;
+        gain[j] = (i < n_vec && n.gain != nullptr) ? __ldg(reinterpret_cast<const float4*>(n.gain) + i) : make_float4(1.f, 1.f, 1.f, 1.f);
+        offs[j] = (i < n_vec && n.offset != nullptr) ? __ldg(reinterpret_cast<const float4*>(n.offset) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    for (int r = warp; r < 16; r += kWarps) {
+        __nv_bfloat16* dst = act + r * ld;
+        if (r >= M) {                              // rows past the step's tokens: zeros
+            for (int i = lane * 8; i < k_pad; i += 256) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
+            continue;
+        }
+        const float* row = n.x + (size_t)r * n.ldx;
+        float4 v[kVecs];
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int i = lane + 32 * j;
+            v[j] = i < n_vec ? __ldcg(reinterpret_cast<const float4*>(row) + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) sum += (v[j].x + v[j].y) + (v[j].z + v[j].w);
+        const float mean = lb_warp_sum(sum) / (float)K;
+        float ss = 0.0f;
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            if (lane + 32 * j < n_vec) {
+                const float d0 = v[j].x - mean, d1 = v[j].y - mean, d2 = v[j].z - mean, d3 = v[j].w - mean;
+                ss = fmaf(d0, d0, ss);
+                ss = fmaf(d1, d1, ss);
+                ss = fmaf(d2, d2, ss);
+                ss = fmaf(d3, d3, ss);
+            }
+        }
+        const float inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)K + n.eps);
+#pragma unroll
+        for (int j = 0; j < kVecs; ++j) {
+            const int i = lane + 32 * j;
+            if (i < n_vec) {
+                const float4 g = gain[j], o = offs[j];
+                const __nv_bfloat162 lo = __floats2bfloat162_rn((v[j].x - mean) * inv * g.x + o.x, (v[j].y - mean) * inv * g.y + o.y);
+                const __nv_bfloat162 hi = __floats2bfloat162_rn((v[j].z - mean) * inv * g.z + o.z, (v[j].w - mean) * inv * g.w + o.w);
+                uint2 packed;
+                packed.x = *reinterpret_cast<const uint32_t*>(&lo);
+                packed.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(dst + 4 * i) = packed;
+            }
+        }
+        for (int i = K + lane; i < k_pad; i += 32) dst[i] = __float2bfloat16_rn(0.0f);
+    }
+}
+
+// MT: tiles of 16 tokens (1 to 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
 // of up to 1024, 2048 or 4096 (NG x chunks = the 16 weight pieces a thread holds: all of a pass's weights are
 // requested at its start, one DRAM round trip, and used as the chunks of activations come in).
-template <int MT, int NG, typename TO>
+template <int MT, int NG, typename TO, bool NORM = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
                  const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M, int N, int K,
-                 int act, KvScatter kv) {
+                 int act, KvScatter kv, RowNorm norm) {
+    static_assert(!NORM || (MT == 1 && NG == 4), "rows are normalised in the kernel for up to 16 tokens and K up to 1024");
     constexpr int kRows = MT * 16, MC = kWRegs / NG;
     extern __shared__ __align__(16) uint8_t smem_bytes[];
-    __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);                       // [2][kRows][kChunkLd]
-    float* red_s = reinterpret_cast<float*>(smem_bytes + (size_t)2 * kRows * kChunkLd * sizeof(__nv_bfloat16));   // [kWarps][NG][MT][128]
+    // The activations: two buffers of one chunk each, [2][kRows][kChunkLd]; or (NORM) all columns at once, [16][kNormLd].
+    __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
+    constexpr size_t kActBytes = NORM ? (size_t)16 * kNormLd * sizeof(__nv_bfloat16) : (size_t)2 * kRows * kChunkLd * sizeof(__nv_bfloat16);
+    float* red_s = reinterpret_cast<float*>(smem_bytes + kActBytes);   // [kWarps][NG][MT][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n_groups = (N + 7) / 8;
     const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -103,24 +178,34 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             for (int m = 0; m < MT; ++m) acc[i][m][0] = acc[i][m][1] = acc[i][m][2] = acc[i][m][3] = 0.0f;
         if (gp == g_begin) {
             // The first pass's weights are under way; the activations come from the kernel before this one.
-            lb_wait_for_predecessor();
-            lb_dependents_may_launch();
+            if constexpr (NORM) {
+                layernorm_rows_to_smem(norm, M, K, act_s, kNormLd, n_chunks * kChunk);
+                __syncthreads();
+            } else {
+                lb_wait_for_predecessor();
+                lb_dependents_may_launch();
+            }
         }
-        stage(0);
-        cp_async_commit();
+        if constexpr (!NORM) {
+            stage(0);
+            cp_async_commit();
+        }
 #pragma unroll
         for (int c = 0; c < MC; ++c) {
             if (c < n_chunks) {                                 // the same for every thread
-                if (c + 1 < n_chunks) stage(c + 1);
-                cp_async_commit();
-                cp_async_wait<1>();
-                __syncthreads();
-                const __nv_bfloat16* buf = act_s + (size_t)(c & 1) * kRows * kChunkLd + warp * 32 + t * 8;
+                if constexpr (!NORM) {
+                    if (c + 1 < n_chunks) stage(c + 1);
+                    cp_async_commit();
+                    cp_async_wait<1>();
+                    __syncthreads();
+                }
+                constexpr int kLd = NORM ? kNormLd : kChunkLd;
+                const __nv_bfloat16* buf = (NORM ? act_s + c * kChunk : act_s + (size_t)(c & 1) * kRows * kChunkLd) + warp * 32 + t * 8;
                 if (c * kChunk + warp * 32 < K) {
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
-                        const uint4 lo = *reinterpret_cast<const uint4*>(buf + (m * 16 + g) * kChunkLd);
-                        const uint4 hi = *reinterpret_cast<const uint4*>(buf + (m * 16 + g + 8) * kChunkLd);
+                        const uint4 lo = *reinterpret_cast<const uint4*>(buf + (m * 16 + g) * kLd);
+                        const uint4 hi = *reinterpret_cast<const uint4*>(buf + (m * 16 + g + 8) * kLd);
 #pragma unroll
                         for (int gi = 0; gi < NG; ++gi) {
                             if (gi < ng) {
@@ -130,7 +215,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
                         }
                     }
                 }
-                __syncthreads();        // the buffer is free: the chunk after next goes into it
+                if constexpr (!NORM) __syncthreads();        // the buffer is free: the chunk after next goes into it
             }
         }
         // Partial tiles of the eight warps -> shared memory -> summed in warp order -> epilogue.
@@ -178,19 +263,20 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
     }
 }
 
-template <int MT, int NG, typename TO>
+template <int MT, int NG, typename TO, bool NORM = false>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
-           void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s) {
-    constexpr size_t smem = (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16) + (size_t)kWarps * NG * MT * 128 * sizeof(float);
+           void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s, RowNorm norm = RowNorm{}) {
+    constexpr size_t act_bytes = NORM ? (size_t)16 * kNormLd * sizeof(__nv_bfloat16) : (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16);
+    constexpr size_t smem = act_bytes + (size_t)kWarps * NG * MT * 128 * sizeof(float);
     static bool configured = false;
     if (!configured) {
-        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = true;
     }
     const int n_groups = (N + 7) / 8;
     const int grid = n_groups < n_sm ? n_groups : n_sm;
-    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
-                                       (const __nv_bfloat16*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, kv));
+    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO, NORM>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
+                                       (const __nv_bfloat16*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, kv, norm));
     return LB_OK;
 }
 
@@ -213,6 +299,43 @@ extern "C" int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, 
     if (K > kWRegs * kChunk) return 0;
     const int ng = K <= 4 * kChunk ? 4 : K <= 8 * kChunk ? 2 : 1;
     return (N + 7) / 8 <= 148 * 4 * ng;
+}
+
+// The same product for up to 16 tokens and a reduction length of up to 1024 with the activations made in the kernel:
+// LayerNorm (two-pass 32-bit statistics, eps, gain and offset or null) of the float32 rows x, normalised by every
+// block for itself.  lb_gemm_rows_normed_supports says whether the kernel takes the operands.
+extern "C" int lb_gemm_rows_normed_supports(const void* x, int64_t ldx, const void* W, int64_t ldw, int M, int N, int K) {
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K > 4 * kChunk) return 0;
+    if (K % 8 != 0 || ldx % 4 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return 0;
+    return (N + 7) / 8 <= 148 * 4 * 4;
+}
+
+extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, const float* gain, const float* offset, float eps,
+                                   const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr, void* out,
+                                   int64_t ldo, int M, int N, int K, int act, void* kv_cache, const int32_t* slot_mapping, int q_dim,
+                                   int n_kv_head, int head_dim, int page_size, void* stream) {
+    LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows_normed: unknown output dtype %d", out_dtype);
+    if (!lb_gemm_rows_normed_supports(x, ldx, W, ldw, M, N, K) || ((uintptr_t)gain & 15) != 0 || ((uintptr_t)offset & 15) != 0)
+        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows_normed: takes 1 to 16 tokens, K up to 1024 and a multiple of 8, 16-byte aligned bases "
+                       "(M=%d N=%d K=%d ldx=%lld ldw=%lld)", M, N, K, (long long)ldx, (long long)ldw);
+    LB_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm_rows_normed: a row stride is shorter than the row");
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        LB_CHECK_CUDA(cudaGetDevice(&dev));
+        LB_CHECK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    KvScatter kv{static_cast<__nv_bfloat16*>(kv_cache), slot_mapping, q_dim, n_kv_head, head_dim, page_size};
+    if (kv_cache != nullptr)
+        LB_CHECK_ARG(slot_mapping != nullptr && q_dim >= 0 && n_kv_head > 0 && head_dim > 0 && page_size > 0 &&
+                         q_dim + 2 * n_kv_head * head_dim == N,
+                     "gemm_rows_normed: the cache destination needs N = q_dim + 2 * n_kv_head * head_dim (N=%d q_dim=%d heads %d x %d)", N,
+                     q_dim, n_kv_head, head_dim);
+    const RowNorm norm{x, ldx, gain, offset, eps};
+    auto s = static_cast<cudaStream_t>(stream);
+    if (out_dtype == LB_F32)
+        return launch<1, 4, float, true>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
+    return launch<1, 4, __nv_bfloat16, true>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
 }
 
 extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,

@@ -24,11 +24,6 @@ from ..status import ErrorCode, LiyabError, invalid_argument
 FINISH_REASONS = ["unfinished", "eos", "length", "context", "stopped", "cancelled", "error"]
 
 
-def _fused_code(choice: Optional[bool]) -> int:
-    """The C interface's code for the one-kernel decode step: 0 never, 1 where it is expected to win, 2 wherever it fits."""
-    return 1 if choice is None else (2 if choice else 0)
-
-
 @dataclass
 class EngineConfig:
     """Options of `Engine`; names follow the reference's engine config and CLI where they exist
@@ -43,7 +38,7 @@ class EngineConfig:
     num_pages: int = 0                 # 0: enough for max_requests full contexts, within kv_memory_fraction
     kv_memory_fraction: float = 0.5    # of the free device memory, at most, for the cache when num_pages is 0
     cuda_graphs: bool = True           # replay captured graphs for steps whose shape repeats
-    fused_decode: Optional[bool] = None   # the one-kernel decode step: None = where it is expected to win, True = wherever it fits, False = never
+    fused_decode: bool = False         # decode steps of up to 16 requests as one persistent kernel (bfloat16); off: the part-by-part path is faster
     pipeline: bool = True              # plan and launch step n+1 while step n runs (tokens stay on the device)
     profile_phases: bool = False       # time every step's phases (slower)
 
@@ -102,7 +97,7 @@ class Engine:
         c.device, c.context_length, c.max_batched_tokens = cfg.device, cfg.context_length, cfg.max_batched_tokens
         c.max_sequences, c.page_size, c.num_pages = cfg.max_requests, cfg.page_size, cfg.num_pages
         c.kv_memory_fraction = cfg.kv_memory_fraction
-        c.cuda_graphs, c.fused_decode, c.pipeline = int(cfg.cuda_graphs), _fused_code(cfg.fused_decode), int(cfg.pipeline)
+        c.cuda_graphs, c.fused_decode, c.pipeline = int(cfg.cuda_graphs), int(cfg.fused_decode), int(cfg.pipeline)
         c.profile_phases = int(cfg.profile_phases)
         h = C.c_void_p()
         _capi.check(self._lib.lb_engine_create(C.byref(c), C.byref(h)))
@@ -206,9 +201,9 @@ class Replayer:
     """A model on the device, a cache sized for `max_tokens` live tokens and the step function."""
 
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = 16, max_requests: int = 16, num_pages: int = 0,
-                 cuda_graphs: bool = False, fused_decode: Optional[bool] = None, max_step_tokens: int = 0, device: int = 0):
+                 cuda_graphs: bool = False, fused_decode: bool = False, max_step_tokens: int = 0, device: int = 0):
         self._lib = _capi.lib()
-        o = _capi.ReplayerOptionsC(device, page_size, max_requests, num_pages, int(cuda_graphs), _fused_code(fused_decode), max_step_tokens)
+        o = _capi.ReplayerOptionsC(device, page_size, max_requests, num_pages, int(cuda_graphs), int(fused_decode), max_step_tokens)
         h = C.c_void_p()
         _capi.check(self._lib.lb_replayer_create(_capi.b(model_dir), _capi.b(dtype), max_tokens, C.byref(o), C.byref(h)))
         self._h = h

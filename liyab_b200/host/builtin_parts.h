@@ -68,6 +68,7 @@ public:
     void forward(StepContext& ctx, const Rows& x, const Rows& out, int n_rows, const int32_t* rows) override {
         kernels::layernorm(ctx.stream(), x, rows, weight_, bias_, out, n_rows, eps_);
     }
+    std::optional<NormRecipe> recipe() const override { return NormRecipe{weight_, bias_, eps_}; }
     const float* weight_ = nullptr;
     const float* bias_ = nullptr;
     float eps_;
@@ -141,6 +142,23 @@ public:
     bool capturable() const override { return true; }
     std::optional<KvNeed> kv_need() const override { return KvNeed{shape.n_kv_head, shape.head_dim, shape.window}; }
 
+    // A step of up to 16 tokens in bfloat16 with rows of up to 1024 values: the projection normalises the rows inside
+    // its kernel (and fills the cache from its epilogue), so the LayerNorm before the mixer is not launched.
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) override {
+        const int T = ctx.n_tokens;
+        if (!unit.write || !kernels::gemm_rows_normed_supports(ctx.runtime, x_in, qkv.weight, T)) return false;
+        const Rows qkv_out = ctx.workspace->get("attn.qkv", T, q_dim + 2 * kv_dim, ctx.runtime.dtype);
+        const GroupView* view = nullptr;
+        void* cache = ctx.kv(unit.read, &view);
+        kernels::AttentionShape a = shape;
+        a.page_size = view->group->page_size;
+        const kernels::KvDestination dest{cache, view->slot_mapping, q_dim, a.n_kv_head, a.head_dim, a.page_size};
+        kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, qkv.weight, qkv.bias, qkv_out, T, kernels::kNone,
+                                  nullptr, &dest);
+        attend_and_project(ctx, qkv_out, cache, *view, a, x);
+        return true;
+    }
+
     void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) override {
         const int T = ctx.n_tokens;
         const DType dt = ctx.runtime.dtype;
@@ -167,14 +185,20 @@ public:
                 kernels::kv_append(ctx.stream(), qkv_out.columns(q_dim, kv_dim), qkv_out.columns(q_dim + kv_dim, kv_dim),
                                    view->slot_mapping, cache, dt, T, a.n_kv_head, a.head_dim, a.page_size);
         }
+        attend_and_project(ctx, qkv_out, cache, *view, a, x);
+    }
+
+private:
+    void attend_and_project(StepContext& ctx, const Rows& qkv_out, void* cache, const GroupView& view, const kernels::AttentionShape& a,
+                            const Rows& x) {
+        const int T = ctx.n_tokens;
         const Rows q = qkv_out.columns(0, q_dim);
-        const Rows att = ws.get("attn.out", T, q_dim, dt);
-        attend(ctx, q, cache, *view, att, a);
+        const Rows att = ctx.workspace->get("attn.out", T, q_dim, ctx.runtime.dtype);
+        attend(ctx, q, cache, view, att, a);
         ctx.tap("attention", att);
         out.forward(ctx, att, x, T, kernels::kNone, &x);
     }
 
-private:
     // Chooses the attention kernel.  bfloat16: a split-key decode kernel for steps of single tokens (on the
     // tensor cores where that one takes the shape, else scalar), the tensor-core prefill kernel for steps with
     // prompt portions, where they take the shape.  Else the generic kernel; all of the 32-bit engine runs on it,
@@ -241,6 +265,15 @@ public:
         up.forward(ctx, h, mid, T, activation);
         down.forward(ctx, mid, x, T, kernels::kNone, &x);
     }
+    // As the attention's: the up projection of a few tokens normalises the rows inside its kernel.
+    bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) override {
+        const int T = ctx.n_tokens;
+        if (!kernels::gemm_rows_normed_supports(ctx.runtime, x_in, up.weight, T)) return false;
+        const Rows mid = ctx.workspace->get("ff.inner", T, inner, ctx.runtime.dtype);
+        kernels::gemm_rows_normed(ctx.stream(), x_in, norm.gain, norm.offset, norm.eps, up.weight, up.bias, mid, T, activation, nullptr, nullptr);
+        down.forward(ctx, mid, x, T, kernels::kNone, &x);
+        return true;
+    }
     int64_t inner = 0;
     int activation = 0;
     Linear up, down;
@@ -266,17 +299,27 @@ public:
     void forward(StepContext& ctx, const Rows& x, CacheUnit unit) override {
         const int T = ctx.n_tokens;
         const Rows h = ctx.workspace->get("block.normed", T, x.cols, ctx.runtime.dtype);
-        ctx.phase(Phase::Norm);
-        mixer_norm.forward(ctx, x, h, T, nullptr);
-        ctx.tap("mixer_norm", h);
+        // A norm that has a recipe offers it, with the rows as they are, to the part after it; where that part
+        // declines (or a test wants to see the norm's output), the norm runs by itself as usual.
+        const std::optional<NormRecipe> first = ctx.tap_fn == nullptr ? mixer_norm.recipe() : std::nullopt;
         ctx.phase(Phase::Mixer);
-        mixer.forward(ctx, h, x, unit);
+        if (!(first && mixer.forward_from(ctx, x, *first, x, unit))) {
+            ctx.phase(Phase::Norm);
+            mixer_norm.forward(ctx, x, h, T, nullptr);
+            ctx.tap("mixer_norm", h);
+            ctx.phase(Phase::Mixer);
+            mixer.forward(ctx, h, x, unit);
+        }
         ctx.tap("mixer", x);
-        ctx.phase(Phase::Norm);
-        ff_norm.forward(ctx, x, h, T, nullptr);
-        ctx.tap("ff_norm", h);
+        const std::optional<NormRecipe> second = ctx.tap_fn == nullptr ? ff_norm.recipe() : std::nullopt;
         ctx.phase(Phase::FeedForward);
-        feed_forward.forward(ctx, h, x);
+        if (!(second && feed_forward.forward_from(ctx, x, *second, x))) {
+            ctx.phase(Phase::Norm);
+            ff_norm.forward(ctx, x, h, T, nullptr);
+            ctx.tap("ff_norm", h);
+            ctx.phase(Phase::FeedForward);
+            feed_forward.forward(ctx, h, x);
+        }
         ctx.tap("feed_forward", x);
     }
     Norm& mixer_norm;

@@ -197,7 +197,7 @@ int32_t lb_engine_create(const lb_engine_config* c, lb_engine** out) {
         e.num_pages = c->num_pages;
         if (c->kv_memory_fraction > 0) e.kv_memory_fraction = c->kv_memory_fraction;
         e.cuda_graphs = c->cuda_graphs != 0;
-        e.fused_decode = c->fused_decode;
+        e.fused_decode = c->fused_decode != 0;
         e.pipeline = c->pipeline != 0;
         e.profile_phases = c->profile_phases != 0;
         auto handle = std::make_unique<lb_engine>();
@@ -667,7 +667,7 @@ int32_t lb_replayer_create(const char* model_dir, const char* dtype, int64_t max
             if (options->max_requests > 0) o.max_requests = options->max_requests;
             o.num_pages = options->num_pages;
             o.cuda_graphs = options->cuda_graphs != 0;
-            o.fused_decode = options->fused_decode;
+            o.fused_decode = options->fused_decode != 0;
             o.max_step_tokens = options->max_step_tokens;
         }
         auto h = std::make_unique<lb_replayer>();

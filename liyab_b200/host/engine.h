@@ -53,7 +53,7 @@ struct EngineConfig {
     int num_pages = 0;                  // 0: enough for max_requests full contexts, within kv_memory_fraction
     double kv_memory_fraction = 0.5;    // of the free device memory, at most, for the cache when num_pages is 0
     bool cuda_graphs = true;            // replay captured graphs for steps whose shape repeats
-    int fused_decode = 1;               // the one-kernel decode step (bfloat16, up to 16 requests): 0 never, 1 where it is expected to win, 2 wherever it fits
+    bool fused_decode = false;          // decode steps of up to 16 requests as one persistent kernel (bfloat16), where it takes the model
     bool pipeline = true;               // plan and launch step n+1 while step n runs (tokens stay on the device)
     bool profile_phases = false;        // time every step's phases (steps then run part by part, one at a time)
 };

@@ -57,8 +57,6 @@ std::unique_ptr<FusedDecodeStack> FusedDecodeStack::try_build(const DecoderModel
         s->max_heads_ = std::max(s->max_heads_, a.n_head);
         s->max_kv_heads_ = std::max(s->max_kv_heads_, a.n_kv_head);
         s->max_k_ = std::max({s->max_k_, qd, static_cast<int>(ff->inner)});
-        const int64_t layer_bytes = 2 * ((static_cast<int64_t>(qd) + 2 * a.n_kv_head * a.head_dim + qd) * spec.hidden() + 2 * ff->inner * spec.hidden());
-        s->min_layer_bytes_ = records.empty() ? layer_bytes : std::min(s->min_layer_bytes_, layer_bytes);
         LayerRecord r{};
         const void* ptrs[13] = {n1->weight_, n1->bias_, n2->weight_, n2->bias_, at->qkv.weight.data, at->qkv.bias, at->out.weight.data,
                                 at->out.bias, ff->up.weight.data, ff->up.bias, ff->down.weight.data, ff->down.bias,
@@ -100,8 +98,7 @@ std::unique_ptr<FusedDecodeStack> FusedDecodeStack::try_build(const DecoderModel
 }
 
 bool FusedDecodeStack::accepts(int n_tokens) const {
-    return n_tokens >= 1 && n_tokens <= kMaxTokens && n_tokens * max_kv_heads_ <= model_->runtime.sm_count &&
-           (light_layers_too_ || min_layer_bytes_ >= kMinLayerBytes);
+    return n_tokens >= 1 && n_tokens <= kMaxTokens && n_tokens * max_kv_heads_ <= model_->runtime.sm_count;
 }
 
 void FusedDecodeStack::splits(int n_tokens, int* n_splits, int* unit_warps) const {

@@ -9,6 +9,11 @@
 // float32, more tokens, prompt portions, a head with a scale or a cap) takes the
 // part-by-part path; the results agree to bfloat16 rounding, which the tests check.
 //
+// It is an option (off by default): with one-launch products, launches that overlap the kernel before and the rows
+// normalised inside the projections, the part-by-part path in a captured graph has become as fast or faster at
+// every size measured (8 tokens: GPT-2 small 379 against 417 us, medium 820 against 820 us, GPT-2 large 1.47
+// against 3.38 ms, whose slices no longer fit the registers this kernel sets aside for a phase's weights).
+//
 // This class only describes the model to the kernel: it packs one record per
 // run-order entry from the parts' own parameters and owns the step's buffers.
 #pragma once
@@ -27,16 +32,8 @@ public:
     static std::unique_ptr<FusedDecodeStack> try_build(const DecoderModel& model, const CacheManager& cache);
 
     // Up to 16 tokens, and no more (token, key/value head) pairs than the GPU has SMs: beyond that the attention phase
-    // takes two rounds and the part-by-part path with its overlapped launches is faster (measured: GPT-2 small at 14
-    // tokens 537 us against 486 us, medium at 12 tokens 1,042 us against 1,005 us).  And only for layers heavy enough:
-    // the one kernel streams a layer's matrices better (it asks for them while blocks wait at its barriers: about 1.7 us
-    // more a layer from GPT-2 small's 14 MB to medium's 25 MB, against 4.2 us part by part), the part-by-part path has
-    // the shorter chain per layer (small: 28.8 against 29.5 us a layer, 8 tokens: 396 against 417 us a step; medium: 33.0
-    // against 31.2 us, 864 against 803 us), so the one kernel is taken from 18 MB of matrices a layer on.
+    // takes two rounds (measured: GPT-2 small at 14 tokens 537 us against 486 us part by part).
     bool accepts(int n_tokens) const;
-    static constexpr int64_t kMinLayerBytes = 18 << 20;
-    // Lifts that last condition (tests of the kernel with tiny models; measurements).
-    void take_light_layers() { light_layers_too_ = true; }
     // Computes the logits of a decode step ([n_tokens, vocab] float32, valid until the next run).
     Rows run(StepContext& ctx);
     // Time stamps from inside the kernel (a measuring aid): once switched on, every launch has block 0 write the
@@ -58,8 +55,6 @@ private:
     const float* lnf_b_ = nullptr;
     float lnf_eps_ = 0.0f;
     DeviceBuffer layers_, x_, q_, att_, inner_, logits_, partial_, counters_, barrier_, stamps_;
-    int64_t min_layer_bytes_ = 0;    // the lightest layer's matrices
-    bool light_layers_too_ = false;
     uint64_t launches_ = 0;
 };
 

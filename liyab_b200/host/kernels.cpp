@@ -82,6 +82,21 @@ bool tcgen05_accepts(const Rows& a, const Tensor& w) {
            aligned16(a.data) && aligned16(w.data);
 }
 
+bool gemm_rows_normed_supports(const Runtime& rt, const Rows& x, const Tensor& w, int m) {
+    return rt.dtype == DType::BF16 && x.dtype == DType::F32 && w.dtype == DType::BF16 && x.cols == w.dim(1) &&
+           lb_gemm_rows_normed_supports(x.data, x.stride, w.data, w.dim(1), m, static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1))) != 0;
+}
+
+void gemm_rows_normed(cudaStream_t s, const Rows& x, const float* gain, const float* offset, float eps, const Tensor& w, const float* bias,
+                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv) {
+    check(lb_gemm_rows_normed(code(out.dtype, "out"), x.f32(), x.stride, gain, offset, eps, w.data, w.dim(1), bias,
+                              residual ? residual->f32() : nullptr, residual ? residual->stride : 0, out.data, out.stride, m,
+                              static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1)), act, kv ? kv->cache : nullptr,
+                              kv ? kv->slot_mapping : nullptr, kv ? kv->q_dim : 0, kv ? kv->n_kv_head : 0, kv ? kv->head_dim : 0,
+                              kv ? kv->page_size : 0, s),
+          "gemm_rows_normed");
+}
+
 int gemm_splits(int m, int n, int k) {
     // How many ways K is split for a product of few tokens: enough blocks for most of the GPU's SMs.
     if (m > 64 || m <= 0) return 1;

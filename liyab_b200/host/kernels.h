@@ -53,6 +53,11 @@ void gemm_tcgen05(cudaStream_t s, const Rows& a, const Tensor& w, const float* b
 // blocks and a second half wins, at 8 tokens as at 64).
 inline constexpr int kRowsMaxK = 1024;
 bool gemm_rows_supports(const Rows& a, const Tensor& w, int m);
+// The same product with the rows of the float32 matrix x normalised inside the kernel (LayerNorm: gain, offset or
+// null, eps): up to 16 tokens, K up to 1024, bfloat16 weights.
+bool gemm_rows_normed_supports(const Runtime& rt, const Rows& x, const Tensor& w, int m);
+void gemm_rows_normed(cudaStream_t s, const Rows& x, const float* gain, const float* offset, float eps, const Tensor& w, const float* bias,
+                      const Rows& out, int m, int act, const Rows* residual, const KvDestination* kv);
 void gemm_rows(cudaStream_t s, const Rows& a, const Tensor& w, const float* bias, const Rows& out, int m, int act,
                const Rows* residual, const KvDestination* kv);
 int gemm_persistent_tile(const Rows& a, const Tensor& w, const Rows& out, int m, const Rows* residual);

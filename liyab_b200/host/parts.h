@@ -129,11 +129,23 @@ public:
     virtual bool capturable() const { return false; }
 };
 
+// What a norm may hand to the part after it instead of its output: the recipe of a LayerNorm with 32-bit two-pass
+// statistics, y = (x - mean) / sqrt(var + eps) * gain + offset (gain and offset may be null).  A part that can apply
+// it while it reads its input (a projection of a few tokens normalises the rows inside its kernel) saves the launch.
+struct NormRecipe {
+    const float* gain = nullptr;
+    const float* offset = nullptr;
+    float eps = 0.0f;
+};
+
 class Norm : public Part {
 public:
     // out[r] = norm(x[rows ? rows[r] : r]) for r < n_rows; x is the float32 residual stream,
     // `rows` a device array or null.
     virtual void forward(StepContext& ctx, const Rows& x, const Rows& out, int n_rows, const int32_t* rows) = 0;
+    // The recipe, where the norm is of that kind; an arrangement may then offer the un-normalised rows and the recipe
+    // to the part after the norm (forward_from) and only runs the norm itself where that part declines.
+    virtual std::optional<NormRecipe> recipe() const { return std::nullopt; }
 };
 
 class PositionEncoding : public Part {
@@ -149,11 +161,16 @@ public:
     virtual std::optional<StateNeed> state_need() const { return std::nullopt; }
     // Adds the mixer's output for the step's tokens to the residual stream x; `h` is its normalised input.
     virtual void forward(StepContext& ctx, const Rows& h, const Rows& x, CacheUnit unit) = 0;
+    // The same from the un-normalised rows `x_in` (float32) and the norm's recipe; false (and nothing done) where the
+    // mixer cannot apply the recipe itself for this step.
+    virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x, CacheUnit unit) { return false; }
 };
 
 class FeedForward : public Part {
 public:
     virtual void forward(StepContext& ctx, const Rows& h, const Rows& x) = 0;
+    // As Mixer::forward_from.
+    virtual bool forward_from(StepContext& ctx, const Rows& x_in, const NormRecipe& norm, const Rows& x) { return false; }
 };
 
 // The built parts of one layer, by slot name.

@@ -27,7 +27,7 @@ struct ReplayerOptions {
     int max_requests = 16;
     int num_pages = 0;              // 0: from max_tokens
     bool cuda_graphs = false;
-    int fused_decode = 1;            // 0 never, 1 where it is expected to win, 2 wherever it fits
+    bool fused_decode = false;
     int max_step_tokens = 0;        // scratch sized up front for this many tokens (what lets steps with portions be captured)
 };
 

@@ -21,8 +21,7 @@ Stepper::Stepper(DecoderModel& model_, CacheManager& cache_, const StepperOption
     cache.stream = model.runtime.stream;
     model_capturable_ = model.capturable();
     // Decode steps of a few tokens go to the one-kernel path where the model is made of standard parts.
-    if (o.fused_decode != 0) fused_ = FusedDecodeStack::try_build(model, cache);
-    if (fused_ != nullptr && o.fused_decode == 2) fused_->take_light_layers();
+    if (o.fused_decode) fused_ = FusedDecodeStack::try_build(model, cache);
 }
 
 Stepper::~Stepper() {

@@ -56,7 +56,7 @@ struct StepperOptions {
     int max_step_tokens = 0;        // scratch is sized for this many tokens up front (0: grows on demand)
     int max_logit_rows = 0;         // and for this many wanted rows
     bool cuda_graphs = false;
-    int fused_decode = 1;            // 0 never, 1 where it is expected to win, 2 wherever it fits
+    bool fused_decode = false;
     int max_positions = 0;          // 0: the model's
 };
 

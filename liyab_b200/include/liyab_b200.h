@@ -57,9 +57,10 @@ typedef struct lb_engine_config {
     int32_t num_pages;             /* 0: enough for max_sequences full contexts, within kv_memory_fraction */
     float kv_memory_fraction;      /* of the free device memory, at most, for the cache when num_pages is 0 (default 0.5) */
     int32_t cuda_graphs;           /* nonzero (default): replay captured graphs for steps whose shape repeats */
-    int32_t fused_decode;          /* the one-kernel decode step for up to 16 requests: 0 never, 1 (default) where it is
-                                      expected to beat the part-by-part path (layers of 18 MB of matrices or more), 2 wherever
-                                      the kernel takes the model */
+    int32_t fused_decode;          /* nonzero: decode steps of up to 16 requests run as one persistent kernel where that
+                                      kernel takes the model.  Default 0: the part-by-part path (one-launch products,
+                                      launches that overlap the kernel before, a captured graph) is faster at every
+                                      size measured */
     int32_t pipeline;              /* nonzero (default): plan and launch step n+1 while step n runs */
     int32_t profile_phases;        /* nonzero: time every step's phases (slower: part by part, one step at a time) */
 } lb_engine_config;
@@ -255,7 +256,7 @@ typedef struct lb_replayer_options {
     int32_t max_requests;          /* default 16 */
     int32_t num_pages;             /* 0: from max_tokens */
     int32_t cuda_graphs;           /* default 0 */
-    int32_t fused_decode;          /* 0 never, 1 (default) where expected to win, 2 wherever it fits: as lb_engine_config */
+    int32_t fused_decode;          /* default 0; as lb_engine_config */
     int32_t max_step_tokens;       /* scratch sized up front (0: grows on demand; steps with portions are captured only within it) */
 } lb_replayer_options;
 LB_API void lb_replayer_options_default(lb_replayer_options* options);

@@ -23,6 +23,7 @@ GPT2_SMALL = dict(model_type="gpt2", n_layer=12, n_embd=768, n_head=12, n_inner=
                   n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
 GPT2_SIZES = {"small": GPT2_SMALL,
               "medium": dict(GPT2_SMALL, n_layer=24, n_embd=1024, n_head=16, n_inner=4096),
+              "large": dict(GPT2_SMALL, n_layer=36, n_embd=1280, n_head=20, n_inner=5120),
               "xl": dict(GPT2_SMALL, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)}
 
 
@@ -196,7 +197,7 @@ def case_decode_step(args) -> None:
     from .engine import Replayer
     B = args.batch
     rep = Replayer(_model_folder(args.layers, args.dtype, args.size), args.dtype, max_tokens=B * 1024, max_requests=B,
-                   cuda_graphs=not args.eager, fused_decode=False if args.no_fused else (True if args.fused else None), max_step_tokens=1024)
+                   cuda_graphs=not args.eager, fused_decode=args.fused and not args.no_fused, max_step_tokens=1024)
     r = rep.bench_decode(B, args.context, args.reps, 3)
     path = "fused" if r["fused_steps"] else ("graph" if r["graph_steps"] else "parts")
     print(f"decode-step size={args.size} batch={B} layers={len(rep.info['spec']['layers'])} context~{r['mean_context']:.0f} path={path}: "
@@ -294,7 +295,7 @@ def main(argv=None) -> int:
         p.add_argument("--reps", type=int, default=10)
         p.add_argument("--eager", action="store_true", help="no captured graphs")
         p.add_argument("--no-fused", action="store_true", help="not the one-kernel decode step")
-        p.add_argument("--fused", action="store_true", help="the one-kernel decode step wherever it fits (default: where it is expected to win)")
+        p.add_argument("--fused", action="store_true", help="decode steps of up to 16 requests as one persistent kernel (default: part by part)")
         p.add_argument("--stamps", action="store_true", help="decode-step: per-phase times from inside the one-kernel step")
     args = ap.parse_args(argv)
     {"gemm": case_gemm, "generic-attention": case_generic_attention, "gemm-f32": case_gemm_f32, "decode-attention": case_decode_attention, "prefill-attention": case_prefill_attention, "sample": case_sample, "decode-step": case_decode_step,

@@ -32,6 +32,8 @@ _SIGNATURES = {
     "lb_gemm_tcgen05": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _i, _p, _p, _i, _p],
     "lb_gemm_tcgen05_status": [_p],
     "lb_gemm_rows_supports": [_p, _l, _p, _l, _i, _i, _i],
+    "lb_gemm_rows_normed_supports": [_p, _l, _p, _l, _i, _i, _i],
+    "lb_gemm_rows_normed": [_i, _p, _l, _p, _p, _f, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_rows": [_i, _p, _l, _p, _l, _p, _p, _l, _p, _l, _i, _i, _i, _i, _p, _p, _i, _i, _i, _i, _p],
     "lb_gemm_persistent_tile": [_i, _p, _l, _p, _l, _p, _l, _p, _l, _i, _i, _i],
     "lb_gemm_persistent_timing": [_p],
@@ -248,6 +250,22 @@ def gemm_rows(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
                              _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
                              residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n, k,
                              ACTIVATIONS[activation], *_kv_args(kv), stream_ptr()), "gemm_rows")
+    return out
+
+
+def gemm_rows_normed(x: torch.Tensor, gain: Optional[torch.Tensor], offset: Optional[torch.Tensor], eps: float, w: torch.Tensor,
+                     bias: Optional[torch.Tensor], out: torch.Tensor, m: int, activation: str = "none",
+                     residual: Optional[torch.Tensor] = None, kv: Optional[tuple] = None) -> torch.Tensor:
+    """out[:m] = act(LayerNorm(x[:m]) @ w.T + bias) + residual for up to 16 tokens and K up to 1024: the rows are
+    normalised inside the product's kernel.  `kv` as for gemm_rows."""
+    n, k = w.shape
+    cache, slots, q_dim, n_kv_head, head_dim, page_size = _kv_args(kv)
+    check(lib().lb_gemm_rows_normed(_code(out.dtype, "out"), _dev(x, "x", torch.float32), x.stride(0), _opt(gain, "gain", torch.float32),
+                                    _opt(offset, "offset", torch.float32), float(eps), _dev(w, "w", torch.bfloat16), w.stride(0),
+                                    _opt(bias, "bias", torch.float32), _opt(residual, "residual", torch.float32),
+                                    residual.stride(0) if residual is not None else 0, _dev(out, "out"), out.stride(0), m, n, k,
+                                    ACTIVATIONS[activation], cache, slots, q_dim, n_kv_head, head_dim, page_size, stream_ptr()),
+          "gemm_rows_normed")
     return out
 
 

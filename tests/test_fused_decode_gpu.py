@@ -118,6 +118,8 @@ def test_decode_steps_of_dozens_of_requests(name, graphs, folders):
 
 def test_models_of_other_parts_do_not_take_the_fused_path(tmp_path):
     from liyab_b200.engine import Replayer
-    assert not Replayer(write_model(str(tmp_path), "B", "bfloat16"), "bfloat16", max_tokens=256).info["fused"]    # head size 32 is not one the kernel takes
-    assert not Replayer(write_model(str(tmp_path), "D", "float32"), "float32", max_tokens=256).info["fused"]      # the 32-bit engine keeps its part-by-part kernels
-    assert Replayer(write_model(str(tmp_path), "D", "bfloat16"), "bfloat16", max_tokens=256).info["fused"]
+    on = dict(max_tokens=256, fused_decode=True)
+    assert not Replayer(write_model(str(tmp_path), "B", "bfloat16"), "bfloat16", **on).info["fused"]    # head size 32 is not one the kernel takes
+    assert not Replayer(write_model(str(tmp_path), "D", "float32"), "float32", **on).info["fused"]      # the 32-bit engine keeps its part-by-part kernels
+    assert Replayer(write_model(str(tmp_path), "D", "bfloat16"), "bfloat16", **on).info["fused"]
+    assert not Replayer(write_model(str(tmp_path), "D", "bfloat16"), "bfloat16", max_tokens=256).info["fused"]     # it is an option, off unless asked for

@@ -637,3 +637,39 @@ def test_gemm_tcgen05_split_k(dev, out_dtype, M, N, K, splits):
         ops.gemm_tcgen05(a, w, bias, x, M, "none", residual=x, partial=partial, counters=counters, n_splits=splits)
         want = a.double() @ w.double().t() + bias.double() + res.double()
         assert (x.double() - want).abs().max().item() <= tol * max(1.0, want.abs().max().item())
+
+
+@pytest.mark.parametrize("out_dtype,M,N,K", [
+    (torch.bfloat16, 8, 2304, 768), (torch.bfloat16, 1, 130, 72), (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 768, 768),
+    (torch.float32, 13, 1000, 328), (torch.bfloat16, 9, 4096, 1024)])
+def test_gemm_rows_with_layernorm_made_in_the_kernel(dev, out_dtype, M, N, K):
+    """The product of a few tokens whose activations are the LayerNorm of float32 rows, normalised by every block
+    itself: as the LayerNorm kernel followed by the plain product (to a rounding of bfloat16 here and there: the two sum a
+    row's statistics in different trees), and right against float64."""
+    from liyab_b200 import ops
+    x = _rand((M + 2, K + 8), 70, dev) * 3.0 + 0.5
+    gain, offs = _rand((K,), 71, dev) * 0.1 + 1.0, _rand((K,), 72, dev) * 0.1
+    w, bias = _rand((N, K), 73, dev, torch.bfloat16, 0.2), _rand((N,), 74, dev)
+    res = _rand((M, N), 75, dev)
+    eps = 1e-5
+    normed = torch.empty((M, K), dtype=torch.bfloat16, device=dev)
+    ops.layernorm(x[:M, :K].contiguous(), gain, offs, eps, normed, M)
+    for act in ("none", "gelu_tanh"):
+        want = torch.empty((M, N), dtype=out_dtype, device=dev)
+        ops.gemm_rows(normed, w, bias, want, M, act)
+        got = torch.full((M, N), float("nan"), dtype=out_dtype, device=dev)
+        ops.gemm_rows_normed(x[:, :K], gain, offs, eps, w, bias, got, M, act)
+        assert (got.double() - want.double()).abs().max().item() <= 1e-2 * max(1.0, want.double().abs().max().item()), act
+    xd = x[:M, :K].double()
+    ref_normed = (xd - xd.mean(1, keepdim=True)) / torch.sqrt(xd.var(1, unbiased=False, keepdim=True) + eps) * gain.double() + offs.double()
+    base = ref_normed.float().to(torch.bfloat16).double() @ w.double().t()
+    scale = max(1.0, base.abs().max().item())
+    if out_dtype == torch.float32:
+        out2 = res.clone()
+        ops.gemm_rows_normed(x[:, :K], gain, None, eps, w, bias, out2, M, "none", residual=out2)
+        ref2 = ((xd - xd.mean(1, keepdim=True)) / torch.sqrt(xd.var(1, unbiased=False, keepdim=True) + eps) * gain.double())
+        base2 = ref2.float().to(torch.bfloat16).double() @ w.double().t()
+        assert (out2.double() - (base2 + bias.double() + res.double())).abs().max().item() <= 2e-3 * scale
+    got = torch.empty((M, N), dtype=out_dtype, device=dev)
+    ops.gemm_rows_normed(x[:, :K], gain, offs, eps, w, bias, got, M)
+    assert (got.double() - (base + bias.double())).abs().max().item() <= (2e-3 if out_dtype == torch.float32 else 1e-2) * scale
