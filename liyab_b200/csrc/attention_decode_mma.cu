@@ -103,13 +103,9 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     const int tile0 = begin / kTile;                                                // first tile of the range
     const int n_tiles = end > begin ? (end - 1) / kTile + 1 - tile0 : 0;
 
-    // Positions and block table came from the host before any kernel of the step; queries, and the newest keys and
-    // values, come from the kernel before this one.
-    lb_wait_for_predecessor();
-    lb_dependents_may_launch();
-    // Q as the A operand: row r = query head kvh * G + r (rows past G are zero).
+    // Q as the A operand: row r = query head kvh * G + r (rows past G are zero).  Filled after the wait below.
     uint32_t qf[KS][4];
-    {
+    auto load_queries = [&]() {
         const __nv_bfloat16* q_seq = q + (size_t)seq * q_stride + (size_t)kvh * G * HD;
 #pragma unroll
         for (int kk = 0; kk < KS; ++kk) {
@@ -119,7 +115,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
             qf[kk][2] = g < G ? *reinterpret_cast<const uint32_t*>(q_seq + (size_t)g * HD + c + 8) : 0u;
             qf[kk][3] = g + 8 < G ? *reinterpret_cast<const uint32_t*>(q_seq + (size_t)(g + 8) * HD + c + 8) : 0u;
         }
-    }
+    };
     const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
     // This warp's i-th tile (tile index tile0 + warp + kWarps i) -> stage.  Rows outside [begin, end) are not read
     // and arrive as zeros: their scores are masked, and a zero weight times whatever the cache holds there (it
@@ -173,9 +169,23 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
         __syncwarp();
     }
     int gave_up_at = -1;
+    // Positions and block table came from the host before any kernel of the step, and keys and values of earlier
+    // positions from earlier steps: the first tiles travel before this kernel waits for the one before it, all but
+    // a tile that holds the request's newest position, which that kernel writes (TMA tiles only: the other path counts
+    // its copies in groups, in order).  Queries come from that kernel too.
+    const int newest_tile = pos / kTile;
+    bool held_back[kStages - 1 > 0 ? kStages - 1 : 1];
 #pragma unroll
     for (int i = 0; i < kStages - 1; ++i) {          // kStages - 1 tiles ahead; a group per tile, empty past the end
-        if (i < my_tiles) load_tile(i, i);
+        held_back[i] = !TMA || tile0 + warp + kWarps * i == newest_tile;
+        if (i < my_tiles && !held_back[i]) load_tile(i, i);
+    }
+    lb_wait_for_predecessor();
+    lb_dependents_may_launch();
+    load_queries();
+#pragma unroll
+    for (int i = 0; i < kStages - 1; ++i) {
+        if (i < my_tiles && held_back[i]) load_tile(i, i);
         cp_async_commit();
     }
     for (int i = 0; i < my_tiles; ++i) {
