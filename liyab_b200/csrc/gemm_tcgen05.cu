@@ -303,19 +303,25 @@ struct FinishKv {
 template <typename TO>
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, const float* __restrict__ bias, const float* residual,
                                      int64_t ldr, TO* out, int64_t ldo, int M, int N, int n_splits, int act, const FinishKv kv) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const bool mine = idx < M * N;
+    const int t = mine ? idx / N : 0, f = mine ? idx - t * N : 0;
+    // The bias is a weight, and the residual was complete before the product whose sums this kernel finishes began
+    // its own work (that product waited for the kernel before it): both are asked for before this kernel waits for
+    // the product.  (Through L2: what an SM's first-level cache may still hold of the residual is older.)
+    const float b = (mine && bias != nullptr) ? __ldg(bias + f) : 0.0f;
+    const float r = (mine && residual != nullptr) ? __ldcg(residual + (size_t)t * ldr + f) : 0.0f;
     lb_wait_for_predecessor();
     lb_dependents_may_launch();
-    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx >= M * N) return;
-    const int t = idx / N, f = idx - t * N;
+    if (!mine) return;
     float v[16];
 #pragma unroll
     for (int sp = 0; sp < 16; ++sp) v[sp] = sp < n_splits ? partial[((size_t)sp * M + t) * N + f] : 0.0f;
     float acc = 0.0f;
 #pragma unroll
     for (int sp = 0; sp < 16; ++sp) acc += v[sp];
-    float y = lb_activate(acc + (bias != nullptr ? bias[f] : 0.0f), act);
-    if (residual != nullptr) y += residual[(size_t)t * ldr + f];
+    float y = lb_activate(acc + b, act);
+    if (residual != nullptr) y += r;
     out[(size_t)t * ldo + f] = lb_from_float<TO>(y);
     if (kv.cache != nullptr && f >= kv.q_dim) {
         const int slot = kv.slot_mapping[t];
