@@ -28,7 +28,6 @@ constexpr int kChunk = 256;           // columns of the activations per chunk: o
 constexpr int kChunkLd = kChunk + 32; // row stride in a buffer: 64 bytes mod 128, conflict-free 16-byte reads
 constexpr int kMaxRows = 64;
 constexpr int kWRegs = 16;            // 16-byte weight pieces a thread holds: groups per pass x chunks
-constexpr int kNormLd = 4 * kChunk + 32;   // row stride where all columns (up to 1024) of normalised rows are kept
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
@@ -129,18 +128,24 @@ __device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bflo
 // MT: tiles of 16 tokens (1 to 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
 // of up to 1024, 2048 or 4096 (NG x chunks = the 16 weight pieces a thread holds: all of a pass's weights are
 // requested at its start, one DRAM round trip, and used as the chunks of activations come in).
-template <int MT, int NG, typename TO, bool NORM = false>
+// STAGE: how the activations reach shared memory.  0: chunk by chunk through two buffers (any number of tokens).
+// 1 (up to 16 tokens): all columns at once, one round trip, kept for all of the block's passes.  2 (up to 16 tokens,
+// K up to 1024): the same, made here from the float32 rows by a LayerNorm.
+template <int MT, int NG, typename TO, int STAGE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
                  const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M, int N, int K,
                  int act, KvScatter kv, RowNorm norm) {
-    static_assert(!NORM || (MT == 1 && NG == 4), "rows are normalised in the kernel for up to 16 tokens and K up to 1024");
+    static_assert(STAGE == 0 || MT == 1, "all columns at once for up to 16 tokens only");
+    static_assert(STAGE != 2 || NG == 4, "rows are normalised in the kernel for K up to 1024");
+    constexpr bool FULL = STAGE != 0;
     constexpr int kRows = MT * 16, MC = kWRegs / NG;
     extern __shared__ __align__(16) uint8_t smem_bytes[];
-    // The activations: two buffers of one chunk each, [2][kRows][kChunkLd]; or (NORM) all columns at once, [16][kNormLd].
+    // The activations: two buffers of one chunk each, [2][kRows][kChunkLd]; or (FULL) all columns at once, [16][ld_full].
     __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
-    constexpr size_t kActBytes = NORM ? (size_t)16 * kNormLd * sizeof(__nv_bfloat16) : (size_t)2 * kRows * kChunkLd * sizeof(__nv_bfloat16);
-    float* red_s = reinterpret_cast<float*>(smem_bytes + kActBytes);   // [kWarps][NG][MT][128]
+    const int ld_full = (K + kChunk - 1) / kChunk * kChunk + 32;        // 64 bytes mod 128 as well
+    const size_t act_bytes = FULL ? (size_t)16 * ld_full * sizeof(__nv_bfloat16) : (size_t)2 * kRows * kChunkLd * sizeof(__nv_bfloat16);
+    float* red_s = reinterpret_cast<float*>(smem_bytes + act_bytes);   // [kWarps][NG][MT][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n_groups = (N + 7) / 8;
     const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -178,29 +183,41 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             for (int m = 0; m < MT; ++m) acc[i][m][0] = acc[i][m][1] = acc[i][m][2] = acc[i][m][3] = 0.0f;
         if (gp == g_begin) {
             // The first pass's weights are under way; the activations come from the kernel before this one.
-            if constexpr (NORM) {
-                layernorm_rows_to_smem(norm, M, K, act_s, kNormLd, n_chunks * kChunk);
+            if constexpr (STAGE == 2) {
+                layernorm_rows_to_smem(norm, M, K, act_s, ld_full, n_chunks * kChunk);
+                __syncthreads();
+            } else if constexpr (STAGE == 1) {
+                lb_wait_for_predecessor();
+                lb_dependents_may_launch();
+                const int pieces = n_chunks * kChunk / 8;
+                for (int idx = threadIdx.x; idx < 16 * pieces; idx += kThreads) {
+                    const int r = idx / pieces, p = idx - r * pieces;
+                    const bool valid = r < M && p * 8 < K;
+                    cp_async16(act_s + r * ld_full + p * 8, A + (valid ? (size_t)r * lda + p * 8 : 0), valid);
+                }
+                cp_async_commit();
+                cp_async_wait<0>();
                 __syncthreads();
             } else {
                 lb_wait_for_predecessor();
                 lb_dependents_may_launch();
             }
         }
-        if constexpr (!NORM) {
+        if constexpr (!FULL) {
             stage(0);
             cp_async_commit();
         }
 #pragma unroll
         for (int c = 0; c < MC; ++c) {
             if (c < n_chunks) {                                 // the same for every thread
-                if constexpr (!NORM) {
+                if constexpr (!FULL) {
                     if (c + 1 < n_chunks) stage(c + 1);
                     cp_async_commit();
                     cp_async_wait<1>();
                     __syncthreads();
                 }
-                constexpr int kLd = NORM ? kNormLd : kChunkLd;
-                const __nv_bfloat16* buf = (NORM ? act_s + c * kChunk : act_s + (size_t)(c & 1) * kRows * kChunkLd) + warp * 32 + t * 8;
+                const int kLd = FULL ? ld_full : kChunkLd;
+                const __nv_bfloat16* buf = (FULL ? act_s + c * kChunk : act_s + (size_t)(c & 1) * kRows * kChunkLd) + warp * 32 + t * 8;
                 if (c * kChunk + warp * 32 < K) {
 #pragma unroll
                     for (int m = 0; m < MT; ++m) {
@@ -215,7 +232,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
                         }
                     }
                 }
-                if constexpr (!NORM) __syncthreads();        // the buffer is free: the chunk after next goes into it
+                if constexpr (!FULL) __syncthreads();        // the buffer is free: the chunk after next goes into it
             }
         }
         // Partial tiles of the eight warps -> shared memory -> summed in warp order -> epilogue.
@@ -263,29 +280,30 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
     }
 }
 
-template <int MT, int NG, typename TO, bool NORM = false>
+template <int MT, int NG, typename TO, int STAGE = 0>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
            void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s, RowNorm norm = RowNorm{}) {
-    constexpr size_t act_bytes = NORM ? (size_t)16 * kNormLd * sizeof(__nv_bfloat16) : (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16);
-    constexpr size_t smem = act_bytes + (size_t)kWarps * NG * MT * 128 * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
+    const size_t ld_full = (size_t)(K + kChunk - 1) / kChunk * kChunk + 32;
+    const size_t act_bytes = STAGE != 0 ? 16 * ld_full * sizeof(__nv_bfloat16) : (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16);
+    const size_t smem = act_bytes + (size_t)kWarps * NG * MT * 128 * sizeof(float);
+    static size_t configured = 0;
+    if (smem > configured) {
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO, STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured = smem;
     }
     const int n_groups = (N + 7) / 8;
     const int grid = n_groups < n_sm ? n_groups : n_sm;
-    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO, NORM>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
+    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO, STAGE>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
                                        (const __nv_bfloat16*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, kv, norm));
     return LB_OK;
 }
 
-template <int MT, typename TO>
+template <int MT, typename TO, int STAGE = 0>
 int launch_by_k(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
                 void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s) {
-    if (K <= 4 * kChunk) return launch<MT, 4, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
-    if (K <= 8 * kChunk) return launch<MT, 2, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
-    return launch<MT, 1, TO>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
+    if (K <= 4 * kChunk) return launch<MT, 4, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
+    if (K <= 8 * kChunk) return launch<MT, 2, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
+    return launch<MT, 1, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
 }
 
 }  // namespace
@@ -334,8 +352,8 @@ extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, c
     const RowNorm norm{x, ldx, gain, offset, eps};
     auto s = static_cast<cudaStream_t>(stream);
     if (out_dtype == LB_F32)
-        return launch<1, 4, float, true>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
-    return launch<1, 4, __nv_bfloat16, true>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
+        return launch<1, 4, float, 2>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
+    return launch<1, 4, __nv_bfloat16, 2>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
 }
 
 extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
@@ -364,7 +382,9 @@ extern "C" int lb_gemm_rows(int out_dtype, const void* A, int64_t lda, const voi
 #define LB_GO(MT)                                                                                                          \
     return out_dtype == LB_F32 ? launch_by_k<MT, float>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)   \
                                : launch_by_k<MT, __nv_bfloat16>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)
-    if (mt <= 1) LB_GO(1);
+    if (mt <= 1)           // up to 16 tokens: all columns of the activations at once
+        return out_dtype == LB_F32 ? launch_by_k<1, float, 1>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s)
+                                   : launch_by_k<1, __nv_bfloat16, 1>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
     if (mt == 2) LB_GO(2);
     if (mt == 3) LB_GO(3);
     LB_GO(4);

@@ -170,7 +170,7 @@ public:
         a.page_size = view->group->page_size;
         const kernels::KvDestination dest{cache, view->slot_mapping, q_dim, a.n_kv_head, a.head_dim, a.page_size};
         const Tensor& w = qkv.weight;
-        if (unit.write && dt == DType::BF16 && T <= 64 && w.dim(1) <= kernels::kRowsMaxK && kernels::gemm_rows_supports(h, w, T)) {
+        if (unit.write && dt == DType::BF16 && kernels::gemm_rows_takes(T, static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1)), ctx.runtime.sm_count) && kernels::gemm_rows_supports(h, w, T)) {
             // A step of a few dozen tokens: the projection's epilogue also puts the new keys and values into their pages.
             kernels::gemm_rows(ctx.stream(), h, w, qkv.bias, qkv_out, T, kernels::kNone, nullptr, &dest);
         } else if (unit.write && dt == DType::BF16 && T > 64 && kernels::gemm_persistent_tile(h, w, qkv_out, T, nullptr) > 0 &&

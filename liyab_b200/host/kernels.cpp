@@ -97,6 +97,14 @@ void gemm_rows_normed(cudaStream_t s, const Rows& x, const float* gain, const fl
           "gemm_rows_normed");
 }
 
+bool gemm_rows_takes(int m, int n, int k, int sm_count) {
+    if (m < 1 || m > 64) return false;
+    if (k <= kRowsMaxK) return true;
+    if (m > 16 || k > 4096) return false;
+    const int groups = (n + 7) / 8, blocks = std::min(groups, std::max(1, sm_count)), per_block = (groups + blocks - 1) / blocks;
+    return per_block <= (k <= 2048 ? 2 : 1);          // the groups a block holds in its registers at that K
+}
+
 int gemm_splits(int m, int n, int k) {
     // How many ways K is split for a product of few tokens: enough blocks for most of the GPU's SMs.
     if (m > 64 || m <= 0) return 1;
@@ -168,7 +176,7 @@ void linear(const Runtime& rt, Workspace* ws, const Rows& a, const Tensor& w, co
         // Up to 64 tokens: one launch on mma.sync where every block can afford to fetch all activations (measured on
         // B200, 64 tokens: 6-7 us against 8-9 us for K = 768; for K = 3072 the 393 KB of activations per block cost
         // more than the split of K saves: 13 us against 8 us).
-        if (m <= 64 && k <= kRowsMaxK && gemm_rows_supports(a, w, m))
+        if (gemm_rows_takes(m, n, k, rt.sm_count) && gemm_rows_supports(a, w, m))
             return gemm_rows(rt.stream, a, w, bias, out, m, act, residual, nullptr);
         const int splits = ws != nullptr ? gemm_splits(m, n, k) : 1;
         float* partial = nullptr;
@@ -182,7 +190,7 @@ bool linear_with_cache(const Runtime& rt, Workspace* ws, const Rows& a, const Te
                        const KvDestination& kv) {
     if (ws == nullptr || m > 64 || !tcgen05_accepts(a, w)) return false;
     const int n = static_cast<int>(w.dim(0)), k = static_cast<int>(w.dim(1));
-    if (k <= kRowsMaxK && gemm_rows_supports(a, w, m)) return false;          // that kernel has a cache epilogue of its own
+    if (gemm_rows_takes(m, n, k, rt.sm_count) && gemm_rows_supports(a, w, m)) return false;          // that kernel has a cache epilogue of its own
     const int splits = gemm_splits(m, n, k);
     if (lb_gemm_tcgen05_splits(m, k, splits) <= 1) return false;
     check_product(a, w, out, nullptr);

@@ -52,6 +52,10 @@ void gemm_tcgen05(cudaStream_t s, const Rows& a, const Tensor& w, const float* b
 // activations: a reduction length of up to 1024 (measured: with K = 1600 or 3072 the tcgen05 kernel with K split over
 // blocks and a second half wins, at 8 tokens as at 64).
 inline constexpr int kRowsMaxK = 1024;
+// Up to 16 tokens the kernel keeps all columns of the activations, so a longer reduction (up to 4096) is worth it too
+// where a block then asks for all its weights at once: one pass over its feature groups (GPT-2 small's and medium's
+// down projections; GPT-2 XL's projections would take three passes and stay with the split product: 2.30 against 2.16 ms).
+bool gemm_rows_takes(int m, int n, int k, int sm_count);
 bool gemm_rows_supports(const Rows& a, const Tensor& w, int m);
 // The same product with the rows of the float32 matrix x normalised inside the kernel (LayerNorm: gain, offset or
 // null, eps): up to 16 tokens, K up to 1024, bfloat16 weights.

@@ -93,9 +93,9 @@ def test_engine_ends_the_requests_of_a_step_whose_wait_ran_out_and_goes_on(tmp_p
     from liyab_b200.engine import Engine, EngineConfig, device_status, withhold_next
     from liyab_b200.sampling import SamplingParams
     from liyab_b200.weights import write_random_model
-    # An inner size above 1,024: the down projection of a few tokens is then a split tcgen05 product (shorter
-    # reductions take the one-launch mma.sync kernel), the family whose wait this test makes run out.
-    raw, seed = dict(CONFIGS["D"][0], n_inner=1096), CONFIGS["D"][1]
+    # A vocabulary of 20,000: the head of a decode step is then a tcgen05 product (the one-launch mma.sync kernel takes
+    # the layers' projections but not that many features), the family whose wait this test makes run out.
+    raw, seed = dict(CONFIGS["D"][0], vocab_size=20000), CONFIGS["D"][1]
     folder = write_random_model(str(tmp_path / "m"), raw, seed=seed, dtype="bfloat16")
     prompt = random_tokens(77 + seed, 5, raw["vocab_size"])
     params = SamplingParams(temperature=0.0, max_tokens=8)

@@ -390,7 +390,8 @@ def test_gemm_persistent(dev, out_dtype, M, N, K, tile):
     (torch.float32, 17, 768, 768), (torch.float32, 64, 768, 3072), (torch.float32, 33, 1000, 200), (torch.float32, 48, 36, 4096),
     (torch.float32, 50, 130, 1032), (torch.bfloat16, 64, 2304, 768), (torch.bfloat16, 40, 3072, 768), (torch.bfloat16, 25, 4800, 1600),
     (torch.bfloat16, 64, 72, 328), (torch.bfloat16, 18, 5000, 2048), (torch.bfloat16, 1, 2304, 768), (torch.float32, 8, 768, 768),
-    (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 130, 72)])
+    (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 130, 72), (torch.float32, 8, 768, 3072), (torch.bfloat16, 3, 1024, 4096),
+    (torch.float32, 16, 1600, 1600)])
 def test_gemm_rows(dev, out_dtype, M, N, K):
     """The one-launch product for 1 to 64 tokens against float64: every number of token tiles and of groups per
     pass, several passes per block, ragged edges in M, N and K, all epilogues, the residual in place, a strided
