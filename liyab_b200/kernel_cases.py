@@ -73,7 +73,9 @@ def case_gemm(args) -> None:
     bias = torch.randn(args.n, device=dev)
     out = torch.zeros(args.m, args.n, dtype=odt, device=dev)
     res = out if odt == torch.float32 else None
-    if args.one_tile:
+    if args.rows:
+        launch = lambda: ops.gemm_rows(a, w, bias, out, args.m, args.act, residual=res)
+    elif args.one_tile:
         launch = lambda: ops.gemm_tcgen05(a, w, bias, out, args.m, args.act, residual=res, token_tile=args.tile)
     elif args.m > 64 and ops.gemm_persistent_tile(a, w, out, args.m, res) > 0:
         launch = lambda: ops.gemm_persistent(a, w, bias, out, args.m, args.act, residual=res, feature_tile=args.tile)
@@ -242,6 +244,7 @@ def main(argv=None) -> int:
     g.add_argument("--tile", type=int, default=0, help="feature tile of the persistent kernel (token tile with --one-tile)")
     g.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     g.add_argument("--one-tile", action="store_true", help="the one-tile-per-block kernel also for many tokens")
+    g.add_argument("--rows", action="store_true", help="the one-launch mma.sync product (up to 64 tokens) whatever the size")
     g.add_argument("--reps", type=int, default=20)
     d = sub.add_parser("decode-attention")
     d.add_argument("--batch", type=int, default=64)
