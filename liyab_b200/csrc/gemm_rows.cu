@@ -125,83 +125,21 @@ __device__ void layernorm_rows_to_smem(const RowNorm& n, int M, int K, __nv_bflo
     }
 }
 
-// The same for rows of up to 2048 values: the float32 rows come into shared memory first (one round trip), gain and
-// offset too (asked for before the wait), and the three walks over a row read them there.  Same arithmetic.
-__device__ void layernorm_rows_through_smem(const RowNorm& n, int M, int K, __nv_bfloat16* act, int ld, int k_pad, float* rows_s,
-                                            float* gain_s, float* offs_s) {
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n_vec = K / 4;
-    for (int i = threadIdx.x; i < n_vec; i += kThreads) {
-        if (n.gain != nullptr) cp_async16(gain_s + 4 * i, n.gain + 4 * i, true);
-        if (n.offset != nullptr) cp_async16(offs_s + 4 * i, n.offset + 4 * i, true);
-    }
-    cp_async_commit();
-    lb_wait_for_predecessor();
-    lb_dependents_may_launch();
-    for (int idx = threadIdx.x; idx < M * n_vec; idx += kThreads) {
-        const int r = idx / n_vec, i = idx - r * n_vec;
-        cp_async16(rows_s + (size_t)r * K + 4 * i, n.x + (size_t)r * n.ldx + 4 * i, true);
-    }
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-    for (int r = warp; r < 16; r += kWarps) {
-        __nv_bfloat16* dst = act + r * ld;
-        if (r >= M) {
-            for (int i = lane * 8; i < k_pad; i += 256) *reinterpret_cast<uint4*>(dst + i) = make_uint4(0, 0, 0, 0);
-            continue;
-        }
-        const float4* row = reinterpret_cast<const float4*>(rows_s + (size_t)r * K);
-        float sum = 0.0f;
-        for (int i = lane; i < n_vec; i += 32) {
-            const float4 v = row[i];
-            sum += (v.x + v.y) + (v.z + v.w);
-        }
-        const float mean = lb_warp_sum(sum) / (float)K;
-        float ss = 0.0f;
-        for (int i = lane; i < n_vec; i += 32) {
-            const float4 v = row[i];
-            const float d0 = v.x - mean, d1 = v.y - mean, d2 = v.z - mean, d3 = v.w - mean;
-            ss = fmaf(d0, d0, ss);
-            ss = fmaf(d1, d1, ss);
-            ss = fmaf(d2, d2, ss);
-            ss = fmaf(d3, d3, ss);
-        }
-        const float inv = 1.0f / sqrtf(lb_warp_sum(ss) / (float)K + n.eps);
-        for (int i = lane; i < n_vec; i += 32) {
-            const float4 v = row[i];
-            const float4 g = n.gain != nullptr ? reinterpret_cast<const float4*>(gain_s)[i] : make_float4(1.f, 1.f, 1.f, 1.f);
-            const float4 o = n.offset != nullptr ? reinterpret_cast<const float4*>(offs_s)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-            const __nv_bfloat162 lo = __floats2bfloat162_rn((v.x - mean) * inv * g.x + o.x, (v.y - mean) * inv * g.y + o.y);
-            const __nv_bfloat162 hi = __floats2bfloat162_rn((v.z - mean) * inv * g.z + o.z, (v.w - mean) * inv * g.w + o.w);
-            uint2 packed;
-            packed.x = *reinterpret_cast<const uint32_t*>(&lo);
-            packed.y = *reinterpret_cast<const uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(dst + 4 * i) = packed;
-        }
-        for (int i = K + lane; i < k_pad; i += 32) dst[i] = __float2bfloat16_rn(0.0f);
-    }
-}
-
 // MT: tiles of 16 tokens (1 to 4).  NG: feature groups (of 8 features) per pass: 4, 2 or 1, for a reduction length
 // of up to 1024, 2048 or 4096 (NG x chunks = the 16 weight pieces a thread holds: all of a pass's weights are
 // requested at its start, one DRAM round trip, and used as the chunks of activations come in).
 // STAGE: how the activations reach shared memory.  0: chunk by chunk through two buffers (any number of tokens).
 // 1 (up to 16 tokens): all columns at once, one round trip, kept for all of the block's passes.  2 (up to 16 tokens,
-// K up to 1024): the same, made here from the float32 rows by a LayerNorm.  3: the same for K up to 2048, the rows
-// passing through shared memory.
-// WR: the 16-byte weight pieces a thread holds (NG x chunks): 16, or about 40 for up to 16 tokens, where wider rows or
-// more groups in one pass (all of a block's weights in flight at once) beat K split over blocks and a second kernel.
-template <int MT, int NG, typename TO, int STAGE = 0, int WR = kWRegs>
+// K up to 1024): the same, made here from the float32 rows by a LayerNorm.
+template <int MT, int NG, typename TO, int STAGE = 0>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bfloat16* __restrict__ W, int64_t ldw,
                  const float* __restrict__ bias, const float* residual, int64_t ldr, TO* out, int64_t ldo, int M, int N, int K,
                  int act, KvScatter kv, RowNorm norm) {
     static_assert(STAGE == 0 || MT == 1, "all columns at once for up to 16 tokens only");
-    static_assert(STAGE != 2 || NG == 4, "rows are normalised in registers for K up to 1024");
-    static_assert(STAGE != 3 || NG >= 2, "rows are normalised through shared memory for K up to 2048");
+    static_assert(STAGE != 2 || NG == 4, "rows are normalised in the kernel for K up to 1024");
     constexpr bool FULL = STAGE != 0;
-    constexpr int kRows = MT * 16, MC = WR / NG;
+    constexpr int kRows = MT * 16, MC = kWRegs / NG;
     extern __shared__ __align__(16) uint8_t smem_bytes[];
     // The activations: two buffers of one chunk each, [2][kRows][kChunkLd]; or (FULL) all columns at once, [16][ld_full].
     __nv_bfloat16* act_s = reinterpret_cast<__nv_bfloat16*>(smem_bytes);
@@ -210,9 +148,8 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
     float* red_s = reinterpret_cast<float*>(smem_bytes + act_bytes);   // [kWarps][NG][MT][128]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int n_groups = (N + 7) / 8;
-    // Feature groups dealt evenly: the first n_groups % blocks blocks take one more.
-    const int base = n_groups / (int)gridDim.x, extra = n_groups - base * (int)gridDim.x;
-    const int g_begin = (int)blockIdx.x * base + min((int)blockIdx.x, extra), g_end = g_begin + base + ((int)blockIdx.x < extra ? 1 : 0);
+    const int per_cta = (n_groups + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int g_begin = min(n_groups, (int)blockIdx.x * per_cta), g_end = min(n_groups, g_begin + per_cta);
     const int n_chunks = (K + kChunk - 1) / kChunk;            // at most MC (the host checks)
 
     // Chunk c of the activations -> buffer c & 1 (rows past M and columns past K as zeros).
@@ -230,7 +167,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
     for (int gp = g_begin; gp < g_end; gp += NG) {
         const int ng = min(NG, g_end - gp);
         // This warp's k-block of every chunk (columns c * 256 + warp * 32 ...), for every group of the pass.
-        uint4 w[WR];
+        uint4 w[kWRegs];
 #pragma unroll
         for (int c = 0; c < MC; ++c)
 #pragma unroll
@@ -248,11 +185,6 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             // The first pass's weights are under way; the activations come from the kernel before this one.
             if constexpr (STAGE == 2) {
                 layernorm_rows_to_smem(norm, M, K, act_s, ld_full, n_chunks * kChunk);
-                __syncthreads();
-            } else if constexpr (STAGE == 3) {
-                float* rows_s = red_s + (size_t)kWarps * NG * MT * 128;          // [16][K], then gain [K] and offset [K]
-                layernorm_rows_through_smem(norm, M, K, act_s, ld_full, n_chunks * kChunk, rows_s, rows_s + (size_t)16 * K,
-                                            rows_s + (size_t)17 * K);
                 __syncthreads();
             } else if constexpr (STAGE == 1) {
                 lb_wait_for_predecessor();
@@ -275,14 +207,12 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             stage(0);
             cp_async_commit();
         }
-        // Up to 16 tokens: a thread finishes at most kEarly elements of a pass; their bias and residual are asked for
-        // now and arrive under the products instead of after them.
-        constexpr int kEarly = MT == 1 ? (NG * 128 + kThreads - 1) / kThreads : 1;
-        float2 early[kEarly];
+        // Up to 16 tokens: a thread finishes at most two elements of a pass; their bias and residual are asked for now
+        // and arrive under the products instead of after them.
+        float2 early[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
         if constexpr (MT == 1) {
 #pragma unroll
-            for (int e = 0; e < kEarly; ++e) {
-                early[e] = make_float2(0.f, 0.f);
+            for (int e = 0; e < 2; ++e) {
                 const int idx = threadIdx.x + e * kThreads;
                 const int gi = idx / (kRows * 8), rest = idx - gi * kRows * 8, r = rest >> 3, f = (gp + gi) * 8 + (rest & 7);
                 if (gi < ng && r < M && f < N)
@@ -342,10 +272,7 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
                 for (int wp = 0; wp < kWarps; ++wp) v += red_s[((size_t)(wp * NG + gi) * MT + m) * 128 + rr * 8 + cfeat];
                 float y;
                 if constexpr (MT == 1) {                      // element idx = threadIdx.x + 256 e: its bias and residual are here
-                    float2 had = early[0];
-#pragma unroll
-                    for (int e = 1; e < kEarly; ++e)
-                        if (idx >= e * kThreads) had = early[e];
+                    const float2 had = idx < kThreads ? early[0] : early[1];
                     y = lb_activate(v + had.x, act);
                     if (residual != nullptr) y += had.y;
                 } else {
@@ -372,28 +299,20 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
     }
 }
 
-// The widest sets of registers for up to 16 tokens: 6 groups of rows of up to 1792 values, 5 of up to 2048.
-constexpr int kWideK6 = 7 * kChunk, kWideK5 = 8 * kChunk;
-constexpr size_t kSmemLimit = 227 * 1024;
-
-size_t smem_bytes_for(int mt, int ng, int stage, int K) {
-    const size_t ld_full = (size_t)(K + kChunk - 1) / kChunk * kChunk + 32;
-    const size_t act_bytes = stage != 0 ? 16 * ld_full * sizeof(__nv_bfloat16) : (size_t)2 * mt * 16 * kChunkLd * sizeof(__nv_bfloat16);
-    return act_bytes + (size_t)kWarps * ng * mt * 128 * sizeof(float) + (stage == 3 ? (size_t)18 * K * sizeof(float) : 0);
-}
-
-template <int MT, int NG, typename TO, int STAGE = 0, int WR = kWRegs>
+template <int MT, int NG, typename TO, int STAGE = 0>
 int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
            void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s, RowNorm norm = RowNorm{}) {
-    const size_t smem = smem_bytes_for(MT, NG, STAGE, K);
+    const size_t ld_full = (size_t)(K + kChunk - 1) / kChunk * kChunk + 32;
+    const size_t act_bytes = STAGE != 0 ? 16 * ld_full * sizeof(__nv_bfloat16) : (size_t)2 * MT * 16 * kChunkLd * sizeof(__nv_bfloat16);
+    const size_t smem = act_bytes + (size_t)kWarps * NG * MT * 128 * sizeof(float);
     static size_t configured = 0;
     if (smem > configured) {
-        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO, STAGE, WR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_rows_kernel<MT, NG, TO, STAGE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured = smem;
     }
     const int n_groups = (N + 7) / 8;
     const int grid = n_groups < n_sm ? n_groups : n_sm;
-    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO, STAGE, WR>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
+    LB_CHECK_CUDA(lb_launch_overlapped(gemm_rows_kernel<MT, NG, TO, STAGE>, dim3(grid), dim3(kThreads), smem, s, (const __nv_bfloat16*)A, lda,
                                        (const __nv_bfloat16*)W, ldw, bias, residual, ldr, (TO*)out, ldo, M, N, K, act, kv, norm));
     return LB_OK;
 }
@@ -401,14 +320,6 @@ int launch(const void* A, int64_t lda, const void* W, int64_t ldw, const float* 
 template <int MT, typename TO, int STAGE = 0>
 int launch_by_k(const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual, int64_t ldr,
                 void* out, int64_t ldo, int M, int N, int K, int act, KvScatter kv, int n_sm, cudaStream_t s) {
-    if constexpr (MT == 1 && STAGE == 1) {
-        // Longer rows and more groups for a block than the narrow set holds in one pass: the wide sets.
-        const int n_groups = (N + 7) / 8, blocks = n_groups < n_sm ? n_groups : n_sm, per_block = (n_groups + blocks - 1) / blocks;
-        if (K > 4 * kChunk && K <= kWideK6 && per_block > 2)
-            return launch<1, 6, TO, 1, 42>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
-        if (K > kWideK6 && K <= kWideK5 && per_block > 2)
-            return launch<1, 5, TO, 1, 40>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
-    }
     if (K <= 4 * kChunk) return launch<MT, 4, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
     if (K <= 8 * kChunk) return launch<MT, 2, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
     return launch<MT, 1, TO, STAGE>(A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s);
@@ -427,14 +338,13 @@ extern "C" int lb_gemm_rows_supports(const void* A, int64_t lda, const void* W, 
     return (N + 7) / 8 <= 148 * 4 * ng;
 }
 
-// The same product for up to 16 tokens and a reduction length of up to 2048 with the activations made in the kernel:
+// The same product for up to 16 tokens and a reduction length of up to 1024 with the activations made in the kernel:
 // LayerNorm (two-pass 32-bit statistics, eps, gain and offset or null) of the float32 rows x, normalised by every
 // block for itself.  lb_gemm_rows_normed_supports says whether the kernel takes the operands.
 extern "C" int lb_gemm_rows_normed_supports(const void* x, int64_t ldx, const void* W, int64_t ldw, int M, int N, int K) {
-    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K > kWideK5) return 0;
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K > 4 * kChunk) return 0;
     if (K % 8 != 0 || ldx % 4 != 0 || ldw % 8 != 0 || ((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return 0;
-    if (K > 4 * kChunk && smem_bytes_for(1, K <= kWideK6 ? 6 : 5, 3, K) > kSmemLimit) return 0;      // the float32 rows must fit beside the rest
-    return (N + 7) / 8 <= 148 * 4 * (K <= 4 * kChunk ? 4 : K <= kWideK6 ? 6 : 5);
+    return (N + 7) / 8 <= 148 * 4 * 4;
 }
 
 extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, const float* gain, const float* offset, float eps,
@@ -443,7 +353,7 @@ extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, c
                                    int n_kv_head, int head_dim, int page_size, void* stream) {
     LB_CHECK_ARG(out_dtype == LB_BF16 || out_dtype == LB_F32, "gemm_rows_normed: unknown output dtype %d", out_dtype);
     if (!lb_gemm_rows_normed_supports(x, ldx, W, ldw, M, N, K) || ((uintptr_t)gain & 15) != 0 || ((uintptr_t)offset & 15) != 0)
-        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows_normed: takes 1 to 16 tokens, K up to 2048 (rows that fit shared memory) and a multiple of 8, 16-byte aligned bases "
+        return lb_fail(LB_ERR_UNSUPPORTED, "gemm_rows_normed: takes 1 to 16 tokens, K up to 1024 and a multiple of 8, 16-byte aligned bases "
                        "(M=%d N=%d K=%d ldx=%lld ldw=%lld)", M, N, K, (long long)ldx, (long long)ldw);
     LB_CHECK_ARG(ldx >= K && ldw >= K && ldo >= N, "gemm_rows_normed: a row stride is shorter than the row");
     static int n_sm = 0;
@@ -460,16 +370,6 @@ extern "C" int lb_gemm_rows_normed(int out_dtype, const float* x, int64_t ldx, c
                      q_dim, n_kv_head, head_dim);
     const RowNorm norm{x, ldx, gain, offset, eps};
     auto s = static_cast<cudaStream_t>(stream);
-    if (K > kWideK6) {
-        if (out_dtype == LB_F32)
-            return launch<1, 5, float, 3, 40>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
-        return launch<1, 5, __nv_bfloat16, 3, 40>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
-    }
-    if (K > 4 * kChunk) {
-        if (out_dtype == LB_F32)
-            return launch<1, 6, float, 3, 42>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
-        return launch<1, 6, __nv_bfloat16, 3, 42>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
-    }
     if (out_dtype == LB_F32)
         return launch<1, 4, float, 2>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);
     return launch<1, 4, __nv_bfloat16, 2>(nullptr, 0, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, kv, n_sm, s, norm);

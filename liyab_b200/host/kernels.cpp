@@ -84,7 +84,6 @@ bool tcgen05_accepts(const Rows& a, const Tensor& w) {
 
 bool gemm_rows_normed_supports(const Runtime& rt, const Rows& x, const Tensor& w, int m) {
     return rt.dtype == DType::BF16 && x.dtype == DType::F32 && w.dtype == DType::BF16 && x.cols == w.dim(1) &&
-           gemm_rows_takes(m, static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1)), rt.sm_count) &&
            lb_gemm_rows_normed_supports(x.data, x.stride, w.data, w.dim(1), m, static_cast<int>(w.dim(0)), static_cast<int>(w.dim(1))) != 0;
 }
 
@@ -102,10 +101,8 @@ bool gemm_rows_takes(int m, int n, int k, int sm_count) {
     if (m < 1 || m > 64) return false;
     if (k <= kRowsMaxK) return true;
     if (m > 16 || k > 4096) return false;
-    // Up to 16 tokens and longer rows: while one pass covers a block's feature groups (all its weights in flight at
-    // once); the kernel holds 6 groups of rows of up to 1792 values, 5 of up to 2048, 1 of up to 4096.
     const int groups = (n + 7) / 8, blocks = std::min(groups, std::max(1, sm_count)), per_block = (groups + blocks - 1) / blocks;
-    return per_block <= (k <= 1792 ? 6 : k <= 2048 ? 5 : 1);
+    return per_block <= (k <= 2048 ? 2 : 1);          // the groups a block holds in its registers at that K
 }
 
 int gemm_splits(int m, int n, int k) {

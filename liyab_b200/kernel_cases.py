@@ -73,7 +73,19 @@ def case_gemm(args) -> None:
     bias = torch.randn(args.n, device=dev)
     out = torch.zeros(args.m, args.n, dtype=odt, device=dev)
     res = out if odt == torch.float32 else None
-    if args.rows:
+    if args.weights > 1:
+        # A chain of the same product over several weight matrices (more bytes than L2 holds: every launch streams
+        # its weights from DRAM, as a layer's products do in a step).
+        ws, many, turn = _Scratch(dev), [w] + [w.clone() for _ in range(args.weights - 1)], [0]
+
+        def launch():
+            wi = many[turn[0] % len(many)]
+            turn[0] += 1
+            if args.rows:
+                ops.gemm_rows(a, wi, bias, out, args.m, args.act, residual=res)
+            else:
+                ops.linear(a, wi, bias, out, args.m, args.act, residual=res, workspace=ws)
+    elif args.rows:
         launch = lambda: ops.gemm_rows(a, w, bias, out, args.m, args.act, residual=res)
     elif args.one_tile:
         launch = lambda: ops.gemm_tcgen05(a, w, bias, out, args.m, args.act, residual=res, token_tile=args.tile)
@@ -244,6 +256,7 @@ def main(argv=None) -> int:
     g.add_argument("--tile", type=int, default=0, help="feature tile of the persistent kernel (token tile with --one-tile)")
     g.add_argument("--graph", action="store_true", help="time 20 launches captured in a CUDA graph")
     g.add_argument("--one-tile", action="store_true", help="the one-tile-per-block kernel also for many tokens")
+    g.add_argument("--weights", type=int, default=1, help="cycle through this many copies of the weights (with --graph: 20 per graph)")
     g.add_argument("--rows", action="store_true", help="the one-launch mma.sync product (up to 64 tokens) whatever the size")
     g.add_argument("--reps", type=int, default=20)
     d = sub.add_parser("decode-attention")

@@ -391,9 +391,8 @@ def test_gemm_persistent(dev, out_dtype, M, N, K, tile):
     (torch.float32, 50, 130, 1032), (torch.bfloat16, 64, 2304, 768), (torch.bfloat16, 40, 3072, 768), (torch.bfloat16, 25, 4800, 1600),
     (torch.bfloat16, 64, 72, 328), (torch.bfloat16, 18, 5000, 2048), (torch.bfloat16, 1, 2304, 768), (torch.float32, 8, 768, 768),
     (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 130, 72), (torch.float32, 8, 768, 3072), (torch.bfloat16, 3, 1024, 4096),
-    (torch.float32, 16, 1600, 1600), (torch.bfloat16, 8, 4800, 1600), (torch.bfloat16, 13, 6400, 1600), (torch.float32, 4, 2500, 4096),
-    (torch.bfloat16, 16, 9000, 768), (torch.float32, 2, 3840, 1280),,
-    (torch.bfloat16, 16, 5000, 2048)])
+    (torch.float32, 16, 1600, 1600), (torch.bfloat16, 8, 4800, 1600), (torch.float32, 4, 2500, 4096), (torch.bfloat16, 16, 9000, 768),
+    (torch.float32, 2, 3840, 1280)])
 def test_gemm_rows(dev, out_dtype, M, N, K):
     """The one-launch product for 1 to 64 tokens against float64: every number of token tiles and of groups per
     pass, several passes per block, ragged edges in M, N and K, all epilogues, the residual in place, a strided
@@ -644,8 +643,7 @@ def test_gemm_tcgen05_split_k(dev, out_dtype, M, N, K, splits):
 
 @pytest.mark.parametrize("out_dtype,M,N,K", [
     (torch.bfloat16, 8, 2304, 768), (torch.bfloat16, 1, 130, 72), (torch.bfloat16, 16, 3072, 1024), (torch.float32, 5, 768, 768),
-    (torch.float32, 13, 1000, 328), (torch.bfloat16, 9, 4096, 1024), (torch.bfloat16, 8, 4800, 1600), (torch.float32, 3, 1600, 1600),
-    (torch.bfloat16, 16, 6400, 1600), (torch.bfloat16, 5, 3840, 1280), (torch.float32, 11, 1000, 2016), (torch.bfloat16, 2, 520, 1032), (torch.bfloat16, 7, 5900, 1800)])
+    (torch.float32, 13, 1000, 328), (torch.bfloat16, 9, 4096, 1024)])
 def test_gemm_rows_with_layernorm_made_in_the_kernel(dev, out_dtype, M, N, K):
     """The product of a few tokens whose activations are the LayerNorm of float32 rows, normalised by every block
     itself: as the LayerNorm kernel followed by the plain product (to a rounding of bfloat16 here and there: the two sum a
