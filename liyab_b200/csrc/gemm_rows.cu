@@ -207,17 +207,17 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             stage(0);
             cp_async_commit();
         }
-        // Up to 16 tokens: a thread finishes at most two elements of a pass; their bias and residual are asked for now
-        // and arrive under the products instead of after them.
-        float2 early[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-        if constexpr (MT == 1) {
+        // A thread finishes at most kEarly elements of a pass (element idx = threadIdx.x + 256 e); their bias and residual
+        // are asked for now and arrive under the products instead of after them.
+        constexpr int kEarly = (NG * kRows * 8 + kThreads - 1) / kThreads;
+        float2 early[kEarly];
 #pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int idx = threadIdx.x + e * kThreads;
-                const int gi = idx / (kRows * 8), rest = idx - gi * kRows * 8, r = rest >> 3, f = (gp + gi) * 8 + (rest & 7);
-                if (gi < ng && r < M && f < N)
-                    early[e] = make_float2(bias != nullptr ? __ldg(bias + f) : 0.0f, residual != nullptr ? __ldcg(residual + (size_t)r * ldr + f) : 0.0f);
-            }
+        for (int e = 0; e < kEarly; ++e) {
+            early[e] = make_float2(0.f, 0.f);
+            const int idx = threadIdx.x + e * kThreads;
+            const int gi = idx / (kRows * 8), rest = idx - gi * kRows * 8, r = rest >> 3, f = (gp + gi) * 8 + (rest & 7);
+            if (gi < ng && r < M && f < N)
+                early[e] = make_float2(bias != nullptr ? __ldg(bias + f) : 0.0f, residual != nullptr ? __ldcg(residual + (size_t)r * ldr + f) : 0.0f);
         }
 #pragma unroll
         for (int c = 0; c < MC; ++c) {
@@ -262,23 +262,18 @@ gemm_rows_kernel(const __nv_bfloat16* __restrict__ A, int64_t lda, const __nv_bf
             }
         }
         __syncthreads();
-        for (int idx = threadIdx.x; idx < ng * kRows * 8; idx += kThreads) {
+#pragma unroll
+        for (int e = 0; e < kEarly; ++e) {
+            const int idx = threadIdx.x + e * kThreads;
             const int gi = idx / (kRows * 8), rest = idx - gi * kRows * 8, r = rest >> 3, cfeat = rest & 7;
             const int f = (gp + gi) * 8 + cfeat;
-            if (r < M && f < N) {
+            if (gi < ng && r < M && f < N) {
                 const int m = r >> 4, rr = r & 15;
                 float v = 0.0f;
 #pragma unroll
                 for (int wp = 0; wp < kWarps; ++wp) v += red_s[((size_t)(wp * NG + gi) * MT + m) * 128 + rr * 8 + cfeat];
-                float y;
-                if constexpr (MT == 1) {                      // element idx = threadIdx.x + 256 e: its bias and residual are here
-                    const float2 had = idx < kThreads ? early[0] : early[1];
-                    y = lb_activate(v + had.x, act);
-                    if (residual != nullptr) y += had.y;
-                } else {
-                    y = lb_activate(v + (bias != nullptr ? __ldg(bias + f) : 0.0f), act);
-                    if (residual != nullptr) y += residual[(size_t)r * ldr + f];
-                }
+                float y = lb_activate(v + early[e].x, act);
+                if (residual != nullptr) y += early[e].y;
                 out[(size_t)r * ldo + f] = lb_from_float<TO>(y);
                 if (kv.cache != nullptr && f >= kv.q_dim) {
                     // A key or value feature of a fused projection: also into the token's slot of its cache page.
