@@ -17,7 +17,9 @@
 // buffers with cp.async one tile ahead (16-byte chunks XOR-swizzled by the row, so
 // ldmatrix meets no bank twice and nothing is padded), and keeps its own running
 // maximum, sum and output; the warps are merged at the end in warp order, the key
-// ranges by the block that finishes last, in range order.  Softmax, sums and
+// ranges in range order: two to eight ranges are the blocks of one cluster and
+// meet in its first block's shared memory (the launch carries the cluster size),
+// more than eight go through global memory to the block that finishes last.  Softmax, sums and
 // accumulators are 32-bit (exp2 of scores pre-scaled by log2 e).  Measured on
 // B200, 12 heads of 64 over 768 keys: 27 us for 64 requests and 51 us for 128
 // (5.5 and 5.9 TB/s of cache), where the scalar kernel takes 47 us for 64.
@@ -72,7 +74,7 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
                             const int32_t* __restrict__ positions, const int32_t* __restrict__ block_table, int table_stride,
                             __nv_bfloat16* __restrict__ out, int64_t out_stride, float* __restrict__ partial,
                             int* __restrict__ counters, int n_head, int n_kv_head, int page_shift, float scale, int window,
-                            int n_splits) {
+                            int n_splits, int cluster_merge) {
     constexpr int kThreads = kWarps * 32;
     constexpr int LD = HD;                      // a tile's row in shared memory; its 16-byte chunks are XOR-swizzled by the row
     constexpr int CH = HD / 8;                  // 16-byte chunks per row
@@ -90,6 +92,9 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     __shared__ uint64_t bars[kWarps][kStages];
 
     const int split = blockIdx.x, kvh = blockIdx.y, seq = blockIdx.z;
+    // Every block of the cluster has started before one of them writes into another's shared memory: arrive now, wait
+    // just before those writes.
+    if (cluster_merge) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
     const int G = n_head / n_kv_head;           // query heads of this key/value head: the tile's valid rows
     const int page_size = 1 << page_shift;
@@ -298,6 +303,16 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     }
     __syncthreads();
     float* my_partial = partial + (((size_t)seq * n_kv_head + kvh) * n_splits + split) * (size_t)(G * STATE);
+    // With the key ranges of a request and head as the blocks of one cluster, their states meet in the first block's
+    // shared memory (an inbox past the tile buffers, one slot per range) instead of global memory.
+    constexpr size_t kRegion = ((size_t)kWarps * kStages * 2 * kTile * HD * sizeof(__nv_bfloat16) > (size_t)kWarps * 16 * STATE * sizeof(float)
+                                    ? (size_t)kWarps * kStages * 2 * kTile * HD * sizeof(__nv_bfloat16)
+                                    : (size_t)kWarps * 16 * STATE * sizeof(float)) + (TMA ? 1024 : 0);
+    uint32_t first_block = 0;
+    if (cluster_merge) asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    if (cluster_merge && n_splits > 1)
+        asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+                     : "=r"(first_block) : "r"(smem_addr(reinterpret_cast<float*>(smem_raw + kRegion) + (size_t)split * G * STATE)), "r"(0));
     for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
         const int r = idx / HD, d = idx - r * HD;
         float mm = -CUDART_INF_F;
@@ -313,6 +328,13 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
         }
         if (n_splits == 1) {
             out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(a / ll);
+        } else if (cluster_merge) {
+            const uint32_t at = first_block + (uint32_t)(r * STATE) * 4u;
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at + (uint32_t)(2 + d) * 4u), "f"(a) : "memory");
+            if (d == 0) {
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at), "f"(mm) : "memory");
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(at + 4u), "f"(ll) : "memory");
+            }
         } else {
             my_partial[r * STATE + 2 + d] = a;
             if (d == 0) {
@@ -322,6 +344,29 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
         }
     }
     if (n_splits == 1) return;
+    if (cluster_merge) {
+        // The first block of the cluster merges the states, in range order as the other way does.
+        float* inbox = reinterpret_cast<float*>(smem_raw + kRegion);
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (rank != 0) return;
+        for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
+            const int r = idx / HD, d = idx - r * HD;
+            float mm = -CUDART_INF_F;
+            for (int sp = 0; sp < n_splits; ++sp) mm = fmaxf(mm, inbox[(size_t)sp * G * STATE + r * STATE]);
+            float ll = 0.0f, a = 0.0f;
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float* st = inbox + (size_t)sp * G * STATE + r * STATE;
+                const float f = exp2f(st[0] - mm);
+                ll += st[1] * f;
+                a += st[2 + d] * f;
+            }
+            out[(size_t)seq * out_stride + (size_t)(kvh * G + r) * HD + d] = __float2bfloat16_rn(a / ll);
+        }
+        return;
+    }
     __threadfence();
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -348,18 +393,26 @@ decode_attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, int kv_r
     }
 }
 
+// LIYAB_B200_ATTN_CLUSTER=0 in the environment keeps the merge through global memory at every number of ranges
+// (measurements: 8 requests x 12 heads at 650 keys in 3 ranges: 7.3 us that way, 5.8 us inside a cluster).
+bool cluster_merge_enabled() {
+    static const bool on = [] { const char* e = getenv("LIYAB_B200_ATTN_CLUSTER"); return e == nullptr || e[0] != '0'; }();
+    return on;
+}
+
 // Shared memory of one block and how many blocks of an instantiation one SM holds (asked once).
 template <int HD, int kWarps, int kStages, bool TMA>
 struct Variant {
     static constexpr size_t tile_bytes = (size_t)kWarps * kStages * 2 * kTile * HD * sizeof(__nv_bfloat16);
     static constexpr size_t red_bytes = (size_t)kWarps * 16 * (HD + 2) * sizeof(float);
     static constexpr size_t smem = (tile_bytes > red_bytes ? tile_bytes : red_bytes) + (TMA ? 1024 : 0);
+    static constexpr size_t kInboxMax = (size_t)8 * 16 * (HD + 2) * sizeof(float);       // eight ranges of sixteen query heads
 
     static int blocks_per_sm(int* out) {
         static int cached = 0;
         if (cached == 0) {
             LB_CHECK_CUDA(cudaFuncSetAttribute(decode_attention_mma_kernel<HD, kWarps, kStages, TMA>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(smem + kInboxMax)));
             int n = 0;
             LB_CHECK_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_mma_kernel<HD, kWarps, kStages, TMA>,
                                                                         kWarps * 32, smem));
@@ -373,10 +426,18 @@ struct Variant {
                       int table_stride, void* out, int64_t out_stride, float* partial, int* counters, int n_seq, int n_head,
                       int n_kv_head, int page_shift, float scale, int window, int n_splits, cudaStream_t s) {
         dim3 grid(n_splits, n_kv_head, n_seq);
-        LB_CHECK_CUDA(lb_launch_overlapped_kind(3, decode_attention_mma_kernel<HD, kWarps, kStages, TMA>, grid, dim3(kWarps * 32), smem, s, map_kv,
-                                           kv_rows, status, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache, positions,
-                                           block_table, table_stride, (__nv_bfloat16*)out, out_stride, partial, counters, n_head,
-                                           n_kv_head, page_shift, scale, window, n_splits));
+        // Two to eight key ranges: the ranges of a request and head form a cluster and merge in shared memory.
+        const int group = n_head / n_kv_head;
+        const bool cluster = n_splits > 1 && n_splits <= 8 && cluster_merge_enabled();
+        const size_t inbox = cluster ? (size_t)n_splits * group * (HD + 2) * sizeof(float) : 0;
+        int per_sm = 0;
+        const int rc = blocks_per_sm(&per_sm);              // sets the kernel's shared-memory limit
+        if (rc != LB_OK) return rc;
+        LB_CHECK_CUDA(lb_launch_overlapped_cluster(3, cluster ? n_splits : 1, decode_attention_mma_kernel<HD, kWarps, kStages, TMA>, grid,
+                                                   dim3(kWarps * 32), smem + inbox, s, map_kv, kv_rows, status, (const __nv_bfloat16*)q,
+                                                   q_stride, (const __nv_bfloat16*)cache, positions, block_table, table_stride,
+                                                   (__nv_bfloat16*)out, out_stride, partial, counters, n_head, n_kv_head, page_shift,
+                                                   scale, window, n_splits, cluster ? 1 : 0));
         return LB_OK;
     }
 };

@@ -68,20 +68,34 @@ __device__ __forceinline__ void lb_wait_for_predecessor() { asm volatile("gridde
 
 bool lb_launch_overlap_enabled(int kind = 0);
 
+// cluster_x > 1: the grid's blocks form clusters of cluster_x blocks along x (gridDim.x a multiple of it).
 template <typename... Params, typename... Args>
-inline cudaError_t lb_launch_overlapped_kind(int kind, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                        Args... args) {
+inline cudaError_t lb_launch_overlapped_cluster(int kind, int cluster_x, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem,
+                                                cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t config = {};
     config.gridDim = grid;
     config.blockDim = block;
     config.dynamicSmemBytes = smem;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
+    cudaLaunchAttribute attribute[2];
     attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute[0].val.programmaticStreamSerializationAllowed = lb_launch_overlap_enabled(kind) ? 1 : 0;
     config.attrs = attribute;
     config.numAttrs = 1;
+    if (cluster_x > 1) {
+        attribute[1].id = cudaLaunchAttributeClusterDimension;
+        attribute[1].val.clusterDim.x = (unsigned)cluster_x;
+        attribute[1].val.clusterDim.y = 1;
+        attribute[1].val.clusterDim.z = 1;
+        config.numAttrs = 2;
+    }
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
+template <typename... Params, typename... Args>
+inline cudaError_t lb_launch_overlapped_kind(int kind, void (*kernel)(Params...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                        Args... args) {
+    return lb_launch_overlapped_cluster(kind, 1, kernel, grid, block, smem, stream, args...);
 }
 
 __device__ __forceinline__ float lb_to_float(float v) { return v; }

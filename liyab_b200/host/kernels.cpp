@@ -1,5 +1,6 @@
 #include "kernels.h"
 
+#include <cstdlib>
 #include <algorithm>
 
 #include "../csrc/api.h"
@@ -209,12 +210,14 @@ bool prefill_tc_supports(const AttentionShape& a) { return lb_prefill_attention_
 int decode_splits(int n_seq, int n_kv_head, int max_context, bool tensor_cores) {
     // How many ways each request's keys are split.  Scalar kernel: enough blocks for about four full waves of
     // the GPU, but no ranges shorter than 128 keys at the longest context.  Tensor-core kernel: a block gets through
-    // its keys far faster, so fewer and longer ranges (about 450 blocks, 192 keys or more each); from 32 requests of
-    // 12 heads on, none.  A function of the batch's shape only, so a captured step and an eager one split alike.
+    // its keys far faster, so fewer and longer ranges (about 450 blocks, 96 keys or more each; up to eight ranges merge
+    // inside a cluster, which made shorter ranges pay: GPT-2 small, one request, 278 -> 270 us a step); from 32 requests
+    // of 12 heads on, none.  A function of the batch's shape only, so a captured step and an eager one split alike.
     const int work = std::max(1, n_seq * n_kv_head);
     if (tensor_cores) {
-        const int cap = max_context ? std::max(1, max_context / 192) : 32;
-        return std::max(1, std::min({32, cap, 444 / work}));
+        const int cap = max_context ? std::max(1, max_context / 96) : 32;
+        const int n = std::max(1, std::min({32, cap, 444 / work}));
+        return n > 8 && n < 16 ? 8 : n;          // eight ranges that merge inside a cluster beat a few more that cannot
     }
     const int cap = max_context ? std::max(1, max_context / 128) : 32;
     return std::max(1, std::min({32, cap, (2960 + work - 1) / work}));

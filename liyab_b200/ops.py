@@ -368,12 +368,13 @@ def decode_attention_supports(n_head: int, n_kv_head: int, head_dim: int, page_s
 def decode_splits(n_seq: int, n_kv_head: int, max_context: int = 0, tensor_cores: bool = False) -> int:
     """How many ways each request's keys are split.  Scalar kernel: enough blocks for about four full waves of
     the GPU, but no ranges shorter than 128 keys at the longest context.  Tensor-core kernel: a block gets through
-    its keys far faster, so fewer and longer ranges (about 450 blocks, 192 keys or more each); from 32 requests of
-    12 heads on, none.  A function of the batch's shape only, so a captured step and an eager one split alike."""
+    its keys far faster, so fewer and longer ranges (about 450 blocks, 96 keys or more each; up to eight ranges merge
+    inside a cluster); from 32 requests of 12 heads on, none.  A function of the batch's shape only, so a captured step and an eager one split alike."""
     work = max(1, n_seq * n_kv_head)
     if tensor_cores:
-        cap = max(1, max_context // 192) if max_context else 32
-        return max(1, min(32, cap, 444 // work))
+        cap = max(1, max_context // 96) if max_context else 32
+        n = max(1, min(32, cap, 444 // work))
+        return 8 if 8 < n < 16 else n          # eight ranges that merge inside a cluster beat a few more that cannot
     cap = max(1, max_context // 128) if max_context else 32
     return max(1, min(32, cap, -(-2960 // work)))
 

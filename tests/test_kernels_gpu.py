@@ -524,10 +524,11 @@ def test_gemm_tcgen05_refuses_what_tma_cannot_fetch(dev):
 @pytest.mark.parametrize("n_head,n_kv_head,head_dim,page_size,window,splits", [
     (12, 12, 64, 16, 0, 1), (12, 12, 64, 16, 0, 5), (4, 4, 16, 16, 0, 3), (3, 3, 32, 32, 0, 32), (8, 2, 128, 16, 0, 4),
     (16, 2, 64, 64, 0, 7), (2, 1, 256, 16, 0, 2), (6, 3, 64, 16, 33, 4), (4, 4, 32, 16, 5, 16), (32, 2, 64, 16, 0, 3),
-    (5, 5, 128, 32, 70, 2), (16, 1, 128, 16, 0, 1)])
+    (5, 5, 128, 32, 70, 2), (16, 1, 128, 16, 0, 1), (12, 12, 64, 16, 0, 12), (16, 1, 128, 16, 0, 8), (12, 12, 64, 16, 0, 8)])
 def test_decode_attention(dev, n_head, n_kv_head, head_dim, page_size, window, splits):
-    """One new token per request over its pages, keys split several ways, against float64; the same
-    scratch is used by two launches in a row (the kernel must leave its counters at zero)."""
+    """One new token per request over its pages, keys split several ways (two to eight ranges merge inside a
+    cluster, more through global memory), against float64; the same scratch is used by two launches in a row (the
+    kernel must leave its counters at zero)."""
     from liyab_b200 import ops
     scalar, tensor = ops.decode_attention_kernels(n_head, n_kv_head, head_dim, page_size)
     assert scalar or tensor
