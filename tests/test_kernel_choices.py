@@ -36,7 +36,7 @@ def test_decode_splits_depend_on_the_shape_only(n_seq, n_kv, ctx, tensor):
     s = ops.decode_splits(n_seq, n_kv, ctx, tensor_cores=tensor)
     assert 1 <= s <= 32 and s == ops.decode_splits(n_seq, n_kv, ctx, tensor_cores=tensor)
     if ctx:
-        assert s <= max(1, ctx // (192 if tensor else 128))               # no key range shorter than that
+        assert s <= max(1, ctx // (96 if tensor else 128))                # no key range shorter than that
     if n_seq * n_kv >= 444:
         assert ops.decode_splits(n_seq, n_kv, ctx, tensor_cores=True) == 1
 
