@@ -13,12 +13,12 @@
 // logits' bit patterns (four passes of eight bits), by count for top-k and by
 // probability mass for top-p.  A top-k of up to 256 (the usual case: 40) takes a
 // short way instead: a threshold that at least k logits reach comes from the
-// block's 1,024 per-thread maxima, the few logits that reach it are listed in
-// shared memory and the rest happens among them (27 us instead of 200 us per step
-// at a vocabulary of 50,257; one block per row walks the row three times).  Top-p
-// without top-k takes the same way with the 256 largest logits as candidates
-// whenever they hold the asked share of the whole row's mass (72 us instead of
-// 750 us), and the general path otherwise.
+// block's 1,024 per-thread maxima (radix selection among them), the few logits
+// that reach it are listed in shared memory and the rest happens among them
+// (21 us instead of 200 us per step at a vocabulary of 50,257; one block per row
+// walks the row twice).  Top-p without top-k takes the same way with the 256
+// largest logits as candidates whenever they hold the asked share of the whole
+// row's mass (67 us instead of 750 us), and the general path otherwise.
 #include "api.h"
 #include "common.cuh"
 
@@ -99,6 +99,80 @@ __device__ T block_exclusive_scan(T v, T* scratch /* 33 */, T* total) {
     return scratch[warp] + inc - v;
 }
 
+// Sums over a short array in shared memory by one warp: every lane adds its run of consecutive elements in order, the
+// lanes' sums are scanned in lane order.  Returns the lane's offset (the sum of everything before its run) and the
+// total through *total; `value(i)` gives element i as a double.  The order of the additions is fixed.
+template <typename F>
+__device__ __forceinline__ double warp_ordered_offsets(int n, F value, double* mine, double* total, int* first, int* last) {
+    const int lane = threadIdx.x & 31, per = (n + 31) / 32;
+    const int a = min(n, lane * per), b = min(n, a + per);
+    double s = 0.0;
+    for (int i = a; i < b; ++i) s += value(i);
+    double inc = s;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const double up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+    }
+    *mine = s;
+    *total = __shfl_sync(0xffffffffu, inc, 31);
+    *first = a;
+    *last = b;
+    return inc - s;
+}
+
+// The n-th largest of the block's keys (one per thread, n >= 1 and at most the block's size), to its upper 24 bits:
+// a value that at least n of the keys reach.  Radix selection, eight bits a pass; a pass is a histogram in shared
+// memory (lanes with the same bucket add once, together) and one warp that finds the bucket of the n-th largest.
+__device__ uint32_t nth_largest_floor(uint32_t key, int n, int* hist /* 256 */, uint32_t* sh_prefix, int* sh_remaining) {
+    const int tid = threadIdx.x, lane = tid & 31;
+    uint32_t prefix = 0;
+    int remaining = n;
+    for (int shift = 24; shift >= 8; shift -= 8) {
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
+        const int bucket = (key & mask) == prefix ? (int)((key >> shift) & 255u) : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, bucket);
+        if (bucket >= 0 && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], __popc(peers));
+        __syncthreads();
+        if (tid < 32) {
+            // Lane l holds buckets 255 - 8 l down to 248 - 8 l; the lanes' sums are scanned from the top bucket down.
+            int c[8], sum = 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c[j] = hist[255 - 8 * lane - j];
+                sum += c[j];
+            }
+            int inc = sum;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, inc, o);
+                if (lane >= o) inc += up;
+            }
+            const unsigned reached = __ballot_sync(0xffffffffu, inc >= remaining);        // never empty: the keys that match number at least `remaining`
+            if (lane == __ffs(reached) - 1) {
+                int rem = remaining - (inc - sum), digit = 255 - 8 * lane;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (rem > c[j] && j < 7) {
+                        rem -= c[j];
+                        --digit;
+                    } else {
+                        break;
+                    }
+                }
+                *sh_prefix = prefix | ((uint32_t)digit << shift);
+                *sh_remaining = rem;
+            }
+        }
+        __syncthreads();
+        prefix = *sh_prefix;
+        remaining = *sh_remaining;
+    }
+    return prefix;
+}
+
 __global__ void __launch_bounds__(kThreads)
 sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, const float* __restrict__ temperature,
               const int32_t* __restrict__ top_k, const float* __restrict__ top_p, const double* __restrict__ uniform,
@@ -160,7 +234,6 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
             for (int i = tid; i < vocab; i += kThreads) mine += (double)expf((x[i] - max_logit) * inv_t);
             block_exclusive_scan<double>(mine, d_scratch, &vocab_mass);
         }
-        __shared__ uint32_t max_keys[kThreads];
         __shared__ int list_idx[kMaxList];
         __shared__ uint32_t list_key[kMaxList];
         __shared__ int list_rank[kMaxList];
@@ -168,63 +241,58 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
         __shared__ float cand_e[kSmallK];          // exp((logit - max) / T), in index order
         __shared__ int cand_rank[kSmallK];         // place by (logit descending, index ascending)
         __shared__ float sorted_e[kSmallK];        // cand_e in that order
-        __shared__ int sh_count, sh_list_n, sh_cut;
+        __shared__ int sh_list_n, sh_cut;
         // The k-th largest of the 1,024 threads' own maxima is a lower bound of the k-th largest logit (k logits
-        // are at least that large), and few other logits are: it is the threshold of the list.  Found by sorting
-        // the maxima (bitonic, descending, in shared memory: no atomics).
-        max_keys[tid] = my_max_key;
+        // are at least that large), and few other logits are: it is the threshold of the list (taken to its upper
+        // 24 bits, which lets a few more in).  The logits that reach it are listed in one walk; a list that would
+        // not fit is counted to its end and left to the general path.
         if (tid == 0) sh_list_n = 0;
-        __syncthreads();
-        for (int size = 2; size <= kThreads; size <<= 1) {
-            for (int stride = size >> 1; stride > 0; stride >>= 1) {
-                const int partner = tid ^ stride;
-                if (partner > tid) {
-                    const uint32_t a = max_keys[tid], b2 = max_keys[partner];
-                    const bool descending = (tid & size) == 0;
-                    if (descending ? a < b2 : a > b2) {
-                        max_keys[tid] = b2;
-                        max_keys[partner] = a;
-                    }
-                }
-                __syncthreads();
-            }
-        }
-        const uint32_t threshold = max_keys[ke - 1];
-        // How many logits reach the threshold.
-        {
-            int mine = 0;
-            for (int i = tid; i < vocab; i += kThreads) mine += order_key(x[i]) >= threshold ? 1 : 0;
-            int total;
-            block_exclusive_scan<int>(mine, i_scratch, &total);
-            if (tid == 0) sh_count = total;
-        }
-        __syncthreads();
-        const int n_list = sh_count;
-        if (n_list <= kMaxList) {
-            for (int i = tid; i < vocab; i += kThreads) {
-                const uint32_t key = order_key(x[i]);
-                if (key >= threshold) {
-                    const int at = atomicAdd(&sh_list_n, 1);
+        const uint32_t threshold = nth_largest_floor(my_max_key, ke, hist_count, &sh_prefix, &sh_int);
+        for (int i = tid; i < vocab; i += kThreads) {
+            const uint32_t key = order_key(x[i]);
+            if (key >= threshold) {
+                const int at = atomicAdd(&sh_list_n, 1);
+                if (at < kMaxList) {
                     list_idx[at] = i;
                     list_key[at] = key;
                 }
             }
-            __syncthreads();
-            // Place of every listed logit by (key descending, index ascending): the first k are the members.
+        }
+        __syncthreads();
+        const int n_list = sh_list_n;
+        if (n_list <= kMaxList) {
+            // Place of every listed logit by (key descending, index ascending): the first k are the members; then the
+            // members' places in index order.  Both are counts over the list; the block's threads share an entry's
+            // count (threads / entries of them per entry, each over a part of the list, added up in shared memory).
+            __shared__ int list_pos[kMaxList];
             for (int c = tid; c < n_list; c += kThreads) {
+                list_rank[c] = 0;
+                list_pos[c] = 0;
+            }
+            __syncthreads();
+            const int sharers = max(1, kThreads / max(1, n_list)), part_len = (n_list + sharers - 1) / sharers;
+            for (int w = tid; w < n_list * sharers; w += kThreads) {
+                const int c = w % n_list, j0 = (w / n_list) * part_len, j1 = min(n_list, j0 + part_len);
                 const uint32_t key = list_key[c];
                 const int idx = list_idx[c];
                 int before = 0;
-                for (int j = 0; j < n_list; ++j) before += (list_key[j] > key || (list_key[j] == key && list_idx[j] < idx)) ? 1 : 0;
-                list_rank[c] = before;
+                for (int j = j0; j < j1; ++j) before += (list_key[j] > key || (list_key[j] == key && list_idx[j] < idx)) ? 1 : 0;
+                if (before != 0) atomicAdd(&list_rank[c], before);
+            }
+            __syncthreads();
+            for (int w = tid; w < n_list * sharers; w += kThreads) {
+                const int c = w % n_list, j0 = (w / n_list) * part_len, j1 = min(n_list, j0 + part_len);
+                if (list_rank[c] >= ke) continue;
+                const int idx = list_idx[c];
+                int at = 0;
+                for (int j = j0; j < j1; ++j) at += (list_rank[j] < ke && list_idx[j] < idx) ? 1 : 0;
+                if (at != 0) atomicAdd(&list_pos[c], at);
             }
             __syncthreads();
             // Members in index order.
             for (int c = tid; c < n_list; c += kThreads) {
                 if (list_rank[c] >= ke) continue;
-                const int idx = list_idx[c];
-                int at = 0;
-                for (int j = 0; j < n_list; ++j) at += (list_rank[j] < ke && list_idx[j] < idx) ? 1 : 0;
+                const int idx = list_idx[c], at = list_pos[c];
                 const float e = expf((x[idx] - max_logit) * inv_t);
                 cand_idx[at] = idx;
                 cand_e[at] = e;
@@ -239,17 +307,20 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
             __shared__ float cand_p[kSmallK];
             __shared__ double sh_total_mass;
             const float p_cut = top_p[row];
-            if (tid == 0) {
-                double total_mass = 0.0;
-                for (int c = 0; c < n; ++c) total_mass += (double)cand_e[c];
+            if (tid < 32) {
+                double mine, total_mass, run;
+                int a, b;
+                warp_ordered_offsets(n, [&](int c) { return (double)cand_e[c]; }, &mine, &total_mass, &a, &b);
                 if (nucleus_only) total_mass = vocab_mass;          // the share is of the whole vocabulary's mass
-                double acc = 0.0;
-                for (int r = 0; r < n; ++r) {
-                    acc += (double)sorted_e[r];
-                    acc_s[r] = acc;
+                double before_me = warp_ordered_offsets(n, [&](int r) { return (double)sorted_e[r]; }, &mine, &run, &a, &b);
+                for (int r = a; r < b; ++r) {
+                    before_me += (double)sorted_e[r];
+                    acc_s[r] = before_me;
                 }
-                sh_total_mass = total_mass;
-                sh_cut = n;
+                if (tid == 0) {
+                    sh_total_mass = total_mass;
+                    sh_cut = n;
+                }
             }
             __syncthreads();
             if (tid < n && p_cut < 1.0f && acc_s[tid] / sh_total_mass >= (double)p_cut) atomicMin(&sh_cut, tid + 1);
@@ -258,33 +329,43 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
             // Top-p alone, and the candidates do not hold the asked share: the general path takes the row.
             const bool inside = !nucleus_only || n == vocab || acc_s[n - 1] / sh_total_mass >= (double)top_p[row];
             if (inside) {
-            if (tid == 0) {
-                double kept_mass = 0.0;
-                for (int c = 0; c < n; ++c)
-                    if (cand_rank[c] < cut) kept_mass += (double)cand_e[c];
-                sh_double = kept_mass;
+            if (tid < 32) {
+                double mine, kept;
+                int a, b;
+                warp_ordered_offsets(n, [&](int c) { return cand_rank[c] < cut ? (double)cand_e[c] : 0.0; }, &mine, &kept, &a, &b);
+                if (tid == 0) sh_double = kept;
             }
             __syncthreads();
             const double kept_mass = sh_double;
             if (tid < n) cand_p[tid] = cand_rank[tid] < cut ? (float)((double)cand_e[tid] / kept_mass) : 0.0f;
             __syncthreads();
-            if (tid == 0) {
-                double total = 0.0;
-                for (int c = 0; c < n; ++c)
-                    if (cand_rank[c] < cut) total += (double)cand_p[c];
-                double left = uniform[row] * total;
-                int choice = -1, last = -1;
-                for (int c = 0; c < n && choice < 0; ++c) {
-                    if (cand_rank[c] >= cut) continue;
-                    left -= (double)cand_p[c];
-                    if (left < 0.0) choice = cand_idx[c];
+            if (tid < 32) {
+                // The walk in index order: the lane whose run of candidates holds the draw walks it.
+                double mine, total;
+                int a, b;
+                const double before_me = warp_ordered_offsets(n, [&](int c) { return cand_rank[c] < cut ? (double)cand_p[c] : 0.0; },
+                                                              &mine, &total, &a, &b);
+                const double r = uniform[row] * total;
+                int choice = 0x7fffffff;
+                if (before_me <= r && r < before_me + mine) {
+                    double left = r - before_me;
+                    for (int c = a; c < b && choice == 0x7fffffff; ++c) {
+                        if (cand_rank[c] >= cut) continue;
+                        left -= (double)cand_p[c];
+                        if (left < 0.0) choice = cand_idx[c];
+                    }
                 }
-                if (choice < 0) {           // rounding left the draw at or past the last kept id: the last id with mass
-                    for (int c = 0; c < n; ++c)
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) choice = min(choice, __shfl_xor_sync(0xffffffffu, choice, o));
+                if (choice == 0x7fffffff) {           // rounding left the draw at or past the last kept id: the last id with mass
+                    int last = -1;
+                    for (int c = a; c < b; ++c)
                         if (cand_rank[c] < cut && cand_e[c] > 0.0f) last = cand_idx[c];
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1) last = max(last, __shfl_xor_sync(0xffffffffu, last, o));
                     choice = last >= 0 ? last : best.i;
                 }
-                out_ids[row] = choice;
+                if (tid == 0) out_ids[row] = choice;
             }
             if (probs != nullptr) {
                 for (int i = tid; i < vocab; i += kThreads) probs[i] = 0.0f;
