@@ -15,10 +15,12 @@
 // short way instead: a threshold that at least k logits reach comes from the
 // block's 1,024 per-thread maxima (radix selection among them), the few logits
 // that reach it are listed in shared memory and the rest happens among them
-// (21 us instead of 200 us per step at a vocabulary of 50,257; one block per row
+// (16 us instead of 94 us per step at a vocabulary of 50,257; one block per row
 // walks the row twice).  Top-p without top-k takes the same way with the 256
 // largest logits as candidates whenever they hold the asked share of the whole
-// row's mass (67 us instead of 750 us), and the general path otherwise.
+// row's mass (34 us instead of 320 us), and the general path otherwise (whose
+// histograms are built by warps that add their lanes' terms first, in fixed point,
+// and read by one warp in parallel).
 #include "api.h"
 #include "common.cuh"
 
@@ -29,6 +31,11 @@ namespace {
 constexpr int kThreads = 1024;
 constexpr int kSmallK = 256;       // a top-k up to this takes the short way: a threshold, then a list of candidates
 constexpr int kMaxList = 1024;     // candidates (logits that reach the threshold) the short way takes
+// The general path's histograms of probability mass are sums of exp((l - max) / T) <= 1 in fixed point (the unit is
+// 2^-(62 - floor(log2 vocab)), at most 2^-47: a row of ones still fits 64 bits, and what a term loses is far below the
+// float probabilities' own rounding).  Thousands of logits share a few buckets (sign and exponent), so the lanes of a
+// warp that meet in a bucket add their terms first (three 16-bit limbs through the warp's integer reduction) and one
+// of them adds the sum to shared memory; integer sums do not depend on the order of the additions.
 
 // Monotone map from float to uint32: a larger float gives a larger key.
 __device__ __forceinline__ uint32_t order_key(float v) {
@@ -121,6 +128,80 @@ __device__ __forceinline__ double warp_ordered_offsets(int n, F value, double* m
     return inc - s;
 }
 
+// One warp finds, from the top bucket down, the bucket that holds the `remaining`-th largest key of a 256-bucket
+// histogram of counts, and the rank that is left inside it (lane l holds buckets 255 - 8 l down to 248 - 8 l; the
+// lanes' sums are scanned).  The histogram holds at least `remaining` keys.  The answer is the same on every lane.
+__device__ __forceinline__ void warp_bucket_by_count(const int* hist, int remaining, int* digit_out, int* rem_out) {
+    const int lane = threadIdx.x & 31;
+    int c[8], sum = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        c[j] = hist[255 - 8 * lane - j];
+        sum += c[j];
+    }
+    int inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+    }
+    const unsigned reached = __ballot_sync(0xffffffffu, inc >= remaining);
+    const int owner = reached != 0u ? __ffs(reached) - 1 : 31;
+    int rem = remaining - (inc - sum), digit = 255 - 8 * lane;
+#pragma unroll
+    for (int j = 0; j < 7; ++j) {
+        if (rem > c[j] && digit == 255 - 8 * lane - j) {
+            rem -= c[j];
+            --digit;
+        }
+    }
+    *digit_out = __shfl_sync(0xffffffffu, digit, owner);
+    *rem_out = __shfl_sync(0xffffffffu, rem, owner);
+}
+
+// The same by probability mass (fixed point, `unit` per 1.0): the highest bucket at which the mass from the top,
+// `above` included, reaches the share p_cut of total_mass; bucket 0 if none does.  *above_out: the mass above it.
+__device__ __forceinline__ void warp_bucket_by_mass(const unsigned long long* hist, unsigned long long above, double unit,
+                                                    double total_mass, double p_cut, int* digit_out, unsigned long long* above_out) {
+    const int lane = threadIdx.x & 31;
+    unsigned long long c[8], sum = 0ull;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        c[j] = hist[255 - 8 * lane - j];
+        sum += c[j];
+    }
+    unsigned long long inc = sum;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, inc, o);
+        if (lane >= o) inc += up;
+    }
+    unsigned long long before = above + (inc - sum);          // mass above this lane's first bucket
+    int digit = -1;
+    unsigned long long before_hit = 0ull;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int d = 255 - 8 * lane - j;
+        if (digit < 0 && d > 0 && ((double)(before + c[j]) / unit) / total_mass >= p_cut) {
+            digit = d;
+            before_hit = before;
+        }
+        before += c[j];
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, digit >= 0);
+    if (hit != 0u) {
+        const int owner = __ffs(hit) - 1;
+        *digit_out = __shfl_sync(0xffffffffu, digit, owner);
+        *above_out = __shfl_sync(0xffffffffu, before_hit, owner);
+    } else {
+        // No bucket reaches the share: the lowest takes what is left (the last lane's `before` stops short of bucket 0).
+        const unsigned long long all = __shfl_sync(0xffffffffu, inc, 31);
+        const unsigned long long lowest = __shfl_sync(0xffffffffu, c[7], 31);
+        *digit_out = 0;
+        *above_out = above + all - lowest;
+    }
+}
+
 // The n-th largest of the block's keys (one per thread, n >= 1 and at most the block's size), to its upper 24 bits:
 // a value that at least n of the keys reach.  Radix selection, eight bits a pass; a pass is a histogram in shared
 // memory (lanes with the same bucket add once, together) and one warp that finds the bucket of the n-th largest.
@@ -137,31 +218,9 @@ __device__ uint32_t nth_largest_floor(uint32_t key, int n, int* hist /* 256 */, 
         if (bucket >= 0 && lane == __ffs(peers) - 1) atomicAdd(&hist[bucket], __popc(peers));
         __syncthreads();
         if (tid < 32) {
-            // Lane l holds buckets 255 - 8 l down to 248 - 8 l; the lanes' sums are scanned from the top bucket down.
-            int c[8], sum = 0;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                c[j] = hist[255 - 8 * lane - j];
-                sum += c[j];
-            }
-            int inc = sum;
-#pragma unroll
-            for (int o = 1; o < 32; o <<= 1) {
-                const int up = __shfl_up_sync(0xffffffffu, inc, o);
-                if (lane >= o) inc += up;
-            }
-            const unsigned reached = __ballot_sync(0xffffffffu, inc >= remaining);        // never empty: the keys that match number at least `remaining`
-            if (lane == __ffs(reached) - 1) {
-                int rem = remaining - (inc - sum), digit = 255 - 8 * lane;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (rem > c[j] && j < 7) {
-                        rem -= c[j];
-                        --digit;
-                    } else {
-                        break;
-                    }
-                }
+            int digit, rem;
+            warp_bucket_by_count(hist, remaining, &digit, &rem);
+            if (tid == 0) {
                 *sh_prefix = prefix | ((uint32_t)digit << shift);
                 *sh_remaining = rem;
             }
@@ -181,7 +240,7 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     __shared__ int i_scratch[33];
     __shared__ double d_scratch[33];
     __shared__ int hist_count[256];
-    __shared__ double hist_mass[256];
+    __shared__ unsigned long long hist_mass[256];      // masses in fixed point (kMassUnit), so that their sums do not depend on the order
     __shared__ uint32_t sh_prefix;
     __shared__ int sh_int;
     __shared__ double sh_double;
@@ -194,9 +253,27 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     float* probs = out_probs != nullptr ? out_probs + (size_t)row * vocab : nullptr;
     const float temp = temperature[row];
 
-    // Contiguous range of this thread: sums and ranks in index order need one scan.
-    const int per = (vocab + kThreads - 1) / kThreads;
-    const int lo = min(vocab, tid * per), hi = min(vocab, lo + per);
+    // Contiguous range of this thread: sums and ranks in index order need one scan.  The first thread takes the
+    // (up to three) logits before the row's first 16-byte boundary, the others a multiple of four from there on, so
+    // that they read with 16-byte loads (the lanes of a warp read 32 different lines whatever the width of a load:
+    // four times fewer loads, four times fewer trips through the first-level cache).
+    const int peel = (int)((4 - ((reinterpret_cast<uintptr_t>(x) >> 2) & 3)) & 3);
+    const int per = ((vocab + kThreads - 2) / (kThreads - 1) + 3) & ~3;
+    const int lo = min(vocab, max(0, (tid - 1) * per + peel)), hi = min(vocab, max(0, tid * per + peel));
+    const bool vec_ok = (reinterpret_cast<uintptr_t>(x + lo) & 15) == 0;
+    auto for_range = [&](auto&& body) {          // body(i, x[i]) for this thread's i, in order
+        int i = lo;
+        if (vec_ok) {
+            for (; i + 4 <= hi; i += 4) {
+                const float4 q = *reinterpret_cast<const float4*>(x + i);
+                body(i, q.x);
+                body(i + 1, q.y);
+                body(i + 2, q.z);
+                body(i + 3, q.w);
+            }
+        }
+        for (; i < hi; ++i) body(i, x[i]);
+    };
 
     // A logit that is no number counts as the lowest: every row, even one of nothing else, gets an id inside the
     // vocabulary (the next step reads the embedding table with it).
@@ -215,6 +292,8 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     }
     const float max_logit = best.v;
     const float inv_t = 1.0f / temp;
+    const int mass_bits = min(47, 62 - (31 - __clz(vocab)));
+    const double kMassUnit = (double)(1ull << mass_bits);
 
     int k = top_k[row];
     // ---- the short way for the usual top-k of some dozens: two more walks over the vocabulary instead of a dozen.
@@ -402,14 +481,13 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
                 if (bucket >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicAdd(&hist_count[bucket], __popc(peers));
             }
             __syncthreads();
-            if (tid == 0) {
-                int rem = remaining, digit = 255;
-                for (; digit > 0; --digit) {
-                    if (hist_count[digit] >= rem) break;
-                    rem -= hist_count[digit];
+            if (tid < 32) {
+                int digit, rem;
+                warp_bucket_by_count(hist_count, remaining, &digit, &rem);
+                if (tid == 0) {
+                    sh_int = rem;
+                    sh_prefix = prefix | ((uint32_t)digit << shift);
                 }
-                sh_int = rem;
-                sh_prefix = prefix | ((uint32_t)digit << shift);
             }
             __syncthreads();
             remaining = sh_int;
@@ -424,7 +502,7 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     int tie_rank_base = 0;
     {
         int mine = 0;
-        for (int i = lo; i < hi; ++i) mine += order_key(x[i]) == kth_key ? 1 : 0;
+        for_range([&](int, float xi) { mine += order_key(xi) == kth_key ? 1 : 0; });
         int total;
         tie_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
     }
@@ -435,12 +513,12 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     {
         double mine = 0.0;
         int rank = tie_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int, float xi) {
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
-            if (member) mine += (double)expf((x[i] - max_logit) * inv_t);
-        }
+            if (member) mine += (double)expf((xi - max_logit) * inv_t);
+        });
         block_exclusive_scan<double>(mine, d_scratch, &total_mass);
     }
 
@@ -451,36 +529,63 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     double kept_mass = total_mass;
     if (p_cut < 1.0f) {
         uint32_t prefix = 0;
-        double above = 0.0;        // mass of members with a key above the current bucket
+        unsigned long long above_fixed = 0ull;        // mass of members with a key above the current bucket, in fixed point
+        __shared__ unsigned long long sh_above;
         for (int shift = 24; shift >= 0; shift -= 8) {
-            for (int b = tid; b < 256; b += kThreads) hist_mass[b] = 0.0;
+            for (int b = tid; b < 256; b += kThreads) hist_mass[b] = 0ull;
             __syncthreads();
             const uint32_t mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
             int rank = tie_rank_base;
-            for (int i = lo; i < hi; ++i) {
-                const uint32_t key = order_key(x[i]);
-                bool member = key > kth_key;
-                if (key == kth_key) member = rank++ < kth_need;
-                if (member && (key & mask) == prefix)
-                    atomicAdd(&hist_mass[(key >> shift) & 255u], (double)expf((x[i] - max_logit) * inv_t));
-            }
-            __syncthreads();
-            if (tid == 0) {
-                double acc = above;
-                int digit = 255;
-                for (; digit > 0; --digit) {
-                    if ((acc + hist_mass[digit]) / total_mass >= (double)p_cut) break;
-                    acc += hist_mass[digit];
+            float four[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+            for (int it = 0; it < per; ++it) {                  // the same number of trips for every lane
+                const int i = lo + it;
+                if ((it & 3) == 0) {
+                    if (vec_ok && i + 4 <= hi) {
+                        const float4 q = *reinterpret_cast<const float4*>(x + i);
+                        four[0] = q.x; four[1] = q.y; four[2] = q.z; four[3] = q.w;
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) four[e] = i + e < hi ? x[i + e] : 0.0f;
+                    }
                 }
-                sh_double = acc;
-                sh_prefix = prefix | ((uint32_t)digit << shift);
+                int bucket = -1;
+                unsigned long long term = 0ull;
+                if (i < hi) {
+                    const float xi = four[it & 3];
+                    const uint32_t key = order_key(xi);
+                    bool member = key > kth_key;
+                    if (key == kth_key) member = rank++ < kth_need;
+                    if (member && (key & mask) == prefix) {
+                        bucket = (int)((key >> shift) & 255u);
+                        term = (unsigned long long)((double)expf((xi - max_logit) * inv_t) * kMassUnit);      // < 2^48
+                    }
+                }
+                if (!__any_sync(0xffffffffu, bucket >= 0)) continue;          // no lane of the warp has a term (the later passes, mostly)
+                const unsigned peers = __match_any_sync(0xffffffffu, bucket);
+                const unsigned s0 = __reduce_add_sync(peers, (unsigned)(term & 0xffffu));
+                const unsigned s1 = __reduce_add_sync(peers, (unsigned)((term >> 16) & 0xffffu));
+                const unsigned s2 = __reduce_add_sync(peers, (unsigned)(term >> 32));
+                if (bucket >= 0 && (int)(threadIdx.x & 31) == __ffs(peers) - 1)
+                    atomicAdd(&hist_mass[bucket], (unsigned long long)s0 + ((unsigned long long)s1 << 16) + ((unsigned long long)s2 << 32));
             }
             __syncthreads();
-            above = sh_double;
+            if (tid < 32) {
+                int digit;
+                unsigned long long above_digit;
+                warp_bucket_by_mass(hist_mass, above_fixed, kMassUnit, total_mass, (double)p_cut, &digit, &above_digit);
+                if (tid == 0) {
+                    sh_above = above_digit;
+                    sh_prefix = prefix | ((uint32_t)digit << shift);
+                }
+            }
+            __syncthreads();
+            above_fixed = sh_above;
             prefix = sh_prefix;
             __syncthreads();
         }
         cut_key = prefix;
+        const double above = (double)above_fixed / kMassUnit;
         // Members at cut_key all have the same p; keep as many (in index order) as the prefix needs.
         if (tid == 0) {
             const uint32_t b = (cut_key & 0x80000000u) ? (cut_key & 0x7fffffffu) : ~cut_key;
@@ -504,42 +609,42 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
     int cut_rank_base = 0;
     {
         int mine = 0, rank = tie_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int, float xi) {
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
             mine += (member && key == cut_key) ? 1 : 0;
-        }
+        });
         int total;
         cut_rank_base = block_exclusive_scan<int>(mine, i_scratch, &total);
     }
     {
         double mine = 0.0;
         int rank = tie_rank_base, crank = cut_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int, float xi) {
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
             bool kept = member && key > cut_key;
             if (member && key == cut_key) kept = crank++ < cut_need;
-            if (kept) mine += (double)expf((x[i] - max_logit) * inv_t);
-        }
+            if (kept) mine += (double)expf((xi - max_logit) * inv_t);
+        });
         block_exclusive_scan<double>(mine, d_scratch, &kept_mass);
     }
     // Normalised float probabilities, their double sum in index order, and the walk.
     double my_sum = 0.0;
     {
         int rank = tie_rank_base, crank = cut_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int i, float xi) {
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
             bool kept = member && key > cut_key;
             if (member && key == cut_key) kept = crank++ < cut_need;
-            const float p = kept ? (float)((double)expf((x[i] - max_logit) * inv_t) / kept_mass) : 0.0f;
+            const float p = kept ? (float)((double)expf((xi - max_logit) * inv_t) / kept_mass) : 0.0f;
             if (probs != nullptr) probs[i] = p;
             my_sum += (double)p;
-        }
+        });
     }
     double total;
     const double before = block_exclusive_scan<double>(my_sum, d_scratch, &total);
@@ -550,30 +655,31 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
         // The draw falls inside this thread's range: walk it as the reference walks the whole vocabulary.
         double left = r - before;
         int rank = tie_rank_base, crank = cut_rank_base, choice = -1;
-        for (int i = lo; i < hi && choice < 0; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int i, float xi) {
+            if (choice >= 0) return;
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
             bool kept = member && key > cut_key;
             if (member && key == cut_key) kept = crank++ < cut_need;
-            if (!kept) continue;
-            left -= (double)(float)((double)expf((x[i] - max_logit) * inv_t) / kept_mass);
+            if (!kept) return;
+            left -= (double)(float)((double)expf((xi - max_logit) * inv_t) / kept_mass);
             if (left < 0.0) choice = i;
-        }
+        });
         if (choice >= 0) atomicMin(&sh_choice, choice);
     }
     __syncthreads();
     if (sh_choice == 0x7fffffff) {
         // Rounding left r at or past the last kept id: take the last id with mass.
         int last = -1, rank = tie_rank_base, crank = cut_rank_base;
-        for (int i = lo; i < hi; ++i) {
-            const uint32_t key = order_key(x[i]);
+        for_range([&](int i, float xi) {
+            const uint32_t key = order_key(xi);
             bool member = key > kth_key;
             if (key == kth_key) member = rank++ < kth_need;
             bool kept = member && key > cut_key;
             if (member && key == cut_key) kept = crank++ < cut_need;
-            if (kept && expf((x[i] - max_logit) * inv_t) > 0.0f) last = i;
-        }
+            if (kept && expf((xi - max_logit) * inv_t) > 0.0f) last = i;
+        });
         __shared__ int sh_last;
         if (tid == 0) sh_last = -1;
         __syncthreads();
