@@ -1,6 +1,7 @@
 // out[M, N] = epilogue(A[M, K] . W[N, K]^T) for 1 to 64 tokens (bfloat16
 // operands): the products of a decode step, too small to fill a tcgen05 tile row,
-// whose reduction is short enough (the host takes it for K up to 1024).
+// whose reduction is short enough (the host takes it for K up to 1024, and for up
+// to 16 tokens up to 4096 where one pass covers a block's features).
 //
 // At these sizes a product reads a few MB of weights and does next to no
 // arithmetic; what it costs is latency.  The tcgen05 kernel needs K split over
@@ -13,7 +14,11 @@
 // its weights of the pass (up to four groups of eight features) at the start with
 // 16-byte loads that go straight into mma.sync m16n8k16 fragments (tokens are the
 // rows: one to four tiles of 16), and the eight warps' partial tiles are summed in
-// warp order through shared memory.
+// warp order through shared memory.  For up to 16 tokens all columns of the
+// activations are staged at once (or made in the kernel by a LayerNorm of the
+// float32 rows), and a thread asks for the bias and residual of the elements it
+// will finish before its products.  The launch may overlap the kernel before:
+// weights are asked for before the wait for it, activations after.
 // Every weight byte is read once; a row's result does not depend on the other
 // rows.  Accumulators, bias, activation and residual sum are 32-bit, in the
 // reference's order (src/core/transformer.cpp:111-118, 4903-4912, 5526-5532).
