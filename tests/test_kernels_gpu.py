@@ -223,7 +223,8 @@ def test_sampling_matches_plain(dev, vocab):
     from liyab_b200 import ops
     rng = np.random.default_rng(vocab)
     cases = [(0.0, 0, 1.0), (0.8, 40, 0.95), (0.8, 0, 1.0), (1.3, 5, 1.0), (0.7, 0, 0.5), (1.0, 1000000, 0.9),
-             (0.5, 3, 0.2), (2.0, 17, 0.999), (1.0, 1024, 0.97), (0.9, 1025, 0.9), (1.1, 300, 1.0)]
+             (0.5, 3, 0.2), (2.0, 17, 0.999), (1.0, 1024, 0.97), (0.9, 1025, 0.9), (1.1, 300, 1.0), (0.9, 256, 0.9),
+             (0.9, 257, 1.0), (1.0, 255, 0.5), (0.6, 1, 1.0), (1.0, 2, 0.99)]
     R = len(cases)
     logits = rng.standard_normal((R, vocab)).astype(np.float32) * 2.0
     logits[1, 7] = logits[1].max() + 0.5
