@@ -53,6 +53,8 @@ struct Control {
     uint64_t acc_empty[2];
     uint64_t res_full;
     uint64_t staging_free;
+    uint64_t peer_sent;         // (pairs) the other block's half of this block's strips lies in the staging buffer
+    uint64_t may_send;          // (pairs) the other block has read what this block sent for the tile before
     uint32_t tmem_base;
     int abort_flag;
 };
@@ -100,6 +102,44 @@ __device__ __forceinline__ bool wait_u32(uint32_t bar, uint32_t parity, volatile
         if (abort_flag != nullptr && *abort_flag != 0) return false;
         if (clock64() - t0 > kWaitLimitCycles) return false;
     }
+}
+
+// Handshakes between the two blocks of a pair (a cluster): the address of a barrier or of a piece of the staging
+// buffer in the other block, an arrival there that publishes this thread's (and, after a warp barrier, its warp's)
+// writes to the cluster, a wait that sees what the other block published, and a float32 addition into the other
+// block's shared memory.
+__device__ __forceinline__ uint32_t peer_address(uint32_t local, uint32_t rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+    return remote;
+}
+__device__ __forceinline__ void arrive_at_peer(uint32_t remote_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
+}
+__device__ __forceinline__ bool try_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+        if (try_wait_cluster(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; ++i)
+            if (try_wait_cluster(bar, parity)) return true;
+        if (abort_flag != nullptr && *abort_flag != 0) return false;
+        if (clock64() - t0 > kWaitLimitCycles) return false;
+    }
+}
+__device__ __forceinline__ void store_at_peer(uint32_t remote, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(remote), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
 
 __device__ __forceinline__ void expect_tx_u32(uint32_t bar, uint32_t bytes) {
@@ -171,7 +211,13 @@ struct KvTarget {
     int q_dim, n_kv_head, head_dim, page_shift;
 };
 
-template <typename TO, int ACT, bool HAS_RES, bool KV>
+// PAIR: two blocks (a cluster) share every tile, each with half of the k-blocks and its own accumulator, and each
+// finishes half of the tile's strips (block r the strips r, r + 2, ...): it sends its sums of the other block's strips
+// into that block's staging buffer through distributed shared memory (the slot of the neighbouring strip, which that
+// block does not use), and adds what it receives for its own strips, with bias and residual, before it stores them.
+// A product with few tiles and a long reduction (the down projection) gets twice the blocks without handing partial
+// tiles through global memory.  Float32 output without activation, an even number of strips.
+template <typename TO, int ACT, bool HAS_RES, bool KV, bool PAIR = false>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                        const __grid_constant__ CUtensorMap map_res, const __grid_constant__ CUtensorMap map_out,
@@ -193,7 +239,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m_tiles = (M + kLaneTile - 1) / kLaneTile, n_tiles = (N + BN - 1) / BN;
     const int total = m_tiles * n_tiles;
-    const int n_kb = (K + kBlockK - 1) / kBlockK;
+    uint32_t rank = 0;
+    if constexpr (PAIR) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int cta = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x, n_cta = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+    const int all_kb = (K + kBlockK - 1) / kBlockK;
+    const int kb_lo = PAIR && rank != 0 ? (all_kb + 1) / 2 : 0;           // this block's k-blocks: kb_lo .. kb_lo + n_kb - 1
+    const int n_kb = PAIR ? (rank == 0 ? (all_kb + 1) / 2 : all_kb - (all_kb + 1) / 2) : all_kb;
+    const bool res_here = HAS_RES;
+    const int res_first = PAIR ? (int)rank : 0, res_step = PAIR ? 2 : 1;          // the strips whose residual this block needs
     const uint32_t acc_stride = BN > 128 ? 256u : 128u;               // columns between the two accumulators
     const uint32_t tmem_cols = 2 * acc_stride;
 
@@ -212,6 +265,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         }
         mbar_init(&c->res_full, 1);
         mbar_init(&c->staging_free, 2);
+        mbar_init(&c->peer_sent, kEpilogueWarps);
+        mbar_init(&c->may_send, kEpilogueWarps);
         c->abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -224,6 +279,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
     tc_fence_after();
     const uint32_t tmem_base = c->tmem_base;
     if (threadIdx.x == 0) stamp(timing, 1);
+    if constexpr (PAIR) {
+        // Both blocks' barriers exist before one arrives at the other's.
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
 
     if (warp == 0) {
         if (lane == 0) {
@@ -241,17 +301,17 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             // ended (they do not depend on it); activations and residual follow once it has.
             const int ahead = res_at + 1;
             int kb_start = 0;
-            if ((int)blockIdx.x < total) {
-                const int tile = blockIdx.x;
+            if (cta < total) {
+                const int tile = cta;
                 const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
                 for (int kb = 0; kb < ahead; ++kb) {
                     expect_tx_u32(full_u32 + 8 * kb, stage_bytes);
-                    tma_load_u32(stages_u32 + kb * stage_bytes + kATileBytes, &map_w, full_u32 + 8 * kb, kb * kBlockK, n0);
+                    tma_load_u32(stages_u32 + kb * stage_bytes + kATileBytes, &map_w, full_u32 + 8 * kb, (kb_lo + kb) * kBlockK, n0);
                 }
                 lb_wait_for_predecessor();
                 lb_dependents_may_launch();
                 for (int kb = 0; kb < ahead; ++kb)
-                    tma_load_u32(stages_u32 + kb * stage_bytes, &map_a, full_u32 + 8 * kb, kb * kBlockK, m0);
+                    tma_load_u32(stages_u32 + kb * stage_bytes, &map_a, full_u32 + 8 * kb, (kb_lo + kb) * kBlockK, m0);
                 issued = ahead;
                 last_stage = ahead - 1;
                 last_parity = 0;
@@ -260,16 +320,16 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     st = 0;
                     empty_parity ^= 1;
                 }
-                if (HAS_RES) {                     // the staging buffer is free before the first tile
-                    mbar_expect_tx(&c->res_full, (uint32_t)n_strips * kStripBytes);
-                    for (int sp = 0; sp < n_strips; ++sp)
+                if (res_here) {                    // the staging buffer is free before the first tile
+                    mbar_expect_tx(&c->res_full, (uint32_t)((n_strips - res_first + res_step - 1) / res_step) * kStripBytes);
+                    for (int sp = res_first; sp < n_strips; sp += res_step)
                         tma_load_2d(staging + (size_t)sp * kStripBytes, &map_res, &c->res_full, n0 + sp * kStripCols, m0);
                     res_in_flight = true;
                     res_parity = 0;
                 }
                 kb_start = ahead;
             }
-            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+            for (int tile = cta; tile < total && ok; tile += n_cta, ++it) {
                 const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
                 for (int kb = kb_start; kb < n_kb; ++kb) {
                     if (!wait_u32(empty_u32 + 8 * st, empty_parity, abort_flag)) {
@@ -279,8 +339,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                     }
                     const uint32_t dst = stages_u32 + st * stage_bytes, bar = full_u32 + 8 * st;
                     expect_tx_u32(bar, stage_bytes);
-                    tma_load_u32(dst, &map_a, bar, kb * kBlockK, m0);
-                    tma_load_u32(dst + kATileBytes, &map_w, bar, kb * kBlockK, n0);
+                    tma_load_u32(dst, &map_a, bar, (kb_lo + kb) * kBlockK, m0);
+                    tma_load_u32(dst + kATileBytes, &map_w, bar, (kb_lo + kb) * kBlockK, n0);
                     ++issued;
                     last_stage = st;
                     last_parity = empty_parity ^ 1;
@@ -288,14 +348,14 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                         st = 0;
                         empty_parity ^= 1;
                     }
-                    if (HAS_RES && kb == res_at) {
+                    if (res_here && kb == res_at) {
                         if (!mbar_wait(&c->staging_free, (it & 1) ^ 1, abort_flag)) {
                             give_up(c, status, 4, 0);
                             ok = false;
                             break;
                         }
-                        mbar_expect_tx(&c->res_full, (uint32_t)n_strips * kStripBytes);
-                        for (int sp = 0; sp < n_strips; ++sp)
+                        mbar_expect_tx(&c->res_full, (uint32_t)((n_strips - res_first + res_step - 1) / res_step) * kStripBytes);
+                        for (int sp = res_first; sp < n_strips; sp += res_step)
                             tma_load_2d(staging + (size_t)sp * kStripBytes, &map_res, &c->res_full, n0 + sp * kStripCols, m0);
                         res_in_flight = true;
                         res_parity = it & 1;
@@ -321,7 +381,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             uint32_t st = 0, full_parity = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++it) {
+            for (int tile = cta; tile < total && ok; tile += n_cta, ++it) {
                 const int buf = it & 1;
                 if (!mbar_wait(&c->acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) {
                     give_up(c, status, 5, buf);
@@ -366,13 +426,13 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         lb_wait_for_predecessor();           // before anything this block stores, and before a cache page is written
         lb_dependents_may_launch();
         int it = 0;
-        for (int tile = blockIdx.x; tile < total; tile += gridDim.x, ++it) {
+        for (int tile = cta; tile < total; tile += n_cta, ++it) {
             const int m0 = (tile % m_tiles) * kLaneTile, n0 = (tile / m_tiles) * BN;
             const int buf = it & 1;
             // The bias of this tile's features.  (The last tile's readers are past their last barrier.)
             for (int i = et; i < BN; i += kEpilogueThreads) bias_s[i] = (bias != nullptr && n0 + i < N) ? bias[n0 + i] : 0.0f;
             bool ok = mbar_wait(&c->acc_full[buf], (it >> 1) & 1, abort_flag);
-            if (ok && HAS_RES) ok = mbar_wait(&c->res_full, it & 1, abort_flag);
+            if (ok && res_here) ok = mbar_wait(&c->res_full, it & 1, abort_flag);
             if (!ok) give_up(c, status, 3, quarter);
             named_barrier(1, kEpilogueThreads);
             if (*abort_flag != 0) break;                               // the same answer for all epilogue threads
@@ -381,6 +441,71 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
             const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)buf * acc_stride;
             int slot = -1;                                             // where this thread's token lies in the cache
             if constexpr (KV) slot = m0 + row < M ? __ldg(kv.slot_mapping + m0 + row) : -1;
+            if constexpr (PAIR) {
+                const uint32_t peer = rank ^ 1u;
+                const int half = n_strips / 2;
+                // This block's sums of the other block's strips go to that block's staging buffer (the slot beside the
+                // strip's own), once that block has read what was sent for the tile before.
+                if (it > 0 && !wait_cluster(smem_u32(&c->may_send), (uint32_t)((it - 1) & 1), abort_flag)) give_up(c, status, 6, quarter);
+                if (*abort_flag == 0) {
+                    const uint32_t peer_row = peer_address(row_u32, peer);
+                    for (int j = group; j < half; j += 2) {
+                        const int sp = (int)peer + 2 * j;
+                        uint32_t v[32];
+                        tmem_ld32(t_row + (uint32_t)(sp * 32), v);
+                        tmem_ld_wait();
+                        const uint32_t slot = peer_row + (uint32_t)(sp ^ 1) * kStripBytes;
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch)
+                            store_at_peer(slot + (((uint32_t)ch ^ swz) << 4), v[4 * ch], v[4 * ch + 1], v[4 * ch + 2], v[4 * ch + 3]);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) arrive_at_peer(peer_address(smem_u32(&c->peer_sent), peer));
+                // This block's own strips: its sums, the other block's (received beside them), bias and residual.
+                if (!wait_cluster(smem_u32(&c->peer_sent), (uint32_t)(it & 1), abort_flag)) give_up(c, status, 7, quarter);
+                for (int j = group; j < half; j += 2) {
+                    const int sp = (int)rank + 2 * j;
+                    const uint32_t strip = row_u32 + (uint32_t)sp * kStripBytes, inbox = row_u32 + (uint32_t)(sp ^ 1) * kStripBytes;
+                    const uint32_t b = bias_u32 + (uint32_t)(sp * kStripCols) * 4u;
+                    uint32_t v[32];
+                    tmem_ld32(t_row + (uint32_t)(sp * 32), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch) {
+                        const uint32_t off = ((uint32_t)ch ^ swz) << 4;
+                        const float4 bb = lds4(b + 16 * ch), other = lds4(inbox + off);
+                        float4 y;
+                        y.x = (__uint_as_float(v[4 * ch]) + other.x) + bb.x;
+                        y.y = (__uint_as_float(v[4 * ch + 1]) + other.y) + bb.y;
+                        y.z = (__uint_as_float(v[4 * ch + 2]) + other.z) + bb.z;
+                        y.w = (__uint_as_float(v[4 * ch + 3]) + other.w) + bb.w;
+                        if constexpr (HAS_RES) {
+                            const float4 r = lds4(strip + off);
+                            y.x += r.x; y.y += r.y; y.z += r.z; y.w += r.w;
+                        }
+                        sts4(strip + off, y);
+                    }
+                    fence_async_shared();
+                    named_barrier(2 + group, 128);
+                    if (elected) {
+                        if (n0 + sp * kStripCols < N) tma_store_2d(&map_out, staging + (size_t)sp * kStripBytes, n0 + sp * kStripCols, m0);
+                        bulk_commit();
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&c->acc_empty[buf]);
+                    arrive_at_peer(peer_address(smem_u32(&c->may_send), peer));      // what it sent has been read
+                }
+                if (elected) {
+                    bulk_wait_read();
+                    mbar_arrive(&c->staging_free);
+                }
+                if (tile + n_cta < total) named_barrier(1, kEpilogueThreads);
+                continue;
+            }
             for (int sp = group; sp < n_strips; sp += 2) {
                 const uint32_t strip = row_u32 + (uint32_t)sp * kStripBytes;
                 const uint32_t b = bias_u32 + (uint32_t)(sp * kStripCols) * 4u;
@@ -460,7 +585,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 mbar_arrive(&c->staging_free);
             }
             // Nobody writes the staging buffer or the bias again before both groups are done with this tile's.
-            if (tile + (int)gridDim.x < total) named_barrier(1, kEpilogueThreads);
+            if (tile + n_cta < total) named_barrier(1, kEpilogueThreads);
         }
         if (elected) {
             bulk_wait_all();
@@ -474,6 +599,11 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
         tc_fence_after();
         tmem_dealloc(tmem_base, tmem_cols);
     }
+    if constexpr (PAIR) {
+        // Neither block leaves while the other may still reach into its shared memory (also after a wait ran out).
+        asm volatile("barrier.cluster.arrive.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+    }
 }
 
 size_t smem_bytes(int BN, int n_stages, int elem) {
@@ -485,6 +615,36 @@ int stages_for(int BN, int elem) {
     int n = 0;
     while (n < kMaxStages && smem_bytes(BN, n + 1, elem) <= kSmemLimit) ++n;
     return n;
+}
+
+// The feature tile whose rounds over the SMs cost least, and that cost in nanoseconds (0: none fits).  `pairs`: every
+// tile is shared by two blocks with half of the k-blocks each (one round only: tiles x 2 blocks must fit the SMs).
+int best_tile(int elem, int M, int N, int K, int n_sm, bool pairs, long* cost_out) {
+    const int step = elem == 4 ? 32 : 64;
+    const long m_tiles = (M + kLaneTile - 1) / kLaneTile;
+    const long n_kb = (K + kBlockK - 1) / kBlockK;
+    int best = 0;
+    long best_cost = 0;
+    for (int bn = 256; bn >= step; bn -= step) {
+        if (stages_for(bn, elem) < 3) continue;
+        if (bn > step && bn - step >= N) continue;                      // wider than the matrix by a whole strip
+        const long tiles = m_tiles * ((N + bn - 1) / bn);
+        long cost;
+        if (pairs) {
+            // Half the k-blocks, and about 2.5 us for the exchange: the first block's stores wait for the second's sums.
+            if (tiles * 2 > n_sm || n_kb < 8 || (bn / step) % 2 != 0) continue;
+            cost = (n_kb + 1) / 2 * (bn > 192 ? 420 : 300) + 1000 + 1000 * bn / 256 + 2500;
+        } else {
+            const long rounds = (tiles + n_sm - 1) / n_sm;
+            cost = rounds * (n_kb * (bn > 192 ? 420 : 300) + 1000 + 1000 * bn / 256);
+        }
+        if (best == 0 || cost < best_cost) {
+            best = bn;
+            best_cost = cost;
+        }
+    }
+    if (cost_out != nullptr) *cost_out = best_cost;
+    return best;
 }
 
 }  // namespace
@@ -508,23 +668,7 @@ extern "C" int lb_gemm_persistent_tile(int out_dtype, const void* A, int64_t lda
     // B200: a tcgen05.mma of 128 rows takes about as long for 32 columns as for 192 (the tensor core walks the rows),
     // so a k-block costs about 300 ns up to 192 columns and 420 ns at 256; the epilogue of a tile costs about a
     // microsecond plus one per 256 columns.  Ties go to the wider tile (fewer blocks fetch the same activations).
-    const int step = elem == 4 ? 32 : 64;
-    const long m_tiles = (M + kLaneTile - 1) / kLaneTile;
-    const long n_kb = (K + kBlockK - 1) / kBlockK;
-    int best = 0;
-    long best_cost = 0;
-    for (int bn = 256; bn >= step; bn -= step) {
-        if (stages_for(bn, elem) < 3) continue;
-        if (bn > step && bn - step >= N) continue;                      // wider than the matrix by a whole strip
-        const long tiles = m_tiles * ((N + bn - 1) / bn);
-        const long rounds = (tiles + n_sm - 1) / n_sm;
-        const long cost = rounds * (n_kb * (bn > 192 ? 420 : 300) + 1000 + 1000 * bn / 256);
-        if (best == 0 || cost < best_cost) {
-            best = bn;
-            best_cost = cost;
-        }
-    }
-    return best;
+    return best_tile(elem, M, N, K, n_sm, false, nullptr);
 }
 
 // Whether lb_gemm_persistent can send the features from q_dim on to the pages of a cache instead of `out`.
@@ -541,6 +685,16 @@ extern "C" int lb_gemm_persistent_timing(unsigned long long* buffer) {
     g_timing = buffer;
     return LB_OK;
 }
+
+// LIYAB_B200_GEMM_PAIRS=0 in the environment keeps every tile with one block (measurements).
+static bool pairs_enabled() {
+    static const bool on = [] { const char* e = getenv("LIYAB_B200_GEMM_PAIRS"); return e == nullptr || e[0] != '0'; }();
+    return on;
+}
+
+static int launch_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual,
+                             int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, int bn, bool pair, const KvTarget& kv,
+                             int n_sm, void* stream);
 
 extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias,
                                   const float* residual, int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act,
@@ -567,7 +721,33 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
                        "output where a residual is given (M=%d K=%d lda=%lld ldw=%lld ldo=%lld ldr=%lld)",
                        M, K, (long long)lda, (long long)ldw, (long long)ldo, (long long)ldr);
     const int step = elem == 4 ? 32 : 64;
+    static int n_sm = 0;
+    if (n_sm == 0) {
+        int dev = 0;
+        LB_CHECK_CUDA(cudaGetDevice(&dev));
+        LB_CHECK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
+    }
+    // Few tiles and a long reduction (float32 out, no activation): two blocks a tile, where the estimate says it pays.
+    bool pair = false;
+    int bn_used = bn;
+    if (feature_tile <= 0 && elem == 4 && act == LB_ACT_NONE && kv_cache == nullptr && pairs_enabled()) {
+        long single = 0, paired = 0;
+        best_tile(elem, M, N, K, n_sm, false, &single);
+        const int bn_pair = best_tile(elem, M, N, K, n_sm, true, &paired);
+        if (bn_pair > 0 && paired < single) {
+            pair = true;
+            bn_used = bn_pair;
+        }
+    }
     LB_CHECK_ARG(bn % step == 0 && bn >= step && bn <= 256, "gemm_persistent: feature tile %d (a multiple of %d up to 256)", bn, step);
+    return launch_persistent(out_dtype, A, lda, W, ldw, bias, residual, ldr, out, ldo, M, N, K, act, bn_used, pair, kv, n_sm, stream);
+}
+
+static int launch_persistent(int out_dtype, const void* A, int64_t lda, const void* W, int64_t ldw, const float* bias, const float* residual,
+                             int64_t ldr, void* out, int64_t ldo, int M, int N, int K, int act, int bn, bool pair, const KvTarget& kv,
+                             int n_sm, void* stream) {
+    const int elem = out_dtype == LB_F32 ? 4 : 2;
+    const void* kv_cache = kv.cache;
     const int n_stages = stages_for(bn, elem);
     LB_CHECK_ARG(n_stages >= 2, "gemm_persistent: feature tile %d leaves no room for two stages", bn);
     CUtensorMap map_a, map_w, map_res, map_out;
@@ -580,14 +760,8 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
     int* status = nullptr;
     rc = lb_tc_status_word(&status);
     if (rc != LB_OK) return rc;
-    static int n_sm = 0;
-    if (n_sm == 0) {
-        int dev = 0;
-        LB_CHECK_CUDA(cudaGetDevice(&dev));
-        LB_CHECK_CUDA(cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, dev));
-    }
     const long tiles = (long)((M + kLaneTile - 1) / kLaneTile) * ((N + bn - 1) / bn);
-    const int grid = (int)(tiles < n_sm ? tiles : n_sm);
+    const int grid = pair ? (int)(2 * tiles) : (int)(tiles < n_sm ? tiles : n_sm);
     // More than half of an SM's shared memory always, so that two blocks (each holding up to all of tensor memory)
     // never share an SM.
     size_t smem = smem_bytes(bn, n_stages, elem);
@@ -612,7 +786,22 @@ extern "C" int lb_gemm_persistent(int out_dtype, const void* A, int64_t lda, con
         case LB_ACT_GELU_ERF: LB_GO(TO, LB_ACT_GELU_ERF, RES); break;       \
         default: return lb_fail(LB_ERR_INVALID_ARGUMENT, "gemm_persistent: unknown activation %d", act); \
     }
-    if (elem == 4) {
+    if (pair) {
+#define LB_GO_PAIR(RES)                                                                                                  \
+    {                                                                                                                    \
+        static bool configured = false;                                                                                  \
+        if (!configured) {                                                                                               \
+            LB_CHECK_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<float, LB_ACT_NONE, RES, false, true>,            \
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemLimit));           \
+            configured = true;                                                                                           \
+        }                                                                                                                \
+        LB_CHECK_CUDA(lb_launch_overlapped_cluster(0, 2, gemm_persistent_kernel<float, LB_ACT_NONE, RES, false, true>, dim3(grid),        \
+                                                   dim3(kThreads), smem, s, map_a, map_w, map_res, map_out, bias, M, N, K, bn, n_stages, \
+                                                   status, g_timing, kv));                                               \
+    }
+        if (residual != nullptr) LB_GO_PAIR(true) else LB_GO_PAIR(false)
+#undef LB_GO_PAIR
+    } else if (elem == 4) {
         if (residual != nullptr) LB_GO_ACT(float, true) else LB_GO_ACT(float, false)
     } else if (kv_cache != nullptr) {
         LB_GO_KV(__nv_bfloat16, LB_ACT_NONE, false, true)
