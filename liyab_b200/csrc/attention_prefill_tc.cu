@@ -203,6 +203,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             constexpr uint32_t idesc_s = umma_idesc(kBM, kBN);
             constexpr uint32_t idesc_o = umma_idesc_b_mn(kBM, kHD);
             const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+            // Descriptors are made once per operand tile and moved by addition (the start address sits in the low bits
+            // in units of 16 bytes, and no tile crosses the field's range): this thread's instructions between two
+            // products are what the softmax threads wait for.
+            const uint64_t dq = umma_desc(q_addr);
             bool ok = mbar_wait(&c->q_full, 0, abort_flag);
             if (!ok) give_up(c, status, 2);
             auto scores = [&](int tile) -> bool {
@@ -211,10 +215,10 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 const int sb = tile & 1;
                 if (!mbar_wait(&c->s_free[sb], ((tile >> 1) & 1) ^ 1, abort_flag)) { give_up(c, status, 4); return false; }
                 tc_fence_after();
-                const uint32_t k_addr = smem_u32(k_s + (size_t)st * kTileBytes);
+                const uint64_t dk = umma_desc(smem_u32(k_s + (size_t)st * kTileBytes));
 #pragma unroll
                 for (int kk = 0; kk < kHD / kUmmaK; ++kk)
-                    umma_bf16(tmem_base + sb * kBN, umma_desc(q_addr + kk * 32), umma_desc(k_addr + kk * 32), idesc_s, kk != 0 ? 1u : 0u);
+                    umma_bf16(tmem_base + sb * kBN, dq + (uint64_t)(kk * 2), dk + (uint64_t)(kk * 2), idesc_s, kk != 0 ? 1u : 0u);
                 umma_commit(&c->s_full[sb]);
                 return true;
             };
@@ -227,12 +231,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 if (!mbar_wait(&c->p_full[pb], (tile >> 1) & 1, abort_flag)) { give_up(c, status, 5); break; }
                 tc_fence_after();
                 const int st = tile % kStages;
-                const uint32_t v_addr = smem_u32(v_s + (size_t)st * kTileBytes);
+                const uint64_t dp = umma_desc(p_addr + pb * 2 * kTileBytes);
+                const uint64_t dv = umma_desc_mn(smem_u32(v_s + (size_t)st * kTileBytes));
 #pragma unroll
                 for (int ks = 0; ks < kBN / kUmmaK; ++ks) {
                     // P: key half ks / 4 (its own 16 KB tile), 32 bytes per 16 keys within it; V: 16 keys = 2048 bytes.
-                    const uint64_t da = umma_desc(p_addr + (pb * 2 + (ks >> 2)) * kTileBytes + (ks & 3) * 32);
-                    const uint64_t db = umma_desc_mn(v_addr + ks * 2048);
+                    const uint64_t da = dp + (uint64_t)(((ks >> 2) * kTileBytes + (ks & 3) * 32) >> 4);
+                    const uint64_t db = dv + (uint64_t)((ks * 2048) >> 4);
                     umma_bf16(tmem_base + kOCol, da, db, idesc_o, (tile | ks) != 0 ? 1u : 0u);
                 }
                 umma_commit(&c->kv_empty[st]);      // keys and values of the stage have been read
