@@ -445,7 +445,8 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_c
                 const uint32_t peer = rank ^ 1u;
                 const int half = n_strips / 2;
                 // This block's sums of the other block's strips go to that block's staging buffer (the slot beside the
-                // strip's own), once that block has read what was sent for the tile before.
+                // strip's own), once that block has read what was sent for the tile before.  (The host launches one
+                // pair per tile today, so a pair's second tile and its wait are not exercised by any test.)
                 if (it > 0 && !wait_cluster(smem_u32(&c->may_send), (uint32_t)((it - 1) & 1), abort_flag)) give_up(c, status, 6, quarter);
                 if (*abort_flag == 0) {
                     const uint32_t peer_row = peer_address(row_u32, peer);
