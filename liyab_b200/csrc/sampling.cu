@@ -500,7 +500,7 @@ sample_kernel(const float* __restrict__ logits, int64_t row_stride, int vocab, c
 
     // ---- rank of each tie at kth_key in index order (only if some ties are cut).
     int tie_rank_base = 0;
-    {
+    if (k > 0 && k < vocab) {          // without top-k every logit is a member, whatever its rank among equals
         int mine = 0;
         for_range([&](int, float xi) { mine += order_key(xi) == kth_key ? 1 : 0; });
         int total;
